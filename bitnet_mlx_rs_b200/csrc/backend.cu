@@ -1,0 +1,516 @@
+// Host side of the library: the state the reference keeps in its bitnet-cuda crate
+// (device, stream pool, memory accounting, kernel counters, weight life cycle), in C++
+// behind opaque C handles.  Mirrors CudaBackend (bitnet-cuda/src/backend.rs:40-213),
+// CudaMemoryManager (memory.rs:47-186), CudaStream/CudaStreamPool (stream.rs:31-207) and
+// W2A8GemvKernel's counters (kernels/w2a8_gemv.rs:63-189).
+#include <atomic>
+#include <chrono>
+#include <cstring>
+#include <memory>
+#include <mutex>
+#include <new>
+#include <unordered_map>
+#include <vector>
+
+#include "common.cuh"
+
+namespace bitnet {
+namespace host {
+
+// CudaMemoryManager: a byte budget over cudaMalloc (memory.rs:79-127).  Allocations are
+// zero-filled like alloc_zeros; exceeding the budget is MemoryAllocation, not a CUDA call.
+class CudaMemoryManager {
+public:
+    explicit CudaMemoryManager(size_t pool_size) : pool_size_(pool_size) {}
+    ~CudaMemoryManager()
+    {
+        for (auto &kv : live_) cudaFree(kv.first);
+    }
+    bitnet_status_t allocate(size_t bytes, void **out)
+    {
+        if (!out) return fail(BITNET_ERR_NULL_POINTER, "allocate: null output");
+        *out = nullptr;
+        std::lock_guard<std::mutex> lock(mu_);
+        if (allocated_ + bytes > pool_size_)
+            return fail(BITNET_ERR_MEMORY_ALLOCATION, "Allocation would exceed pool size: %zu + %zu > %zu", allocated_,
+                        bytes, pool_size_);
+        void *p = nullptr;
+        BITNET_CUDA(cudaMalloc(&p, bytes ? bytes : 1));
+        const cudaError_t err = cudaMemset(p, 0, bytes);
+        if (err != cudaSuccess) {
+            cudaFree(p);
+            return check_cuda(err, "cudaMemset");
+        }
+        live_[p] = bytes;
+        allocated_ += bytes;
+        if (allocated_ > peak_) peak_ = allocated_;
+        ++count_;
+        *out = p;
+        return BITNET_OK;
+    }
+    bitnet_status_t release(void *p)
+    {
+        if (!p) return BITNET_OK;
+        std::lock_guard<std::mutex> lock(mu_);
+        auto it = live_.find(p);
+        if (it == live_.end()) return fail(BITNET_ERR_INVALID_CONFIG, "free: pointer was not allocated by this backend");
+        allocated_ -= it->second;
+        live_.erase(it);
+        return check_cuda(cudaFree(p), "cudaFree");
+    }
+    float utilization_percent() const
+    {
+        return pool_size_ ? (float)allocated_ / (float)pool_size_ * 100.0f : 0.0f;
+    }
+    size_t allocated() const { return allocated_; }
+    size_t pool_size() const { return pool_size_; }
+    size_t peak() const { return peak_; }
+    uint64_t allocation_count() const { return count_; }
+
+private:
+    std::mutex mu_;
+    size_t pool_size_;
+    size_t allocated_ = 0, peak_ = 0;
+    uint64_t count_ = 0;
+    std::unordered_map<void *, size_t> live_;
+};
+
+// One compute stream with the buffers the host-facing calls stage through.
+struct CudaStream {
+    cudaStream_t stream = nullptr;
+    std::atomic<uint64_t> operation_count{0};
+    void *pinned = nullptr;   // host staging, grown on demand
+    size_t pinned_bytes = 0;
+    void *dev = nullptr;      // device staging (x, h, y) + workspace, grown on demand
+    size_t dev_bytes = 0;
+    std::mutex mu;            // one host-facing call at a time per stream
+};
+
+struct Weights {
+    uint8_t *packed_dev = nullptr;
+    size_t N = 0, K = 0;
+    float w_scale = 1.0f;
+    unsigned long long invalid_codes = 0;
+};
+
+class CudaBackend {
+public:
+    bitnet_backend_config cfg;
+    int device = 0;
+    std::unique_ptr<CudaMemoryManager> memory;
+    std::vector<std::unique_ptr<CudaStream>> streams;
+    // W2A8GemvKernel counters (w2a8_gemv.rs:69-70, :161-189)
+    std::atomic<uint64_t> op_count{0};
+    std::atomic<uint64_t> total_time_ns{0};
+    std::atomic<uint64_t> total_bytes{0};
+
+    ~CudaBackend()
+    {
+        cudaSetDevice(device);
+        for (auto &s : streams) {
+            if (s->stream) cudaStreamSynchronize(s->stream);
+            if (s->pinned) cudaFreeHost(s->pinned);
+            if (s->dev) memory->release(s->dev);
+            if (s->stream) cudaStreamDestroy(s->stream);
+        }
+    }
+
+    bitnet_status_t stream_at(size_t idx, CudaStream **out)
+    {
+        if (idx >= streams.size())
+            return fail(BITNET_ERR_INVALID_CONFIG, "Stream index %zu out of bounds (max: %zu)", idx, streams.size());
+        *out = streams[idx].get();
+        return BITNET_OK;
+    }
+
+    bitnet_status_t ensure_staging(CudaStream &s, size_t host_bytes, size_t dev_bytes)
+    {
+        if (host_bytes > s.pinned_bytes) {
+            if (s.pinned) cudaFreeHost(s.pinned);
+            s.pinned = nullptr;
+            s.pinned_bytes = 0;
+            BITNET_CUDA(cudaMallocHost(&s.pinned, host_bytes));
+            s.pinned_bytes = host_bytes;
+        }
+        if (dev_bytes > s.dev_bytes) {
+            if (s.dev) BITNET_TRY(memory->release(s.dev));
+            s.dev = nullptr;
+            s.dev_bytes = 0;
+            BITNET_TRY(memory->allocate(dev_bytes, &s.dev));
+            s.dev_bytes = dev_bytes;
+        }
+        return BITNET_OK;
+    }
+
+    void record(uint64_t ns, uint64_t bytes)
+    {
+        op_count.fetch_add(1, std::memory_order_relaxed);
+        total_time_ns.fetch_add(ns, std::memory_order_relaxed);
+        total_bytes.fetch_add(bytes, std::memory_order_relaxed);
+    }
+};
+
+// W2A8GemvConfig validation (w2a8_gemv.rs:15-38: "must be multiple of 32").
+static bitnet_status_t validate_config(const bitnet_backend_config &c)
+{
+    if (c.num_streams == 0 || c.num_streams > 64)
+        return fail(BITNET_ERR_INVALID_CONFIG, "num_streams must be in 1..64 (got %zu)", c.num_streams);
+    if (c.w2a8_config.block_size == 0 || c.w2a8_config.block_size % 32 != 0 || c.w2a8_config.block_size > 1024)
+        return fail(BITNET_ERR_INVALID_CONFIG, "block_size must be a multiple of 32 in 32..1024 (got %u)",
+                    c.w2a8_config.block_size);
+    if (c.w2a8_config.grid_strategy < BITNET_GRID_FIXED || c.w2a8_config.grid_strategy > BITNET_GRID_OCCUPANCY)
+        return fail(BITNET_ERR_INVALID_CONFIG, "unknown grid strategy %d", c.w2a8_config.grid_strategy);
+    if (c.w2a8_config.coalescing_level < BITNET_COALESCE_NONE || c.w2a8_config.coalescing_level > BITNET_COALESCE_AGGRESSIVE)
+        return fail(BITNET_ERR_INVALID_CONFIG, "unknown coalescing level %d", c.w2a8_config.coalescing_level);
+    return BITNET_OK;
+}
+
+static uint64_t now_ns()
+{
+    return (uint64_t)std::chrono::duration_cast<std::chrono::nanoseconds>(
+               std::chrono::steady_clock::now().time_since_epoch()).count();
+}
+
+}  // namespace host
+}  // namespace bitnet
+
+using namespace bitnet;
+using namespace bitnet::host;
+
+struct bitnet_backend { CudaBackend impl; };
+struct bitnet_weights { Weights impl; };
+
+extern "C" void bitnet_backend_config_default(bitnet_backend_config *cfg)
+{
+    if (!cfg) return;
+    memset(cfg, 0, sizeof(*cfg));
+    cfg->device_id = 0;                                  // backend.rs:27-37
+    cfg->memory_pool_size = (size_t)1024 * 1024 * 1024;
+    cfg->num_streams = 4;
+    cfg->enable_profiling = 0;
+    cfg->w2a8_config.block_size = 256;                   // w2a8_gemv.rs:28-38
+    cfg->w2a8_config.grid_strategy = BITNET_GRID_DYNAMIC;
+    cfg->w2a8_config.grid_fixed = 0;
+    cfg->w2a8_config.enable_weight_permutation = 1;
+    cfg->w2a8_config.enable_dp4a = 1;
+    cfg->w2a8_config.coalescing_level = BITNET_COALESCE_AGGRESSIVE;
+}
+
+extern "C" bitnet_status_t bitnet_backend_create(const bitnet_backend_config *cfg, bitnet_backend **out)
+{
+    if (!out) return fail(BITNET_ERR_NULL_POINTER, "bitnet_backend_create: null output");
+    *out = nullptr;
+    bitnet_backend_config c;
+    if (cfg) c = *cfg; else bitnet_backend_config_default(&c);
+    BITNET_TRY(validate_config(c));
+
+    bitnet_device_info info;
+    BITNET_TRY(bitnet_query_device((int32_t)c.device_id, &info));
+    // The kernels are sm_100a binaries: anything else cannot run them
+    // (the reference asks for CC >= 7.5, backend.rs:196-201).
+    if (info.cc_major != 10)
+        return fail(BITNET_ERR_UNSUPPORTED_OPERATION,
+                    "Compute capability %d.%d insufficient for BitNet operations (requires 10.x, sm_100a)",
+                    info.cc_major, info.cc_minor);
+    const size_t min_memory = (size_t)512 * 1024 * 1024;   // backend.rs:204-210
+    if (info.free_bytes < min_memory)
+        return fail(BITNET_ERR_MEMORY_ALLOCATION, "Insufficient GPU memory: %zu bytes available, %zu bytes required",
+                    info.free_bytes, min_memory);
+
+    BITNET_CUDA(cudaSetDevice((int)c.device_id));
+    bitnet_backend *b = new (std::nothrow) bitnet_backend();
+    if (!b) return fail(BITNET_ERR_MEMORY_ALLOCATION, "out of host memory");
+    b->impl.cfg = c;
+    b->impl.device = (int)c.device_id;
+    b->impl.memory.reset(new CudaMemoryManager(c.memory_pool_size));
+    for (size_t i = 0; i < c.num_streams; ++i) {
+        std::unique_ptr<CudaStream> s(new CudaStream());
+        const cudaError_t err = cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking);
+        if (err != cudaSuccess) {
+            delete b;
+            return check_cuda(err, "cudaStreamCreateWithFlags");
+        }
+        b->impl.streams.push_back(std::move(s));
+    }
+    *out = b;
+    return BITNET_OK;
+}
+
+extern "C" void bitnet_backend_destroy(bitnet_backend *b) { delete b; }
+
+extern "C" bitnet_status_t bitnet_backend_stream(bitnet_backend *b, size_t index, bitnet_stream_t *out)
+{
+    if (!b || !out) return fail(BITNET_ERR_NULL_POINTER, "bitnet_backend_stream: null argument");
+    CudaStream *s = nullptr;
+    BITNET_TRY(b->impl.stream_at(index, &s));
+    *out = s->stream;
+    return BITNET_OK;
+}
+
+extern "C" bitnet_status_t bitnet_backend_synchronize(bitnet_backend *b)
+{
+    if (!b) return fail(BITNET_ERR_NULL_POINTER, "bitnet_backend_synchronize: null backend");
+    for (auto &s : b->impl.streams) {
+        const cudaError_t err = cudaStreamSynchronize(s->stream);
+        if (err != cudaSuccess) return fail(BITNET_ERR_STREAM_SYNC, "stream synchronize: %s", cudaGetErrorString(err));
+    }
+    return BITNET_OK;
+}
+
+extern "C" bitnet_status_t bitnet_backend_get_performance_stats(bitnet_backend *b, bitnet_performance_stats *out)
+{
+    if (!b || !out) return fail(BITNET_ERR_NULL_POINTER, "bitnet_backend_get_performance_stats: null argument");
+    const uint64_t n = b->impl.op_count.load();
+    const uint64_t ns = b->impl.total_time_ns.load();
+    const uint64_t bytes = b->impl.total_bytes.load();
+    out->total_w2a8_operations = n;
+    out->average_execution_time_us = n ? (float)((double)ns / 1e3 / (double)n) : 0.0f;
+    out->memory_utilization_percent = b->impl.memory->utilization_percent();
+    // bandwidth from the bytes the calls actually moved (the reference divides a
+    // hard-coded 1 MB by the mean time, w2a8_gemv.rs:179-189)
+    out->peak_bandwidth_gbps = ns ? (float)((double)bytes / (double)ns) : 0.0f;
+    return BITNET_OK;
+}
+
+extern "C" bitnet_status_t bitnet_backend_allocate(bitnet_backend *b, size_t bytes, void **dev_ptr)
+{
+    if (!b) return fail(BITNET_ERR_NULL_POINTER, "bitnet_backend_allocate: null backend");
+    BITNET_CUDA(cudaSetDevice(b->impl.device));
+    return b->impl.memory->allocate(bytes, dev_ptr);
+}
+
+extern "C" bitnet_status_t bitnet_backend_free(bitnet_backend *b, void *dev_ptr)
+{
+    if (!b) return fail(BITNET_ERR_NULL_POINTER, "bitnet_backend_free: null backend");
+    return b->impl.memory->release(dev_ptr);
+}
+
+extern "C" bitnet_status_t bitnet_backend_copy_to_device(bitnet_backend *b, void *dst_dev, const void *src_host, size_t bytes)
+{
+    if (!b) return fail(BITNET_ERR_NULL_POINTER, "bitnet_backend_copy_to_device: null backend");
+    if (bytes == 0) return BITNET_OK;
+    if (!dst_dev || !src_host) return fail(BITNET_ERR_NULL_POINTER, "bitnet_backend_copy_to_device: null buffer");
+    BITNET_CUDA(cudaMemcpy(dst_dev, src_host, bytes, cudaMemcpyHostToDevice));
+    return BITNET_OK;
+}
+
+extern "C" bitnet_status_t bitnet_backend_copy_to_host(bitnet_backend *b, void *dst_host, const void *src_dev, size_t bytes)
+{
+    if (!b) return fail(BITNET_ERR_NULL_POINTER, "bitnet_backend_copy_to_host: null backend");
+    if (bytes == 0) return BITNET_OK;
+    if (!dst_host || !src_dev) return fail(BITNET_ERR_NULL_POINTER, "bitnet_backend_copy_to_host: null buffer");
+    BITNET_CUDA(cudaMemcpy(dst_host, src_dev, bytes, cudaMemcpyDeviceToHost));
+    return BITNET_OK;
+}
+
+extern "C" bitnet_status_t bitnet_backend_memory_usage(bitnet_backend *b, size_t *allocated, size_t *pool_size)
+{
+    if (!b) return fail(BITNET_ERR_NULL_POINTER, "bitnet_backend_memory_usage: null backend");
+    if (allocated) *allocated = b->impl.memory->allocated();
+    if (pool_size) *pool_size = b->impl.memory->pool_size();
+    return BITNET_OK;
+}
+
+// CudaBackend::w2a8_gemv with validate_w2a8_dimensions (backend.rs:129-157, :217-257).
+extern "C" bitnet_status_t bitnet_backend_w2a8_gemv(bitnet_backend *b, const uint8_t *weights_dev, size_t weights_len,
+                                                    const int8_t *activations_dev, size_t activations_len,
+                                                    int32_t *output_dev, size_t output_len, size_t m, size_t k,
+                                                    size_t stream_idx)
+{
+    if (!b) return fail(BITNET_ERR_NULL_POINTER, "bitnet_backend_w2a8_gemv: null backend");
+    CudaStream *s = nullptr;
+    BITNET_TRY(b->impl.stream_at(stream_idx, &s));
+    const size_t expected = (m * k + 3) / 4;
+    if (weights_len != expected)
+        return fail(BITNET_ERR_INCOMPATIBLE_SHAPES, "Weight tensor size mismatch: expected %zu bytes for %zux%zu matrix, got %zu",
+                    expected, m, k, weights_len);
+    if (activations_len != k)
+        return fail(BITNET_ERR_INCOMPATIBLE_SHAPES, "Activation tensor size mismatch: expected %zu elements, got %zu", k,
+                    activations_len);
+    if (output_len != m)
+        return fail(BITNET_ERR_INCOMPATIBLE_SHAPES, "Output tensor size mismatch: expected %zu elements, got %zu", m,
+                    output_len);
+    const uint64_t t0 = now_ns();
+    BITNET_TRY(bitnet_w2a8_gemv(weights_dev, activations_dev, output_dev, m, k, s->stream));
+    if (b->impl.cfg.enable_profiling) {
+        // profiling mode times the kernel itself, at the price of a synchronisation
+        const cudaError_t err = cudaStreamSynchronize(s->stream);
+        if (err != cudaSuccess) return fail(BITNET_ERR_STREAM_SYNC, "stream synchronize: %s", cudaGetErrorString(err));
+    }
+    b->impl.record(now_ns() - t0, expected + k + 4 * m);
+    s->operation_count.fetch_add(1, std::memory_order_relaxed);
+    return BITNET_OK;
+}
+
+static bitnet_status_t upload_common(bitnet_backend *b, const void *host, bool is_ternary, size_t N, size_t K,
+                                     float w_scale, bitnet_weights **out)
+{
+    if (!b || !out) return fail(BITNET_ERR_NULL_POINTER, "upload: null argument");
+    *out = nullptr;
+    if (!host) return fail(BITNET_ERR_NULL_POINTER, "upload: null host buffer");
+    if (N == 0 || K == 0) return fail(BITNET_ERR_INCOMPATIBLE_SHAPES, "upload: empty weight matrix %zux%zu", N, K);
+    BITNET_CUDA(cudaSetDevice(b->impl.device));
+    const size_t n_values = N * K, n_bytes = (n_values + 3) / 4;
+    void *packed = nullptr, *counter = nullptr, *tmp = nullptr;
+    cudaStream_t s = b->impl.streams[0]->stream;
+    BITNET_TRY(b->impl.memory->allocate(align_up(n_bytes, 256), &packed));
+    bitnet_status_t st = b->impl.memory->allocate(256, &counter);
+    if (st == BITNET_OK) {
+        if (is_ternary) {
+            st = b->impl.memory->allocate(n_values, &tmp);
+            if (st == BITNET_OK) st = check_cuda(cudaMemcpyAsync(tmp, host, n_values, cudaMemcpyHostToDevice, s), "upload ternary");
+            if (st == BITNET_OK) st = bitnet_pack_ternary(static_cast<const int8_t *>(tmp), n_values, static_cast<uint8_t *>(packed), s);
+        } else {
+            st = check_cuda(cudaMemcpyAsync(packed, host, n_bytes, cudaMemcpyHostToDevice, s), "upload packed");
+        }
+    }
+    unsigned long long found = 0;
+    if (st == BITNET_OK) st = bitnet_sanitize_packed(static_cast<uint8_t *>(packed), n_bytes, static_cast<unsigned long long *>(counter), s);
+    if (st == BITNET_OK) st = check_cuda(cudaMemcpyAsync(&found, counter, sizeof(found), cudaMemcpyDeviceToHost, s), "read counter");
+    if (st == BITNET_OK) st = check_cuda(cudaStreamSynchronize(s), "upload sync");
+    if (tmp) b->impl.memory->release(tmp);
+    if (counter) b->impl.memory->release(counter);
+    if (st != BITNET_OK) {
+        b->impl.memory->release(packed);
+        return st;
+    }
+    // the last partial byte of a ternary upload holds padding codes of 0 (= weight -1 on
+    // positions past the end); they are never read as weights because every kernel stops
+    // at n_values
+    bitnet_weights *w = new (std::nothrow) bitnet_weights();
+    if (!w) {
+        b->impl.memory->release(packed);
+        return fail(BITNET_ERR_MEMORY_ALLOCATION, "out of host memory");
+    }
+    w->impl.packed_dev = static_cast<uint8_t *>(packed);
+    w->impl.N = N;
+    w->impl.K = K;
+    w->impl.w_scale = w_scale;
+    w->impl.invalid_codes = found;
+    *out = w;
+    return BITNET_OK;
+}
+
+extern "C" bitnet_status_t bitnet_backend_upload_packed(bitnet_backend *b, const uint8_t *packed_host, size_t N,
+                                                        size_t K, float w_scale, bitnet_weights **out)
+{
+    return upload_common(b, packed_host, false, N, K, w_scale, out);
+}
+
+extern "C" bitnet_status_t bitnet_backend_upload_ternary(bitnet_backend *b, const int8_t *ternary_host, size_t N,
+                                                         size_t K, float w_scale, bitnet_weights **out)
+{
+    return upload_common(b, ternary_host, true, N, K, w_scale, out);
+}
+
+extern "C" bitnet_status_t bitnet_backend_free_weights(bitnet_backend *b, bitnet_weights *w)
+{
+    if (!w) return BITNET_OK;
+    if (!b) return fail(BITNET_ERR_NULL_POINTER, "bitnet_backend_free_weights: null backend");
+    const bitnet_status_t st = b->impl.memory->release(w->impl.packed_dev);
+    delete w;
+    return st;
+}
+
+extern "C" bitnet_status_t bitnet_weights_info(const bitnet_weights *w, size_t *N, size_t *K, float *w_scale,
+                                               const uint8_t **packed_dev)
+{
+    if (!w) return fail(BITNET_ERR_NULL_POINTER, "bitnet_weights_info: null weights");
+    if (N) *N = w->impl.N;
+    if (K) *K = w->impl.K;
+    if (w_scale) *w_scale = w->impl.w_scale;
+    if (packed_dev) *packed_dev = w->impl.packed_dev;
+    return BITNET_OK;
+}
+
+extern "C" bitnet_status_t bitnet_backend_bitlinear_forward(bitnet_backend *b, const bitnet_weights *w, const float *x_dev,
+                                                            float *y_dev, size_t M, const bitnet_forward_opts *opts,
+                                                            size_t stream_idx)
+{
+    if (!b || !w) return fail(BITNET_ERR_NULL_POINTER, "bitnet_backend_bitlinear_forward: null argument");
+    CudaStream *s = nullptr;
+    BITNET_TRY(b->impl.stream_at(stream_idx, &s));
+    std::lock_guard<std::mutex> lock(s->mu);
+    BITNET_CUDA(cudaSetDevice(b->impl.device));
+    size_t ws = 0;
+    BITNET_TRY(bitnet_bitlinear_workspace_size(M, w->impl.K, w->impl.N, opts ? opts->path : BITNET_PATH_AUTO, &ws));
+    BITNET_TRY(b->impl.ensure_staging(*s, 0, ws));
+    const uint64_t t0 = now_ns();
+    BITNET_TRY(bitnet_bitlinear_forward(w->impl.packed_dev, w->impl.w_scale, x_dev, y_dev, M, w->impl.K, w->impl.N, opts,
+                                        ws ? s->dev : nullptr, ws, s->stream));
+    b->impl.record(now_ns() - t0, w->impl.N * w->impl.K / 4 + 4 * M * w->impl.K + 4 * M * w->impl.N);
+    s->operation_count.fetch_add(1, std::memory_order_relaxed);
+    return BITNET_OK;
+}
+
+extern "C" bitnet_status_t bitnet_backend_bitlinear_forward_host(bitnet_backend *b, const bitnet_weights *w,
+                                                                 const float *x_host, float *y_host, size_t M,
+                                                                 const bitnet_forward_opts *opts, size_t stream_idx)
+{
+    if (!b || !w) return fail(BITNET_ERR_NULL_POINTER, "bitnet_backend_bitlinear_forward_host: null argument");
+    if (M == 0) return BITNET_OK;
+    if (!x_host || !y_host) return fail(BITNET_ERR_NULL_POINTER, "bitnet_backend_bitlinear_forward_host: null buffer");
+    if (opts && (opts->q_out_dev || opts->a_scale_out_dev || opts->acc_out_dev || opts->ldy))
+        return fail(BITNET_ERR_INVALID_CONFIG, "host-buffer forward takes no device outputs");
+    CudaStream *s = nullptr;
+    BITNET_TRY(b->impl.stream_at(stream_idx, &s));
+    std::lock_guard<std::mutex> lock(s->mu);
+    BITNET_CUDA(cudaSetDevice(b->impl.device));
+    const size_t K = w->impl.K, N = w->impl.N;
+    const size_t xb = align_up(M * K * sizeof(float), 256), yb = align_up(M * N * sizeof(float), 256);
+    size_t ws = 0;
+    BITNET_TRY(bitnet_bitlinear_workspace_size(M, K, N, opts ? opts->path : BITNET_PATH_AUTO, &ws));
+    BITNET_TRY(b->impl.ensure_staging(*s, xb + yb, xb + yb + ws));
+    char *pin = static_cast<char *>(s->pinned), *dev = static_cast<char *>(s->dev);
+    const uint64_t t0 = now_ns();
+    memcpy(pin, x_host, M * K * sizeof(float));
+    BITNET_CUDA(cudaMemcpyAsync(dev, pin, M * K * sizeof(float), cudaMemcpyHostToDevice, s->stream));
+    BITNET_TRY(bitnet_bitlinear_forward(w->impl.packed_dev, w->impl.w_scale, reinterpret_cast<float *>(dev),
+                                        reinterpret_cast<float *>(dev + xb), M, K, N, opts, ws ? dev + xb + yb : nullptr, ws,
+                                        s->stream));
+    BITNET_CUDA(cudaMemcpyAsync(pin + xb, dev + xb, M * N * sizeof(float), cudaMemcpyDeviceToHost, s->stream));
+    const cudaError_t err = cudaStreamSynchronize(s->stream);
+    if (err != cudaSuccess) return fail(BITNET_ERR_STREAM_SYNC, "stream synchronize: %s", cudaGetErrorString(err));
+    memcpy(y_host, pin + xb, M * N * sizeof(float));
+    b->impl.record(now_ns() - t0, N * K / 4 + 4 * M * K + 4 * M * N);
+    s->operation_count.fetch_add(1, std::memory_order_relaxed);
+    return BITNET_OK;
+}
+
+extern "C" bitnet_status_t bitnet_backend_ffn_forward_host(bitnet_backend *b, const bitnet_weights *gate,
+                                                           const bitnet_weights *up, const bitnet_weights *down,
+                                                           const float *x_host, float *y_host, size_t M,
+                                                           const bitnet_forward_opts *opts, size_t stream_idx)
+{
+    if (!b || !gate || !up || !down) return fail(BITNET_ERR_NULL_POINTER, "bitnet_backend_ffn_forward_host: null argument");
+    if (M == 0) return BITNET_OK;
+    if (!x_host || !y_host) return fail(BITNET_ERR_NULL_POINTER, "bitnet_backend_ffn_forward_host: null buffer");
+    const size_t hidden = gate->impl.K, ffn = gate->impl.N;
+    if (up->impl.K != hidden || up->impl.N != ffn || down->impl.K != ffn || down->impl.N != hidden)
+        return fail(BITNET_ERR_INCOMPATIBLE_SHAPES, "FFN shapes disagree: gate %zux%zu, up %zux%zu, down %zux%zu", ffn, hidden,
+                    up->impl.N, up->impl.K, down->impl.N, down->impl.K);
+    CudaStream *s = nullptr;
+    BITNET_TRY(b->impl.stream_at(stream_idx, &s));
+    std::lock_guard<std::mutex> lock(s->mu);
+    BITNET_CUDA(cudaSetDevice(b->impl.device));
+    const size_t xb = align_up(M * hidden * sizeof(float), 256), hb = align_up(M * ffn * sizeof(float), 256);
+    size_t ws = 0;
+    BITNET_TRY(bitnet_ffn_workspace_size(M, hidden, ffn, opts ? opts->path : BITNET_PATH_AUTO, &ws));
+    BITNET_TRY(b->impl.ensure_staging(*s, 2 * xb, 2 * xb + hb + ws));
+    char *pin = static_cast<char *>(s->pinned), *dev = static_cast<char *>(s->dev);
+    float *x_dev = reinterpret_cast<float *>(dev), *y_dev = reinterpret_cast<float *>(dev + xb);
+    float *h_dev = reinterpret_cast<float *>(dev + 2 * xb);
+    const uint64_t t0 = now_ns();
+    memcpy(pin, x_host, M * hidden * sizeof(float));
+    BITNET_CUDA(cudaMemcpyAsync(x_dev, pin, M * hidden * sizeof(float), cudaMemcpyHostToDevice, s->stream));
+    BITNET_TRY(bitnet_ffn_forward(gate->impl.packed_dev, gate->impl.w_scale, up->impl.packed_dev, up->impl.w_scale,
+                                  down->impl.packed_dev, down->impl.w_scale, x_dev, h_dev, y_dev, M, hidden, ffn, opts,
+                                  ws ? dev + 2 * xb + hb : nullptr, ws, s->stream));
+    BITNET_CUDA(cudaMemcpyAsync(pin + xb, y_dev, M * hidden * sizeof(float), cudaMemcpyDeviceToHost, s->stream));
+    const cudaError_t err = cudaStreamSynchronize(s->stream);
+    if (err != cudaSuccess) return fail(BITNET_ERR_STREAM_SYNC, "stream synchronize: %s", cudaGetErrorString(err));
+    memcpy(y_host, pin + xb, M * hidden * sizeof(float));
+    b->impl.record(now_ns() - t0, 3 * (ffn * hidden / 4) + 4 * M * (2 * hidden + 2 * ffn) + 4 * M * (2 * ffn + hidden));
+    s->operation_count.fetch_add(1, std::memory_order_relaxed);
+    return BITNET_OK;
+}

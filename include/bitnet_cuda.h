@@ -1,0 +1,261 @@
+/*
+ * bitnet_cuda.h -- C ABI of libbitnet_cuda_kernels (B200 / sm_100a).
+ *
+ * The BitLinear forward hot path of BitNet-Rust behind plain C entry points:
+ * per-token absmax int8 activation quantisation, 2-bit ternary weights in the
+ * reference's packed layout, int8 x ternary contraction with int32
+ * accumulation, dequantisation by weight scale x activation scale.
+ *
+ * Conventions
+ *   - Every function returns a bitnet_status_t (0 = ok) and never aborts; the text of
+ *     the last failure on the calling thread is available from bitnet_last_error_string().
+ *   - All pointers named *_dev are device pointers; kernels are enqueued on the given
+ *     stream and the call returns without synchronising unless stated otherwise.
+ *   - M = tokens (rows of x), K = in_features, N = out_features.
+ *   - Packed weights: the ternary matrix W[N,K] is flattened row-major, code = w + 1,
+ *     four codes per byte, element j of a byte in bits [2j+1:2j]
+ *     (bitnet-quant/src/quantization/packing.rs:352-394, utils.rs:434-475).  The buffer
+ *     holds ceil(N*K/4) bytes.  Code 3 is never produced by the reference's packers and
+ *     its decoders disagree on it; kernels here require it to be absent --
+ *     bitnet_sanitize_packed rewrites it to code 1 (weight 0, the majority rule of
+ *     gguf.rs:1139 and weight_conversion.rs:179-182) and reports how many it found.
+ *   - Citations are paths inside the reference project.
+ */
+#ifndef BITNET_CUDA_H
+#define BITNET_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* A cudaStream_t, spelled without the CUDA headers so that any FFI can bind it. */
+typedef void *bitnet_stream_t;
+
+/* Status codes; one per variant of the reference's CudaError
+ * (bitnet-cuda/src/error.rs:7-56) plus the two this library adds. */
+typedef int32_t bitnet_status_t;
+enum {
+    BITNET_OK = 0,
+    BITNET_ERR_CUDA_NOT_ENABLED = 1,     /* CudaError::CudaNotEnabled: no usable device */
+    BITNET_ERR_CUDA_DRIVER = 2,          /* CudaError::CudaDriver */
+    BITNET_ERR_DEVICE = 3,               /* CudaError::DeviceError */
+    BITNET_ERR_MEMORY_ALLOCATION = 4,    /* CudaError::MemoryAllocation */
+    BITNET_ERR_KERNEL_EXECUTION = 5,     /* CudaError::KernelExecution */
+    BITNET_ERR_INVALID_CONFIG = 6,       /* CudaError::InvalidConfig */
+    BITNET_ERR_UNSUPPORTED_OPERATION = 7,/* CudaError::UnsupportedOperation */
+    BITNET_ERR_STREAM_SYNC = 8,          /* CudaError::StreamSync */
+    BITNET_ERR_UNSUPPORTED_DTYPE = 9,    /* CudaError::UnsupportedDataType */
+    BITNET_ERR_INCOMPATIBLE_SHAPES = 10, /* CudaError::IncompatibleShapes */
+    BITNET_ERR_PERFORMANCE = 11,         /* CudaError::PerformanceDegradation */
+    BITNET_ERR_NULL_POINTER = 12,        /* added: a required pointer was NULL */
+    BITNET_ERR_WORKSPACE = 13            /* added: workspace missing, misaligned or too small */
+};
+
+/* CudaError::is_recoverable (bitnet-cuda/src/error.rs:88-103): 1 or 0. */
+int32_t bitnet_is_recoverable(bitnet_status_t status);
+const char *bitnet_status_string(bitnet_status_t status);
+const char *bitnet_last_error_string(void);
+
+/* Which kernel family runs a forward call. */
+enum {
+    BITNET_PATH_AUTO = 0,    /* decode kernel for M <= 16, tensor-core GEMM for larger M */
+    BITNET_PATH_DECODE = 1,  /* weight-streaming GEMV family, M <= 16, K % 64 == 0 */
+    BITNET_PATH_PREFILL = 2, /* TMA + tcgen05 int8 GEMM, K % 128 == 0 */
+    BITNET_PATH_GENERIC = 3  /* any M, K, N (rows may start mid-byte); slow, exact */
+};
+
+enum {
+    BITNET_FLAG_PDL = 1u /* launch with programmatic dependent launch: the kernel starts
+                            fetching weights before the preceding kernel on the stream has
+                            finished and only then waits for it */
+};
+
+/* Options of a forward call; zero-initialise for the defaults. */
+typedef struct bitnet_forward_opts {
+    int32_t path;           /* BITNET_PATH_* */
+    uint32_t flags;         /* BITNET_FLAG_* */
+    int8_t *q_out_dev;      /* optional [M,K]: the int8 activations */
+    float *a_scale_out_dev; /* optional [M]: absmax/127 per token (1 when the row is all zero) */
+    int32_t *acc_out_dev;   /* optional [M,N]: the int32 accumulators */
+    size_t ldy;             /* row stride of y (and acc_out) in elements; 0 means N */
+    int32_t cluster_k;      /* decode kernel: CTAs per cluster splitting K (0 = choose) */
+    int32_t reserved;
+} bitnet_forward_opts;
+
+/* Device facts (CudaBackend::validate_device_capabilities, bitnet-cuda/src/backend.rs:192-213). */
+typedef struct bitnet_device_info {
+    int32_t device_id;
+    int32_t cc_major, cc_minor;
+    int32_t sm_count;
+    int32_t l2_bytes;
+    int32_t max_smem_per_block;
+    size_t free_bytes, total_bytes;
+    char name[128];
+} bitnet_device_info;
+
+bitnet_status_t bitnet_device_count(int32_t *count);                  /* lib.rs:56-64 device_count() */
+bitnet_status_t bitnet_query_device(int32_t device_id, bitnet_device_info *out);
+
+/* ---- the hot path --------------------------------------------------------------- */
+
+/* Legacy single-token entry point: out[n] = sum_k (code(W[n,k]) - 1) * a[k], int32.
+ * Replaces launch_w2a8_gemv_optimized / w2a8_gemv_kernel
+ * (bitnet-cuda/src/kernels/w2a8_gemv.cu:100-106, :188-214); note the reference calls
+ * n_out "m" and k_in "k".  Unlike the reference it reports launch errors. */
+bitnet_status_t bitnet_w2a8_gemv(const uint8_t *weights_dev, const int8_t *activations_dev,
+                                 int32_t *output_dev, size_t n_out, size_t k_in,
+                                 bitnet_stream_t stream);
+
+/* Same symbol and signature as the reference's launcher (w2a8_gemv.cu:188-195), for
+ * callers that already link against it; errors are only recorded (see
+ * bitnet_last_error_string), as the void return leaves no other channel. */
+void launch_w2a8_gemv_optimized(const uint8_t *weights, const int8_t *activations,
+                                int32_t *output, size_t m, size_t k, bitnet_stream_t stream);
+
+/* Fused BitLinear forward: y[M,N] = dequant(contract(quant(x[M,K]), W)).
+ * Semantics: TernaryProcessor::quantize_activations + ternary_matmul_generic
+ * (bitnet-inference/src/engine/ternary_operations.rs:117-172, :283-338) with int32
+ * accumulation and y = acc * (w_scale * absmax/127), output [M,N] row-major; it is what
+ * BitLinearLayer::forward (transformer_layers.rs:119-202) and
+ * BitLinearForward::forward_with_quantized_weights (bitnet-quant/src/bitlinear/forward.rs:95)
+ * compute for a 2-D input.  The argument order follows the reference's only batched
+ * quantised-GEMM signature (bitnet-metal/src/mps/matrix_ops.rs:318-341).
+ * workspace_dev: bitnet_bitlinear_workspace_size() bytes, 256-byte aligned; may be NULL
+ * when that size is 0 (the decode path needs none). */
+bitnet_status_t bitnet_bitlinear_forward(const uint8_t *weights_dev, float w_scale,
+                                         const float *x_dev, float *y_dev,
+                                         size_t M, size_t K, size_t N,
+                                         const bitnet_forward_opts *opts,
+                                         void *workspace_dev, size_t workspace_bytes,
+                                         bitnet_stream_t stream);
+bitnet_status_t bitnet_bitlinear_workspace_size(size_t M, size_t K, size_t N, int32_t path,
+                                                size_t *bytes);
+
+/* Per-token absmax int8 quantisation on its own
+ * (TernaryProcessor::quantize_activations, ternary_operations.rs:117-172):
+ * q = clamp(round_half_away(x * (127/absmax)), -128, 127), a_scale = absmax/127. */
+bitnet_status_t bitnet_quantize_activations(const float *x_dev, size_t M, size_t K,
+                                            int8_t *q_dev, float *a_scale_dev,
+                                            bitnet_stream_t stream);
+
+/* FFN block: y = down( up(x) * relu(gate(x))^2 ), each projection a BitLinear that
+ * re-quantises its input per token (FeedForwardNetwork::forward,
+ * bitnet-inference/src/engine/transformer_layers.rs:603-623).
+ * h_dev: caller-provided [M,ffn] fp32 buffer that receives the gated activations. */
+bitnet_status_t bitnet_ffn_forward(const uint8_t *w_gate_dev, float s_gate,
+                                   const uint8_t *w_up_dev, float s_up,
+                                   const uint8_t *w_down_dev, float s_down,
+                                   const float *x_dev, float *h_dev, float *y_dev,
+                                   size_t M, size_t hidden, size_t ffn,
+                                   const bitnet_forward_opts *opts,
+                                   void *workspace_dev, size_t workspace_bytes,
+                                   bitnet_stream_t stream);
+bitnet_status_t bitnet_ffn_workspace_size(size_t M, size_t hidden, size_t ffn, int32_t path,
+                                          size_t *bytes);
+
+/* ---- packed-weight helpers (device) -------------------------------------------------- */
+
+/* BitPacked2BitPacker::pack / unpack (packing.rs:352-394) on device buffers.
+ * n_values ternary int8 values <-> ceil(n_values/4) bytes. */
+bitnet_status_t bitnet_pack_ternary(const int8_t *w_dev, size_t n_values, uint8_t *packed_dev,
+                                    bitnet_stream_t stream);
+bitnet_status_t bitnet_unpack_ternary(const uint8_t *packed_dev, size_t n_values, int8_t *w_dev,
+                                      bitnet_stream_t stream);
+/* Rewrites code 3 to code 1 in place and adds the number found to *count_dev (a device
+ * uint64 the caller zeroed; may be NULL). */
+bitnet_status_t bitnet_sanitize_packed(uint8_t *packed_dev, size_t n_bytes,
+                                       unsigned long long *count_dev, bitnet_stream_t stream);
+
+/* ---- host-side backend (handle based) ------------------------------------------------- */
+/* Mirrors CudaBackend / CudaBackendConfig / W2A8GemvConfig / CudaMemoryManager /
+ * CudaStream / PerformanceStats of the reference's bitnet-cuda crate
+ * (backend.rs:14-37, :40-213, :262-290; kernels/w2a8_gemv.rs:15-60; memory.rs:47-186;
+ * stream.rs:31-207) so that a Rust shim can stay a list of declarations. */
+
+typedef struct bitnet_backend bitnet_backend;   /* CudaBackend */
+typedef struct bitnet_weights bitnet_weights;   /* a packed, uploaded weight tensor */
+
+enum { BITNET_GRID_FIXED = 0, BITNET_GRID_DYNAMIC = 1, BITNET_GRID_OCCUPANCY = 2 };    /* GridStrategy */
+enum { BITNET_COALESCE_NONE = 0, BITNET_COALESCE_BASIC = 1, BITNET_COALESCE_AGGRESSIVE = 2 }; /* CoalescingLevel */
+
+typedef struct bitnet_w2a8_config {     /* W2A8GemvConfig, w2a8_gemv.rs:15-38 */
+    uint32_t block_size;                /* must be a non-zero multiple of 32 */
+    int32_t grid_strategy;
+    uint32_t grid_fixed;                /* GridStrategy::Fixed(n) */
+    int32_t enable_weight_permutation;
+    int32_t enable_dp4a;
+    int32_t coalescing_level;
+} bitnet_w2a8_config;
+
+typedef struct bitnet_backend_config {  /* CudaBackendConfig, backend.rs:14-37 */
+    size_t device_id;
+    size_t memory_pool_size;
+    size_t num_streams;
+    int32_t enable_profiling;
+    bitnet_w2a8_config w2a8_config;
+} bitnet_backend_config;
+
+typedef struct bitnet_performance_stats { /* PerformanceStats, backend.rs:262-272 */
+    uint64_t total_w2a8_operations;
+    float average_execution_time_us;
+    float memory_utilization_percent;
+    float peak_bandwidth_gbps;
+} bitnet_performance_stats;
+
+void bitnet_backend_config_default(bitnet_backend_config *cfg);       /* Default impls */
+bitnet_status_t bitnet_backend_create(const bitnet_backend_config *cfg, bitnet_backend **out); /* CudaBackend::new */
+void bitnet_backend_destroy(bitnet_backend *b);
+bitnet_status_t bitnet_backend_stream(bitnet_backend *b, size_t index, bitnet_stream_t *out);  /* CudaBackend::stream */
+bitnet_status_t bitnet_backend_synchronize(bitnet_backend *b);                                  /* CudaBackend::synchronize */
+bitnet_status_t bitnet_backend_get_performance_stats(bitnet_backend *b, bitnet_performance_stats *out);
+
+/* CudaMemoryManager::{allocate, copy_to_device, copy_to_host} (memory.rs:79,:130,:143);
+ * allocations are zero-filled and charged against memory_pool_size. */
+bitnet_status_t bitnet_backend_allocate(bitnet_backend *b, size_t bytes, void **dev_ptr);
+bitnet_status_t bitnet_backend_free(bitnet_backend *b, void *dev_ptr);
+bitnet_status_t bitnet_backend_copy_to_device(bitnet_backend *b, void *dst_dev, const void *src_host, size_t bytes);
+bitnet_status_t bitnet_backend_copy_to_host(bitnet_backend *b, void *dst_host, const void *src_dev, size_t bytes);
+bitnet_status_t bitnet_backend_memory_usage(bitnet_backend *b, size_t *allocated, size_t *pool_size);
+
+/* CudaBackend::w2a8_gemv (backend.rs:129-157) with its length checks (:217-257): lengths
+ * are element counts of the three device buffers; mismatches give
+ * BITNET_ERR_INCOMPATIBLE_SHAPES, a bad stream index BITNET_ERR_INVALID_CONFIG. */
+bitnet_status_t bitnet_backend_w2a8_gemv(bitnet_backend *b,
+                                         const uint8_t *weights_dev, size_t weights_len,
+                                         const int8_t *activations_dev, size_t activations_len,
+                                         int32_t *output_dev, size_t output_len,
+                                         size_t m, size_t k, size_t stream_idx);
+
+/* Weight life cycle of BitLinear (bitnet-quant/src/bitlinear/layer.rs:236-326): pack and
+ * upload once per weight version, launch-only afterwards, drop on update_weights. */
+bitnet_status_t bitnet_backend_upload_packed(bitnet_backend *b, const uint8_t *packed_host,
+                                             size_t N, size_t K, float w_scale, bitnet_weights **out);
+bitnet_status_t bitnet_backend_upload_ternary(bitnet_backend *b, const int8_t *ternary_host,
+                                              size_t N, size_t K, float w_scale, bitnet_weights **out);
+bitnet_status_t bitnet_backend_free_weights(bitnet_backend *b, bitnet_weights *w);
+bitnet_status_t bitnet_weights_info(const bitnet_weights *w, size_t *N, size_t *K, float *w_scale,
+                                    const uint8_t **packed_dev);
+
+/* BitLinear forward on device buffers through the backend (workspace from the pool). */
+bitnet_status_t bitnet_backend_bitlinear_forward(bitnet_backend *b, const bitnet_weights *w,
+                                                 const float *x_dev, float *y_dev, size_t M,
+                                                 const bitnet_forward_opts *opts, size_t stream_idx);
+/* The call a host-side user makes (BitLinearLayer::forward on host tensors,
+ * transformer_layers.rs:119-202): x and y are HOST buffers [M,K] / [M,N]; the copies in
+ * and out run on the chosen stream and the call returns after y is complete. */
+bitnet_status_t bitnet_backend_bitlinear_forward_host(bitnet_backend *b, const bitnet_weights *w,
+                                                      const float *x_host, float *y_host, size_t M,
+                                                      const bitnet_forward_opts *opts, size_t stream_idx);
+/* FFN block on host buffers (FeedForwardNetwork::forward, transformer_layers.rs:603-623). */
+bitnet_status_t bitnet_backend_ffn_forward_host(bitnet_backend *b, const bitnet_weights *gate,
+                                                const bitnet_weights *up, const bitnet_weights *down,
+                                                const float *x_host, float *y_host, size_t M,
+                                                const bitnet_forward_opts *opts, size_t stream_idx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BITNET_CUDA_H */

@@ -1,0 +1,345 @@
+"""Parity of the CUDA path with the CPU oracle, called through the C ABI.
+
+Bar: int8 activations, per-token scales and int32 accumulators bit-exact; fp32 outputs
+within 1e-5 relative (they are in fact bit-identical, which is also asserted where the
+path promises it)."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from bitnet_mlx_rs_b200 import cuda, ops
+from bitnet_mlx_rs_b200.bitlinear import BitLinear, BitLinearConfig, BitLinearLayer, FeedForwardNetwork, ShapeMismatch
+
+pytestmark = pytest.mark.gpu
+GOLDEN = Path(__file__).resolve().parent / "golden"
+RTOL = 1e-5
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def case(seed, M, K, N):
+    wp = oracle.gen_ternary_packed(seed, 1, N * K)
+    x = oracle.gen_activations(seed, 2, (M, K))
+    ws = oracle.gen_weight_scale(seed, 1, K)
+    return wp, ws, x
+
+
+def assert_parity(dbg, y, ref, M, N):
+    assert np.array_equal(dbg["q"].cpu().numpy(), ref["q"]), "int8 activations differ"
+    assert np.array_equal(dbg["a_scale"].cpu().numpy(), ref["a_scale"]), "activation scales differ"
+    assert np.array_equal(dbg["acc"].cpu().numpy(), ref["acc"]), "int32 accumulators differ"
+    yn = y.cpu().numpy()
+    assert yn.shape == (M, N)
+    np.testing.assert_allclose(yn, ref["y"], rtol=RTOL, atol=0)
+    assert np.array_equal(yn, ref["y"]), "fp32 outputs are expected to be bit-identical"
+
+
+# ---- activation quantiser -------------------------------------------------------------------
+
+@pytest.mark.parametrize("M,K", [(1, 2560), (8, 6912), (3, 37), (5, 1), (2, 8192), (33, 130)])
+def test_quantize_activations_bit_exact(M, K):
+    x = oracle.gen_activations(1, 5, (M, K))
+    q, s = ops.quantize_activations(dev(x))
+    rq, rs, _ = oracle.quantize_activations(x)
+    assert np.array_equal(q.cpu().numpy(), rq)
+    assert np.array_equal(s.cpu().numpy(), rs)
+
+
+def test_quantiser_rounding_ties_and_edges():
+    # scale == 1 when absmax == 127: the quantiser then rounds the inputs themselves
+    vals = [127.0]
+    for n in range(-127, 127):
+        h = np.float32(n) + np.float32(0.5)
+        vals += [h, np.nextafter(h, np.float32(200)), np.nextafter(h, np.float32(-200))]
+    vals += [0.49999997, -0.49999997, 0.0, -0.0, 1e-30, -1e-30]
+    x = np.zeros((4, 512), dtype=np.float32)
+    x[0, : len(vals)] = vals
+    x[1, :] = 0.0                                        # all-zero row: scale 1, a_scale 1
+    x[2, :8] = [3.0e38, -3.0e38, 1.0, -1.0, 0.0, 1e20, -1e20, 5.0]
+    x[3, 7] = 1e-38                                      # subnormal-range absmax
+    q, s = ops.quantize_activations(dev(x))
+    rq, rs, _ = oracle.quantize_activations(x)
+    assert np.array_equal(q.cpu().numpy(), rq)
+    assert np.array_equal(s.cpu().numpy(), rs)
+    # and the same rows through the fused decode kernel
+    wp, ws, _ = case(2, 4, 512, 32)
+    y, dbg = ops.bitlinear_forward(dev(wp), ws, dev(x), 32, debug=True, path="decode")
+    assert_parity(dbg, y, oracle.bitlinear_forward(wp, ws, x, 32), 4, 32)
+
+
+# ---- decode kernel ----------------------------------------------------------------------------
+
+DECODE_SHAPES = [
+    (1, 2560, 2560),      # config 1
+    (1, 2560, 6912), (4, 2560, 6912), (8, 2560, 6912),      # config 2 gate/up
+    (1, 6912, 2560), (4, 6912, 2560), (8, 6912, 2560),      # config 2 down
+    (1, 64, 16), (2, 64, 1), (7, 128, 17), (8, 192, 250), (3, 320, 129),   # tails in N and few chunks
+    (9, 256, 48), (16, 1024, 144), (13, 2560, 640),         # two token tiles
+    (1, 8192, 3584), (16, 8192, 3584),                      # one 8-GPU slice of the oversized layer
+]
+
+
+@pytest.mark.parametrize("M,K,N", DECODE_SHAPES)
+def test_decode_matches_oracle(M, K, N):
+    wp, ws, x = case(100 + M, M, K, N)
+    ref = oracle.bitlinear_forward(wp, ws, x, N)
+    y, dbg = ops.bitlinear_forward(dev(wp), ws, dev(x), N, debug=True, path="decode")
+    assert_parity(dbg, y, ref, M, N)
+
+
+@pytest.mark.parametrize("S", [1, 2, 4, 8])
+@pytest.mark.parametrize("M,K,N", [(1, 2560, 300), (8, 6912, 520), (5, 512, 1040), (12, 1536, 272), (8, 64, 40)])
+def test_decode_every_cluster_split(S, M, K, N):
+    wp, ws, x = case(7 * S + M, M, K, N)
+    ref = oracle.bitlinear_forward(wp, ws, x, N)
+    y, dbg = ops.bitlinear_forward(dev(wp), ws, dev(x), N, debug=True, path="decode", cluster_k=S)
+    assert_parity(dbg, y, ref, M, N)
+
+
+def test_decode_with_programmatic_dependent_launch_chain():
+    # y1 = L1(x); y2 = L2(y1): the second launch may start before the first ends and must still see y1
+    M, K, N = 8, 2560, 2560
+    wp1, s1, x = case(31, M, K, N)
+    wp2, s2, _ = case(32, M, N, K)
+    d1, d2, dx = dev(wp1), dev(wp2), dev(x)
+    for _ in range(3):
+        y1 = ops.bitlinear_forward(d1, s1, dx, N, path="decode", pdl=True)
+        y2 = ops.bitlinear_forward(d2, s2, y1, K, path="decode", pdl=True)
+    r1 = oracle.bitlinear_forward(wp1, s1, x, N)["y"]
+    r2 = oracle.bitlinear_forward(wp2, s2, r1, K)["y"]
+    assert np.array_equal(y1.cpu().numpy(), r1)
+    assert np.array_equal(y2.cpu().numpy(), r2)
+
+
+@pytest.mark.parametrize("path", sorted(GOLDEN.glob("*.npz")), ids=lambda p: p.stem)
+def test_golden_fixtures(path):
+    z = np.load(path)
+    if "gate" in z:
+        y, h = ops.ffn_forward(dev(z["gate"]), float(z["s_gate"]), dev(z["up"]), float(z["s_up"]), dev(z["down"]),
+                               float(z["s_down"]), dev(z["x"]), int(z["ffn"]))
+        assert np.array_equal(h.cpu().numpy(), z["h"])
+        np.testing.assert_allclose(y.cpu().numpy(), z["y"], rtol=RTOL, atol=0)
+        return
+    M, N = int(z["M"]), int(z["N"])
+    y, dbg = ops.bitlinear_forward(dev(z["wp"]), float(z["w_scale"]), dev(z["x"]), N, debug=True)
+    assert_parity(dbg, y, {k: z[k] for k in ("q", "a_scale", "acc", "y")}, M, N)
+
+
+# ---- generic path: any shape, rows that start mid-byte ---------------------------------------------
+
+@pytest.mark.parametrize("M,K,N", [(3, 37, 29), (1, 1, 1), (2, 5, 3), (20, 130, 33), (4, 2562, 10), (40, 64, 16)])
+def test_generic_path_matches_oracle(M, K, N):
+    wp, ws, x = case(200 + K, M, K, N)
+    ref = oracle.bitlinear_forward(wp, ws, x, N)
+    y, dbg = ops.bitlinear_forward(dev(wp), ws, dev(x), N, debug=True, path="generic")
+    assert_parity(dbg, y, ref, M, N)
+    y2 = ops.bitlinear_forward(dev(wp), ws, dev(x), N)          # auto dispatch lands on a correct kernel too
+    assert np.array_equal(y2.cpu().numpy(), ref["y"])
+
+
+def test_empty_batch_is_a_no_op():
+    wp, ws, _ = case(1, 1, 64, 16)
+    y = ops.bitlinear_forward(dev(wp), ws, torch.empty((0, 64), device="cuda"), 16)
+    assert tuple(y.shape) == (0, 16)
+
+
+# ---- legacy single-token GEMV -------------------------------------------------------------------------
+
+@pytest.mark.parametrize("n_out,k", [(128, 512), (512, 2048), (2048, 8192), (2560, 2560), (3, 4), (17, 36), (100, 250)])
+def test_w2a8_gemv_matches_oracle(n_out, k):
+    # sizes of bitnet-cuda/examples/w2a8_gemv_demo.rs:45-51 plus ragged ones
+    wp = oracle.gen_ternary_packed(5, n_out, n_out * k)
+    a = np.random.default_rng(k).integers(-127, 128, size=k, dtype=np.int8)
+    out = ops.w2a8_gemv(dev(wp), dev(a), n_out)
+    assert np.array_equal(out.cpu().numpy(), oracle.w2a8_gemv(wp, a, n_out))
+
+
+def test_w2a8_gemv_reference_pins():
+    # bitnet-quant/src/simd/matrix.rs:531-558 through the packed integer path
+    a = np.array([[1, -1, 0, 1], [0, 1, -1, 0], [-1, 0, 1, 1]], dtype=np.int8)
+    packed, _ = oracle.pack_ternary(a)
+    out = ops.w2a8_gemv(dev(packed), dev(np.array([2, 3, 1, -1], dtype=np.int8)), 3)
+    assert out.cpu().tolist() == [-2, 2, -2]
+    # bitnet-cuda/examples/w2a8_gemv_demo.rs:59-61: all codes 1 => all weights 0 => output 0
+    n_out, k = 512, 2048
+    wp = np.full(n_out * k // 4, 0x55, dtype=np.uint8)
+    out = ops.w2a8_gemv(dev(wp), dev(np.ones(k, dtype=np.int8)), n_out)
+    assert not out.any().item()
+
+
+# ---- layout helpers ---------------------------------------------------------------------------------------
+
+def test_pack_unpack_sanitize_on_device():
+    for n in (3, 8, 32, 128 * 64 + 1):
+        w = (np.arange(n) % 3 - 1).astype(np.int8)          # simd_unpacking_correctness_tests.rs:101-133
+        packed = ops.pack_ternary(dev(w))
+        assert np.array_equal(packed.cpu().numpy(), oracle.pack_ternary(w)[0])
+        assert np.array_equal(ops.unpack_ternary(packed, n).cpu().numpy(), w)
+    assert ops.unpack_ternary(dev(np.array([0b00100100], np.uint8)), 4).cpu().tolist() == [-1, 0, 1, -1]   # gguf.rs:2421
+    assert ops.unpack_ternary(dev(np.array([0b11100100], np.uint8)), 4).cpu().tolist() == [-1, 0, 1, 0]    # weight_conversion.rs:478
+    p = dev(np.array([0b11100100, 0xFF, 0x55, 0x00], np.uint8))
+    assert ops.sanitize_packed(p) == 5
+    assert p.cpu().tolist() == [0b01100100, 0x55, 0x55, 0x00]
+    assert ops.sanitize_packed(p) == 0
+
+
+# ---- FFN block ------------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("M", [1, 4, 8])
+def test_ffn_block_config2(M):
+    H, F = 2560, 6912
+    g, u, d = (oracle.gen_ternary_packed(9, i, F * H) for i in (1, 2, 3))
+    sg, su, sd = (oracle.gen_weight_scale(9, i, k) for i, k in ((1, H), (2, H), (3, F)))
+    x = oracle.gen_activations(9, 4, (M, H))
+    ry, rh = oracle.ffn_forward(g, sg, u, su, d, sd, x, F)
+    y, h = ops.ffn_forward(dev(g), sg, dev(u), su, dev(d), sd, dev(x), F)
+    assert np.array_equal(h.cpu().numpy(), rh)
+    np.testing.assert_allclose(y.cpu().numpy(), ry, rtol=RTOL, atol=0)
+    assert np.array_equal(y.cpu().numpy(), ry)
+    y2, _ = ops.ffn_forward(dev(g), sg, dev(u), su, dev(d), sd, dev(x), F, pdl=True)
+    assert np.array_equal(y2.cpu().numpy(), ry)
+
+
+def test_ffn_generic_path_small():
+    M, H, F = 20, 96, 160
+    g, u, d = (oracle.gen_ternary_packed(8, i, F * H) for i in (1, 2, 3))
+    sg, su, sd = 0.1, 0.2, 0.3
+    x = oracle.gen_activations(8, 4, (M, H))
+    ry, rh = oracle.ffn_forward(g, sg, u, su, d, sd, x, F)
+    y, h = ops.ffn_forward(dev(g), sg, dev(u), su, dev(d), sd, dev(x), F, path="generic")
+    assert np.array_equal(h.cpu().numpy(), rh) and np.array_equal(y.cpu().numpy(), ry)
+
+
+# ---- operator and backend mirrors --------------------------------------------------------------------------------
+
+def test_bitlinear_operator_mirror():
+    cfg = BitLinearConfig(in_features=512, out_features=1536)          # test_task_2_1_18...rs:69-110
+    layer = BitLinear(cfg, "test_layer", seed=3)
+    x = torch.randn(2, 16, 512, device="cuda")
+    y = layer.forward(x)
+    assert tuple(y.shape) == (2, 16, 1536) and torch.isfinite(y).all()
+    assert layer.cache_misses == 1
+    layer.forward(x)
+    assert layer.cache_hits == 1                                        # layer.rs:236-294
+    t, scale = oracle.absmean_quantize_weights(layer._weights.numpy())
+    ref = oracle.bitlinear_forward(oracle.pack_ternary(t)[0], scale, x.reshape(-1, 512).cpu().numpy(), 1536)["y"]
+    np.testing.assert_allclose(y.reshape(-1, 1536).cpu().numpy(), ref, rtol=RTOL, atol=1e-30)
+    layer.update_weights(torch.zeros(1536, 512))                        # layer.rs:299-326
+    assert not layer.forward(x).any().item() and layer.cache_misses == 2
+    with pytest.raises(ShapeMismatch):
+        layer.forward(torch.randn(2, 16, 500, device="cuda"))           # forward.rs:63-76
+
+
+def test_feed_forward_network_mirror():
+    H, F, M = 128, 320, 4
+    z = np.load(GOLDEN / "ffn_m4_h128_f320.npz")
+    ffn = FeedForwardNetwork(H, F, BitLinearLayer(H, F, packed=z["gate"], scale=float(z["s_gate"])),
+                             BitLinearLayer(H, F, packed=z["up"], scale=float(z["s_up"])),
+                             BitLinearLayer(F, H, packed=z["down"], scale=float(z["s_down"])))
+    y = ffn.forward(dev(z["x"]).reshape(2, 2, H))
+    assert np.array_equal(y.reshape(M, H).cpu().numpy(), z["y"])
+    assert not BitLinearLayer(64, 16).forward(torch.randn(3, 64, device="cuda")).any().item()   # zero-init weights
+
+
+def test_cuda_backend_mirror():
+    b = cuda.CudaBackend(cuda.CudaBackendConfig(memory_pool_size=256 << 20, num_streams=2))
+    m, k = 512, 2048
+    wp = oracle.gen_ternary_packed(4, 1, m * k)
+    a = np.random.default_rng(0).integers(-127, 128, size=k, dtype=np.int8)
+    dw, da, out = dev(wp), dev(a), torch.zeros(m, dtype=torch.int32, device="cuda")
+    b.w2a8_gemv(dw, da, out, m, k, 1)
+    b.synchronize()
+    assert np.array_equal(out.cpu().numpy(), oracle.w2a8_gemv(wp, a, m))
+    with pytest.raises(cuda.IncompatibleShapes):                        # backend.rs:226-254
+        b.w2a8_gemv(dw[:-1], da, out, m, k, 0)
+    with pytest.raises(cuda.IncompatibleShapes):
+        b.w2a8_gemv(dw, da[:-1], out, m, k, 0)
+    with pytest.raises(cuda.IncompatibleShapes):
+        b.w2a8_gemv(dw, da, out[:-1], m, k, 0)
+    with pytest.raises(cuda.InvalidConfig):                             # backend.rs:112-117
+        b.w2a8_gemv(dw, da, out, m, k, 2)
+    st = b.get_performance_stats()
+    assert st.total_w2a8_operations == 1 and st.average_execution_time_us > 0
+    mm = b.memory_manager()
+    p = mm.allocate(1 << 20)
+    assert mm.utilization_percent() == pytest.approx(100.0 / 256, rel=1e-3)
+    with pytest.raises(cuda.MemoryAllocation) as e:                     # memory.rs:83-89
+        mm.allocate(256 << 20)
+    assert e.value.is_recoverable()
+    mm.free(p)
+    host = np.arange(1000, dtype=np.float32)
+    p = mm.copy_to_device(host)
+    back = np.empty_like(host)
+    mm.copy_to_host(p, back)
+    assert np.array_equal(host, back)
+    mm.free(p)
+    with pytest.raises(cuda.InvalidConfig):
+        cuda.CudaBackend(cuda.CudaBackendConfig(w2a8_config=cuda.W2A8GemvConfig(block_size=100)))
+    with pytest.raises(cuda.DeviceError):
+        cuda.CudaBackend(cuda.CudaBackendConfig(device_id=99))
+    b.close()
+
+
+@pytest.mark.parametrize("M,K,N", [(1, 2560, 2560), (8, 2560, 6912), (3, 37, 29)])
+def test_backend_host_forward(M, K, N):
+    b = cuda.initialize()
+    wp, ws, x = case(300 + M, M, K, N)
+    w = b.upload_packed(wp, N, K, ws)
+    y = b.bitlinear_forward_host(w, x)
+    assert np.array_equal(y, oracle.bitlinear_forward(wp, ws, x, N)["y"])
+    t = oracle.unpack_ternary(wp, N * K).reshape(N, K)
+    w2 = b.upload_ternary(t, ws)
+    assert np.array_equal(b.bitlinear_forward_host(w2, x), y)
+    w.free(); w2.free(); b.close()
+
+
+def test_backend_host_ffn():
+    z = np.load(GOLDEN / "ffn_m4_h128_f320.npz")
+    H, F = int(z["hidden"]), int(z["ffn"])
+    b = cuda.initialize()
+    g, u, d = (b.upload_packed(z[k], n, kk, float(z[s])) for k, n, kk, s in
+               (("gate", F, H, "s_gate"), ("up", F, H, "s_up"), ("down", H, F, "s_down")))
+    assert np.array_equal(b.ffn_forward_host(g, u, d, z["x"]), z["y"])
+    b.close()
+
+
+# ---- full-size properties -------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("M", [1, 16])
+def test_oversized_layer_checksum_and_row_samples(M):
+    # K=8192, N=28672 is too large for the oracle in seconds: check a size-independent identity
+    # (sum_n acc[m,n] == q[m,:] . colsum(W)) with torch integer ops, and compare sampled row
+    # ranges against the oracle exactly.
+    K, N = 8192, 28672
+    wp = oracle.gen_ternary_packed(0, 50, N * K)
+    x = oracle.gen_activations(0, 51, (M, K))
+    ws = oracle.gen_weight_scale(0, 50, K)
+    dwp = dev(wp)
+    y, dbg = ops.bitlinear_forward(dwp, ws, dev(x), N, debug=True)
+    w = ops.unpack_ternary(dwp, N * K).reshape(N, K)
+    colsum = w.sum(dim=0, dtype=torch.int64)
+    assert torch.equal(dbg["acc"].sum(dim=1, dtype=torch.int64), dbg["q"].to(torch.int64) @ colsum)
+    yn = y.cpu().numpy()
+    for r0 in (0, 12345, N - 64):
+        sl = wp[r0 * K // 4:(r0 + 64) * K // 4]
+        ref = oracle.bitlinear_forward(sl, ws, x, 64)
+        assert np.array_equal(dbg["acc"][:, r0:r0 + 64].cpu().numpy(), ref["acc"])
+        np.testing.assert_allclose(yn[:, r0:r0 + 64], ref["y"], rtol=RTOL, atol=0)
+
+
+def test_linearity_of_the_integer_path():
+    # acc is linear in W's rows: a matrix whose second half repeats the first gives repeated outputs,
+    # and negating every weight (code 0 <-> 2) negates the accumulators
+    M, K, N = 8, 2560, 512
+    wp, ws, x = case(77, M, K, N)
+    w = oracle.unpack_ternary(wp, N * K).reshape(N, K)
+    both = np.concatenate([w, -w], axis=0)
+    p2, _ = oracle.pack_ternary(both)
+    _, dbg = ops.bitlinear_forward(dev(p2), ws, dev(x), 2 * N, debug=True)
+    acc = dbg["acc"].cpu().numpy()
+    assert np.array_equal(acc[:, :N], -acc[:, N:])
