@@ -1,0 +1,401 @@
+#!/usr/bin/env python
+"""Benchmark of the BitLinear decode hot path (one JSON line on stdout).
+
+Workload (N=1): the BitNet b1.58 2B-shaped FFN decode GEMVs -- gate/up 2560->6912,
+squared-ReLU gating, down 6912->2560 with per-token re-quantisation -- at M in {1,4,8}
+tokens over 30 distinct layers' weights (398 MB packed, larger than L2), seeded synthetic
+ternary weights (P(0)=0.4, P(+-1)=0.3) and N(0,1) activations with 0.1 % x20 outliers.
+One step = 3 token counts x 30 layers x one FFN block = 180 kernel launches.
+
+metric  = algorithmic HBM GB/s: bytes N*K/4 + 4*M*K + 4*M*N per BitLinear call, summed
+          over the step, divided by device time (CUDA events, max over ranks).
+e2e     = the same bytes over the time of the host-buffer call
+          (bitnet_backend_ffn_forward_host: pinned H2D of x, the launches, D2H of y).
+N > 1   = independent token batches row-sharded over ranks, weights replicated, no
+          collective: weak scaling.
+--impl reference times the CPU restatement of the reference path (the oracle port) on
+the host cores for the same metric.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+HIDDEN, FFN, LAYERS = 2560, 6912, 30
+TOKEN_COUNTS = (1, 4, 8)
+METRIC = "bitlinear_w2a8_gemv_hbm_gbs"
+
+
+def call_bytes(M, K, N):
+    return N * K // 4 + 4 * M * K + 4 * M * N
+
+
+def ffn_bytes(M):
+    return 2 * call_bytes(M, HIDDEN, FFN) + call_bytes(M, FFN, HIDDEN)
+
+
+def step_bytes(layers=LAYERS):
+    return sum(ffn_bytes(M) for M in TOKEN_COUNTS) * layers
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); smax.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------
+# reference arm / CPU baseline: the oracle port on the host cores
+# ------------------------------------------------------------------------------------------
+
+def cpu_ffn_sample(steps, warmup, threads=None):
+    """Times FFN blocks (M in {1,4,8}, one layer's weights) with the threaded oracle port."""
+    import numpy as np
+    import oracle
+    try:
+        oracle.build(native=True)
+        native = True
+    except Exception:
+        native = False
+    threads = threads or os.cpu_count() or 1
+    g, u, d = (oracle.gen_ternary_packed(0, 1000 + i, FFN * HIDDEN) for i in range(3))
+    sg, su, sd = (oracle.gen_weight_scale(0, 1000 + i, k) for i, k in ((0, HIDDEN), (1, HIDDEN), (2, FFN)))
+    xs = {M: oracle.gen_activations(0, 2000 + M, (M, HIDDEN)) for M in TOKEN_COUNTS}
+
+    def one_step():
+        for M in TOKEN_COUNTS:
+            up = oracle.bitlinear_forward_mt(u, su, xs[M], FFN, threads, native)
+            gate = oracle.bitlinear_forward_mt(g, sg, xs[M], FFN, threads, native)
+            h = up * np.square(np.maximum(gate, 0)).astype(np.float32)
+            oracle.bitlinear_forward_mt(d, sd, h, HIDDEN, threads, native)
+
+    for _ in range(warmup):
+        one_step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        one_step()
+    dt = (time.perf_counter() - t0) / steps
+    nbytes = step_bytes(layers=1)
+    return {"value": nbytes / dt / 1e9, "seconds_per_step": dt, "threads": threads, "native": native,
+            "sample": f"FFN block 2560->6912->2560 at M in {list(TOKEN_COUNTS)}, 1 layer of weights, {steps} timed passes"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    r = cpu_ffn_sample(max(args.steps, 1), args.warmup)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": r["value"], "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["seconds_per_step"] * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8xternary->int32, fp32 scales",
+        "data": "synthetic",
+        "config": {"workload": "BitNet b1.58 2B FFN decode GEMVs (gate/up 2560->6912, ReLU^2 gating, down 6912->2560), "
+                               "M in {1,4,8}", "sample": r["sample"]},
+        "cpu_baseline": {"value": r["value"], "unit": "GB/s", "cores": r["threads"], "kind": "port", "sample": r["sample"],
+                         "native_build": r["native"]},
+        "e2e": {"value": r["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------
+# CUDA arm
+# ------------------------------------------------------------------------------------------
+
+def gen_packed_on_device(torch, n_values, gen):
+    """Seeded ternary weights with P(-1)=0.3, P(0)=0.4, P(+1)=0.3, packed 4 per byte (code = w+1)."""
+    u = torch.rand(n_values, device="cuda", generator=gen)
+    codes = ((u >= 0.3).to(torch.uint8) + (u >= 0.7).to(torch.uint8)).view(-1, 4)
+    shifts = torch.tensor([0, 2, 4, 6], dtype=torch.uint8, device="cuda")
+    return (codes << shifts).sum(dim=1, dtype=torch.uint8).contiguous()
+
+
+def gen_activations_on_device(torch, shape, gen):
+    x = torch.randn(shape, device="cuda", generator=gen)
+    out = torch.rand(shape, device="cuda", generator=gen) < 0.001
+    return torch.where(out, x * 20.0, x).contiguous()
+
+
+def run_cuda(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from bitnet_mlx_rs_b200 import _lib, cuda, ops
+
+    _lib.load()   # raises if the CUDA library is missing: there is no fallback
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device (the CPU arm is --impl reference)")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    if args.gpus != world and rank == 0:
+        print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world}", file=sys.stderr)
+
+    gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
+    # layer 0 comes from the host generator so that the oracle can check it byte for byte
+    import oracle
+    host0 = [oracle.gen_ternary_packed(0, 1000 + i, FFN * HIDDEN) for i in range(3)]
+    scales0 = [oracle.gen_weight_scale(0, 1000 + i, k) for i, k in ((0, HIDDEN), (1, HIDDEN), (2, FFN))]
+    Wg, Wu, Wd, S = [], [], [], []
+    for l in range(LAYERS):
+        if l == 0:
+            g, u, d = (torch.from_numpy(h).cuda() for h in host0)
+            S.append(tuple(scales0))
+        else:
+            g, u, d = (gen_packed_on_device(torch, FFN * HIDDEN, gen) for _ in range(3))
+            S.append((0.5 / HIDDEN ** 0.5, 0.6 / HIDDEN ** 0.5, 0.7 / FFN ** 0.5))
+        Wg.append(g); Wu.append(u); Wd.append(d)
+    X = {M: [gen_activations_on_device(torch, (M, HIDDEN), gen) for _ in range(LAYERS)] for M in TOKEN_COUNTS}
+    x0 = oracle.gen_activations(0, 2008, (8, HIDDEN))
+    X[8][0] = torch.from_numpy(x0).cuda()
+    Y = {M: torch.empty((LAYERS, M, HIDDEN), device="cuda") for M in TOKEN_COUNTS}
+    Hb = {M: torch.empty((M, FFN), device="cuda") for M in TOKEN_COUNTS}
+
+    def step(pdl):
+        for M in TOKEN_COUNTS:
+            for l in range(LAYERS):
+                ops.ffn_forward(Wg[l], S[l][0], Wu[l], S[l][1], Wd[l], S[l][2], X[M][l], FFN, out=Y[M][l], h_out=Hb[M],
+                                pdl=pdl)
+
+    launches_per_step = 2 * LAYERS * len(TOKEN_COUNTS)
+
+    # parity spot check against the oracle on layer 0, M=8 (checker only, outside any timing)
+    step(False)
+    torch.cuda.synchronize()
+    if rank == 0:
+        ry, _ = oracle.ffn_forward(host0[0], scales0[0], host0[1], scales0[1], host0[2], scales0[2], x0, FFN)
+        np.testing.assert_allclose(Y[8][0].cpu().numpy(), ry, rtol=1e-5, atol=0)
+
+    # capture the step in a CUDA graph: try programmatic dependent launch first
+    mode, graph = "eager", None
+    side = torch.cuda.Stream()
+    for pdl in ((True, False) if not args.no_pdl else (False,)):
+        try:
+            with torch.cuda.stream(side):
+                step(pdl)
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    step(pdl)
+            g.replay()
+            torch.cuda.synchronize()
+            graph, mode = g, ("cuda_graph+pdl" if pdl else "cuda_graph")
+            break
+        except Exception as ex:   # capture not possible in this mode: try the next one
+            print(f"graph capture (pdl={pdl}) failed: {ex}", file=sys.stderr)
+            torch.cuda.synchronize()
+    if args.eager or graph is None:
+        graph, mode = None, "eager"
+
+    def run_step():
+        if graph is not None:
+            graph.replay()
+        else:
+            step(False)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        run_step()
+    sampler = ClockSampler(local)
+    barrier()
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        run_step()
+    e1.record()
+    barrier()
+    ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_total = float(ms.item())
+    clocks = sampler.stop() if rank == 0 else None
+
+    nbytes = step_bytes()
+    value = world * nbytes * args.steps / (ms_total * 1e-3) / 1e9
+    per_gpu = value / world
+    peak, peak_kind = measured_peaks()
+
+    # ---- end to end through the host-buffer C-ABI call --------------------------------------
+    backend = cuda.CudaBackend(cuda.CudaBackendConfig(device_id=local, memory_pool_size=2 << 30, num_streams=1))
+    e2e_layers = LAYERS
+    dw = [(backend.upload_packed(Wg[l].cpu().numpy(), FFN, HIDDEN, S[l][0]),
+           backend.upload_packed(Wu[l].cpu().numpy(), FFN, HIDDEN, S[l][1]),
+           backend.upload_packed(Wd[l].cpu().numpy(), HIDDEN, FFN, S[l][2])) for l in range(e2e_layers)]
+    xh = {M: [X[M][l].cpu().numpy() for l in range(e2e_layers)] for M in TOKEN_COUNTS}
+    yh = {M: np.empty((M, HIDDEN), dtype=np.float32) for M in TOKEN_COUNTS}
+
+    def e2e_step():
+        for M in TOKEN_COUNTS:
+            for l in range(e2e_layers):
+                backend.ffn_forward_host(dw[l][0], dw[l][1], dw[l][2], xh[M][l], out=yh[M])
+
+    for _ in range(3):
+        e2e_step()
+    e2e_steps = max(3, min(args.steps, 20))
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    torch.cuda.synchronize()
+    dt = torch.tensor([time.perf_counter() - t0], device="cuda")
+    if world > 1:
+        dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+    e2e_value = world * nbytes * e2e_steps / float(dt.item()) / 1e9
+    if rank == 0:
+        np.testing.assert_allclose(yh[8], Y[8][LAYERS - 1].cpu().numpy(), rtol=1e-5, atol=0)
+    io_bytes = sum(M * HIDDEN * 4 for M in TOKEN_COUNTS) * LAYERS
+    backend.close()
+
+    # ---- supporting single-kernel figures (same kernel, other configs of the spec) ---------------
+    extra = {}
+    if rank == 0 and not args.no_extra:
+        extra = single_kernel_figures(torch, ops, gen, peak)
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        r = cpu_ffn_sample(steps=3, warmup=1)
+        cpu = {"value": r["value"], "unit": "GB/s", "cores": r["threads"], "kind": "port", "sample": r["sample"],
+               "native_build": r["native"]}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "int8xternary->int32, fp32 scales", "data": "synthetic",
+            "config": {"workload": "BitNet b1.58 2B FFN decode GEMVs (gate/up 2560->6912, ReLU^2 gating, down 6912->2560), "
+                                   "M in {1,4,8}, 30 layers of distinct weights per step",
+                       "l2": "inputs larger than L2 (398 MB of packed weights per step)", "launch_mode": mode,
+                       "parallelism": f"row-sharded x{world}, weights replicated, no collective"},
+            "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
+                         "peak_kind": peak_kind, "traffic": None,
+                         "kernel": "decode_kernel (gate/up pair and down launches; algorithmic bytes per launch "
+                                   f"{step_bytes() / launches_per_step:.0f} on average)"},
+            "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": io_bytes, "d2h_bytes_per_step": io_bytes,
+                    "steps": e2e_steps, "api": "bitnet_backend_ffn_forward_host"},
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks,
+        }
+        if cpu:
+            line["cpu_baseline"] = cpu
+        if extra:
+            line["kernels"] = extra
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def single_kernel_figures(torch, ops, gen, peak):
+    """Device time of single BitLinear launches at the other decode shapes of the spec,
+    rotating over enough weight copies to exceed L2."""
+    out = {}
+    for name, (M, K, N) in {"cfg1_m1_2560x2560": (1, 2560, 2560), "cfg5_m1_8192x28672": (1, 8192, 28672),
+                            "cfg5_m16_8192x28672": (16, 8192, 28672)}.items():
+        copies = max(2, min(96, int(400e6 // (N * K // 4)) + 1))
+        W = [gen_packed_on_device(torch, N * K, gen) for _ in range(copies)]
+        x = gen_activations_on_device(torch, (M, K), gen)
+        y = torch.empty((M, N), device="cuda")
+        for w in W[:3]:
+            ops.bitlinear_forward(w, 0.01, x, N, out=y, pdl=True)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 3
+        e0.record()
+        for _ in range(reps):
+            for w in W:
+                ops.bitlinear_forward(w, 0.01, x, N, out=y, pdl=True)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (reps * copies)
+        gbs = call_bytes(M, K, N) / us / 1e3
+        out[name] = {"us": us, "gbs": gbs, "frac_of_peak": gbs / peak, "weight_copies": copies}
+        del W
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--eager", action="store_true", help="launch kernels one by one instead of replaying a CUDA graph")
+    ap.add_argument("--no-pdl", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    ap.add_argument("--no-extra", action="store_true", help="skip the single-kernel figures")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_cuda(args)
+
+
+if __name__ == "__main__":
+    main()

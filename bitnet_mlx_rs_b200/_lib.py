@@ -25,7 +25,7 @@ FLAG_PDL = 1
 
 class ForwardOpts(C.Structure):
     _fields_ = [("path", i32), ("flags", u32), ("q_out_dev", vp), ("a_scale_out_dev", vp),
-                ("acc_out_dev", vp), ("ldy", sz), ("cluster_k", i32), ("reserved", i32)]
+                ("acc_out_dev", vp), ("ldy", sz), ("stages", i32), ("reserved", i32)]
 
 
 class DeviceInfo(C.Structure):
@@ -56,6 +56,7 @@ SIGNATURES = {
     "bitnet_last_error_string": (C.c_char_p, []),
     "bitnet_device_count": (i32, [_P(i32)]),
     "bitnet_query_device": (i32, [i32, _P(DeviceInfo)]),
+    "bitnet_device_error_flags": (i32, [_P(u32)]),
     "bitnet_w2a8_gemv": (i32, [vp, vp, vp, sz, sz, vp]),
     "launch_w2a8_gemv_optimized": (None, [vp, vp, vp, sz, sz, vp]),
     "bitnet_bitlinear_forward": (i32, [vp, f32, vp, vp, sz, sz, sz, _P(ForwardOpts), vp, sz, vp]),

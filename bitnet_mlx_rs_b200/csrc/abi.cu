@@ -205,7 +205,7 @@ extern "C" bitnet_status_t bitnet_bitlinear_forward(const uint8_t *weights_dev, 
     ForwardArgs a = {};
     a.wp = weights_dev; a.w_scale = w_scale; a.x = x_dev; a.y = y_dev;
     a.acc_out = o.acc_out_dev; a.q_out = o.q_out_dev; a.a_scale_out = o.a_scale_out_dev;
-    a.M = M; a.K = K; a.N = N; a.ldy = ldy; a.flags = o.flags; a.cluster_k = o.cluster_k;
+    a.M = M; a.K = K; a.N = N; a.ldy = ldy; a.flags = o.flags; a.stages = o.stages;
     cudaStream_t s = as_stream(stream);
 
     switch (path) {
@@ -231,9 +231,10 @@ extern "C" bitnet_status_t bitnet_bitlinear_forward(const uint8_t *weights_dev, 
     return fail(BITNET_ERR_INVALID_CONFIG, "unknown path %d", o.path);
 }
 
-// FFN block.  Workspace: the larger of the two projections' needs, plus (non-decode
-// paths) room for the gate and up outputs.
+// FFN block.  Workspace: [absmax partials of h, 16 KB][gate and up outputs when the pair is
+// not fused][whatever the individual projections need].
 static size_t ffn_pair_bytes(size_t M, size_t ffn) { return align_up(M * ffn * sizeof(float), 256); }
+static const size_t kAmaxBytes = 256 * 16 * sizeof(unsigned);   // up to 256 CTAs x 16 tokens
 
 extern "C" bitnet_status_t bitnet_ffn_workspace_size(size_t M, size_t hidden, size_t ffn, int32_t path, size_t *bytes)
 {
@@ -244,8 +245,8 @@ extern "C" bitnet_status_t bitnet_ffn_workspace_size(size_t M, size_t hidden, si
     size_t w1 = 0, w2 = 0;
     BITNET_TRY(bitnet_bitlinear_workspace_size(M, hidden, ffn, p1, &w1));
     BITNET_TRY(bitnet_bitlinear_workspace_size(M, ffn, hidden, p2, &w2));
-    size_t need = w1 > w2 ? w1 : w2;
-    if (p1 != BITNET_PATH_DECODE) need += 2 * ffn_pair_bytes(M, ffn);
+    size_t need = kAmaxBytes + (w1 > w2 ? w1 : w2);
+    if (p1 != BITNET_PATH_DECODE || !decode_supports_dual(M, hidden, ffn)) need += 2 * ffn_pair_bytes(M, ffn);
     *bytes = need;
     return BITNET_OK;
 }
@@ -268,32 +269,40 @@ extern "C" bitnet_status_t bitnet_ffn_forward(const uint8_t *w_gate_dev, float s
     BITNET_TRY(bitnet_ffn_workspace_size(M, hidden, ffn, o.path, &need));
     BITNET_TRY(check_workspace(workspace_dev, workspace_bytes, need));
     cudaStream_t s = as_stream(stream);
-    const int p1 = resolve_path(o.path, M, hidden, ffn);
+    const int p1 = resolve_path(o.path, M, hidden, ffn), p2 = resolve_path(o.path, M, ffn, hidden);
+    char *ws = static_cast<char *>(workspace_dev);
+    unsigned *amax = reinterpret_cast<unsigned *>(ws);
+    size_t off = kAmaxBytes;
 
-    if (p1 == BITNET_PATH_DECODE) {
+    const bool fused_pair = p1 == BITNET_PATH_DECODE && decode_supports_dual(M, hidden, ffn);
+    // the gate/up launch leaves per-CTA absmax keys of h; the down launch folds them instead of re-reading h
+    const bool chain_amax = fused_pair && p2 == BITNET_PATH_DECODE && decode_grid(ffn) <= 256;
+    if (fused_pair) {
         // gate and up stream through one launch; its epilogue applies up * relu(gate)^2
         ForwardArgs a = {};
         a.wp = w_gate_dev; a.w_scale = s_gate; a.wp2 = w_up_dev; a.w_scale2 = s_up;
         a.x = x_dev; a.y = h_dev; a.M = M; a.K = hidden; a.N = ffn; a.ldy = ffn;
-        a.flags = o.flags; a.cluster_k = o.cluster_k;
+        a.flags = o.flags; a.stages = o.stages;
+        a.amax_out = chain_amax ? amax : nullptr;
         BITNET_TRY(launch_decode(a, s));
     } else {
-        char *ws = static_cast<char *>(workspace_dev);
-        float *gate = reinterpret_cast<float *>(ws);
-        float *up = reinterpret_cast<float *>(ws + ffn_pair_bytes(M, ffn));
-        void *inner = ws + 2 * ffn_pair_bytes(M, ffn);
-        const size_t inner_bytes = workspace_bytes - 2 * ffn_pair_bytes(M, ffn);
+        float *gate = reinterpret_cast<float *>(ws + off);
+        float *up = reinterpret_cast<float *>(ws + off + ffn_pair_bytes(M, ffn));
+        off += 2 * ffn_pair_bytes(M, ffn);
         bitnet_forward_opts po = {};
         po.path = p1; po.flags = o.flags;
-        BITNET_TRY(bitnet_bitlinear_forward(w_up_dev, s_up, x_dev, up, M, hidden, ffn, &po, inner, inner_bytes, stream));
-        BITNET_TRY(bitnet_bitlinear_forward(w_gate_dev, s_gate, x_dev, gate, M, hidden, ffn, &po, inner, inner_bytes, stream));
+        BITNET_TRY(bitnet_bitlinear_forward(w_up_dev, s_up, x_dev, up, M, hidden, ffn, &po, ws + off, workspace_bytes - off, stream));
+        BITNET_TRY(bitnet_bitlinear_forward(w_gate_dev, s_gate, x_dev, gate, M, hidden, ffn, &po, ws + off, workspace_bytes - off, stream));
         BITNET_TRY(launch_gate_relu2(up, gate, h_dev, M * ffn, s));
     }
+    if (chain_amax) {
+        ForwardArgs a = {};
+        a.wp = w_down_dev; a.w_scale = s_down; a.x = h_dev; a.y = y_dev;
+        a.M = M; a.K = ffn; a.N = hidden; a.ldy = hidden; a.flags = o.flags; a.stages = o.stages;
+        a.amax_in = amax; a.n_amax_in = decode_grid(ffn);
+        return launch_decode(a, s);
+    }
     bitnet_forward_opts po = {};
-    po.path = resolve_path(o.path, M, ffn, hidden);
-    po.flags = o.flags; po.cluster_k = o.cluster_k;
-    char *ws = static_cast<char *>(workspace_dev);
-    size_t off = (p1 != BITNET_PATH_DECODE) ? 2 * ffn_pair_bytes(M, ffn) : 0;
-    return bitnet_bitlinear_forward(w_down_dev, s_down, h_dev, y_dev, M, ffn, hidden, &po,
-                                    ws ? ws + off : nullptr, ws ? workspace_bytes - off : 0, stream);
+    po.path = p2; po.flags = o.flags; po.stages = o.stages;
+    return bitnet_bitlinear_forward(w_down_dev, s_down, h_dev, y_dev, M, ffn, hidden, &po, ws + off, workspace_bytes - off, stream);
 }

@@ -45,11 +45,17 @@ struct ForwardArgs {
     float w_scale2;
     size_t M, K, N, ldy;
     uint32_t flags;
-    int cluster_k;
+    int stages;          // decode kernel: weight ring depth (0 = choose)
+    // per-token absmax keys exchanged between chained decode launches (FFN): [ctas][16] each
+    const unsigned *amax_in;
+    int n_amax_in;
+    unsigned *amax_out;
 };
 
 bitnet_status_t launch_decode(const ForwardArgs &a, cudaStream_t stream);
 bool decode_supports(size_t M, size_t K, size_t N);
+bool decode_supports_dual(size_t M, size_t K, size_t N);   // gate and up in one launch
+int decode_grid(size_t N);                                  // CTAs of a decode launch over N output features
 
 bitnet_status_t launch_quantize_rows(const float *x, size_t M, size_t K, int8_t *q, float *a_scale,
                                      cudaStream_t stream);

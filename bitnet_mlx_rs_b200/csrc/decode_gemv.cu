@@ -1,40 +1,57 @@
 // Decode-time BitLinear (M <= 16 tokens): a weight-streaming W2A8 GEMV for sm_100a.
 //
-// What one launch does
-//   1. every lane issues its first 128-bit loads of packed weights (they do not depend
-//      on the preceding kernel, so under programmatic dependent launch they overlap it);
-//   2. the CTAs of a cluster quantise the activations together: each CTA folds |x| over
-//      its own K slice, the partial maxima are exchanged through distributed shared
-//      memory, and each CTA writes the int8 values of its slice to its shared memory in
-//      the order the tensor-core fragments want;
-//   3. packed weights go from global memory straight into mma fragments: masking a
-//      32-bit word with 0x03030303 << 2j leaves code << 2j in each byte, which is fed to
-//      the u8 x s8 tensor-core instruction unshifted; the four j classes accumulate
-//      separately and are combined exactly as acc0 + acc1/4 + acc2/16 + acc3/64.
-//      sum_k (code-1)*q = sum_k code*q - sum_k q, and sum_k q is known from step 2;
-//   4. the K-split partial sums of a cluster meet in the shared memory of the CTA that
-//      owns the 16-row block, which dequantises and writes y.
+// One CTA per SM owns a contiguous range of 16-row blocks of W.  Rows are contiguous in
+// the packed layout, so a block is ONE bulk-async (TMA) copy of 16*K/4 bytes into a ring
+// of shared-memory stages, issued by a producer warp and tracked by mbarriers; the first
+// stages are requested before the kernel waits for its predecessor on the stream
+// (programmatic dependent launch), so weight traffic overlaps the previous kernel, and
+// the kernel is sized so that two CTAs fit on an SM for that overlap.
 //
-// The contraction is order-independent integer arithmetic, so the result is the exact
-// int32 accumulator whatever the tiling.
+// Eight consumer warps split K between them.  Each warp quantises its own K slice of
+// the activations (per-token absmax is folded CTA-wide first, or taken from the partial
+// maxima its producer kernel left behind), keeps the int8 values in tensor-core fragment
+// order (in registers when a CTA has many blocks to stream), and for every block turns
+// packed words into mma operands with one AND per operand: masking a 32-bit word with
+// 0x03030303 << 2j leaves code << 2j in each byte, which the u8 x s8 mma.sync.m16n8k32
+// consumes unshifted; the four j classes accumulate separately and combine exactly as
+// acc0 + acc1/4 + acc2/16 + acc3/64.  sum_k (code-1)*q equals sum_k code*q - sum_k q, and
+// sum_k q is known from the quantiser.  The eight K-partial sums of a block meet in shared
+// memory; the warps take turns to dequantise a block and write y once a barrier says all
+// partial sums are in.
+//
+// The contraction is order-independent integer arithmetic, so the int32 accumulators are
+// exact whatever the tiling.
 //
 // Semantics: TernaryProcessor::quantize_activations + ternary_matmul_generic
 // (bitnet-inference/src/engine/ternary_operations.rs:117-172, :283-338) on the packed
 // layout of BitPacked2BitPacker (bitnet-quant/src/quantization/packing.rs:352-394);
 // replaces w2a8_gemv_kernel (bitnet-cuda/src/kernels/w2a8_gemv.cu:100-182).
-#include <cooperative_groups.h>
-
-#include <map>
-
 #include "common.cuh"
-
-namespace cg = cooperative_groups;
 
 namespace bitnet {
 
-constexpr int DEC_WARPS = 8;
-constexpr int DEC_THREADS = DEC_WARPS * 32;
+#ifdef BITNET_PHASE_TIMERS
+// Debug builds record %globaltimer at phase boundaries (warps 0 and 1 of the first CTAs).
+__device__ unsigned long long g_phase_ns[512][16];
+#define PHASE(i)                                                                      \
+    do {                                                                              \
+        if ((threadIdx.x & 31) == 0 && (threadIdx.x >> 5) <= 1 && blockIdx.x < 512) { \
+            unsigned long long t_;                                                    \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                    \
+            g_phase_ns[blockIdx.x][(i) + 8 * (threadIdx.x >> 5)] = t_;                \
+        }                                                                             \
+    } while (0)
+#else
+#define PHASE(i) do { } while (0)
+#endif
+
+constexpr int DEC_MAX_CWARPS = 16;                     // consumer warps: 8 (two CTAs per SM) or 16
+constexpr int DEC_MAX_STAGES = 8;
 constexpr int DEC_MAX_TOKENS = 16;
+constexpr unsigned DEC_WAIT_LIMIT = 1u << 22;          // polls before a wait gives up
+
+// Set when a bounded wait ran out (bit 0) -- read with bitnet_device_error_flags().
+__device__ unsigned g_decode_error_flags;
 
 struct DecodeParams {
     const uint8_t *wp;
@@ -48,18 +65,60 @@ struct DecodeParams {
     float w_scale, w_scale2;
     int M, K, N;
     size_t ldy;
-    int chunks;    // K / 64: one chunk is the 16 bytes (64 weights) a lane loads at once
-    int n_blocks;  // ceil(N / 16): 16-row blocks, one per warp per round
-    int steps;     // loop steps per round: ceil(ceil(chunks / S) / 4)
+    int chunks;          // K / 64: a chunk is the 16 bytes (64 weights) of one 128-bit load
+    int n_blocks;        // ceil(N / 16)
+    int stages;          // depth of the weight ring
+    int stages_free;     // stages that do not overlap the activation staging area
+    unsigned stage_bytes;   // one block of one matrix is 16 * K/4 contiguous bytes; a stage holds NW of them
+    unsigned stage_stride;  // stage_bytes plus a 128-byte tail whose first 16 bytes stay zero
+    const unsigned *amax_in;   // optional: per-token absmax keys left by the producer kernel, [n_amax_in][16]
+    int n_amax_in;
+    unsigned *amax_out;        // optional: this CTA's per-token absmax keys of what it wrote, [gridDim.x][16]
+    int weights_first;         // 1: start the weight stream at once (the activations are not ready yet anyway)
+    unsigned bst_offset; // where the activation staging area starts in dynamic shared memory
+    unsigned red_offset; // where the K-split sums start
 };
 
-__device__ __forceinline__ uint4 ldg_stream(const uint8_t *p)
+// ---- mbarrier / bulk-copy primitives ---------------------------------------------------------
+
+__device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned long long *bar, unsigned count)
 {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
-    return v;
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long *bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(unsigned long long *bar, unsigned bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait: false when the phase did not complete within DEC_WAIT_LIMIT polls.
+__device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned parity)
+{
+    const unsigned addr = smem_u32(bar);
+    for (unsigned n = 0; n < DEC_WAIT_LIMIT; ++n) {
+        unsigned done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    atomicOr(&g_decode_error_flags, 1u);
+    return false;
+}
+__device__ __forceinline__ void bulk_copy_g2s(void *dst_smem, const void *src, unsigned bytes, unsigned long long *bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(dst_smem)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
 }
 
 __device__ __forceinline__ void mma_u8s8(int (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
@@ -76,421 +135,570 @@ __device__ __forceinline__ unsigned word_of(const uint4 &v, int i)
     return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w));
 }
 
-// Shared memory carve-up (dynamic):
-//   act   : int8 activations of this CTA's K slice, fragment order, steps*4*NT*512 bytes
-//   red   : K-split exchange buffers, 2 * DEC_WARPS * NTD * 512 bytes (S > 1 only)
-// plus small static arrays below.
-template <int NT, int S, bool IN_I8, bool DUAL>
-__global__ void __launch_bounds__(DEC_THREADS, (NT == 1 && !DUAL) ? 2 : 1) decode_kernel(const DecodeParams p)
+template <int CW>
+__device__ __forceinline__ void consumer_barrier()
 {
-    constexpr int NW = DUAL ? 2 : 1;      // weight matrices streamed together
-    constexpr int D = (NW * NT >= 2) ? 2 : 4;  // loop steps of weights in flight per lane
-    constexpr int NTD = NT * NW;
+    asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");   // the consumer warps only
+}
 
-    extern __shared__ __align__(16) unsigned char smem[];
-    __shared__ unsigned s_key[DEC_MAX_TOKENS];       // absmax of this CTA's slice, as ordered keys
-    __shared__ int s_sumq[DEC_MAX_TOKENS];           // sum of int8 activations over this CTA's slice
-    __shared__ float s_ascale[DEC_MAX_TOKENS];       // absmax/127 per token
-    __shared__ float s_qscale[DEC_MAX_TOKENS];       // 127/absmax per token
+// Exact round-half-away quantisation of t = x*scale for |t| <= 2^22: trunc(|t| + c) with
+// c the largest float below 0.5 equals roundf(|t|) for every float (checked exhaustively),
+// and adding 2^23 with round-toward-zero leaves that integer in the low mantissa bits.
+__device__ __forceinline__ int quantize_fast(float x, float scale)
+{
+    const float t = __fmul_rn(x, scale);
+    const float a = fminf(__fadd_rn(fabsf(t), 0.49999997f), 127.0f);   // |t| < 127.5 whenever x is finite
+    const int mag = __float_as_int(__fadd_rz(a, 8388608.0f)) & 0xff;
+    const int neg = __float_as_int(t) >> 31;          // 0 or -1
+    const int q = (mag ^ neg) - neg;
+    return (t == t) ? q : 0;                            // NaN quantises to 0, like the oracle
+}
+
+// Dynamic shared memory: the weight ring [stages x stage_bytes], the activation staging
+// area (eight warp-private regions of SW*4*NT*512 bytes; with BREG and little shared memory
+// it overlaps the last ring stages, which the producer then fills only after every warp has
+// moved its activations to registers), and the K-split sums [stages x CW x NW*NT*512].
+// NT: token tiles of 8; SW: loop steps per warp (a step is 4 chunks = 256 k per warp);
+// BREG: activations live in registers during the main loop (pays when a CTA streams many blocks).
+// CW: consumer warps (8 leaves room for a second CTA on the SM; 16 hides more latency when one CTA
+// streams many blocks).
+template <int CW, int NT, int SW, bool BREG, bool IN_I8, bool DUAL>
+__global__ void __launch_bounds__((CW + 1) * 32, (CW == 8 && NT * (DUAL ? 2 : 1) <= 2 && !(BREG && SW >= 4)) ? 2 : 1)
+decode_kernel(const DecodeParams p)
+{
+    constexpr int DEC_CWARPS = CW;
+    constexpr int DEC_THREADS = (CW + 1) * 32;   // plus the producer warp
+    constexpr int NW = DUAL ? 2 : 1;          // weight matrices streamed together (gate and up)
+    constexpr int NTD = NT * NW;
+    constexpr int NP = 1;                     // accumulator sets per j class
+    constexpr int U = 3;                      // 16-wide groups a lane has in flight in the quantiser
+
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ __align__(8) unsigned long long s_full[DEC_MAX_STAGES], s_done[DEC_MAX_STAGES], s_empty[DEC_MAX_STAGES];
+    __shared__ __align__(8) unsigned long long s_bst_free, s_x_issued;
+    __shared__ unsigned s_key[DEC_MAX_TOKENS], s_okey[DEC_MAX_TOKENS];
+    __shared__ float s_ascale[DEC_MAX_TOKENS], s_qscale[DEC_MAX_TOKENS];
+    __shared__ int s_sumq[DEC_MAX_CWARPS][DEC_MAX_TOKENS];
+
+    // the next kernel on the stream may start (and fetch its own weights) from here on
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, tig = lane & 3;
+    const int NS = p.stages;
+    PHASE(0);
 
-    int rank = 0;
-    if constexpr (S > 1) rank = (int)cg::this_cluster().block_rank();
-    const int cluster_id = blockIdx.x / S;
-    const int n_clusters = gridDim.x / S;
+    const int b0 = (int)((long long)blockIdx.x * p.n_blocks / gridDim.x);
+    const int b1 = (int)((long long)(blockIdx.x + 1) * p.n_blocks / gridDim.x);
+    const int nb = b1 - b0;
+    const unsigned row_bytes = (unsigned)p.K / 4;
 
-    const int cb = (int)((long long)rank * p.chunks / S);
-    const int ce = (int)((long long)(rank + 1) * p.chunks / S);
-    const int Cs = ce - cb;
-    const int steps = p.steps;
-    const int blk_begin = (int)((long long)cluster_id * p.n_blocks / n_clusters);
-    const int blk_end = (int)((long long)(cluster_id + 1) * p.n_blocks / n_clusters);
-    const int rounds = (blk_end - blk_begin + DEC_WARPS - 1) / DEC_WARPS;
-    const int total = rounds * steps;
-    const size_t row_bytes = (size_t)p.K / 4;
+    unsigned char *s_w = smem;
+    unsigned char *s_bst = smem + p.bst_offset;
+    int *s_red = reinterpret_cast<int *>(smem + p.red_offset);
 
-    unsigned char *s_act = smem;
-    uint4 *s_red = reinterpret_cast<uint4 *>(smem + (size_t)steps * 4 * NT * 512);
-
-    // ---- weight pipeline -----------------------------------------------------------
-    uint4 wa[NW][D], wb[NW][D];   // rows g and g+8 of this warp's block, per matrix
-    int l_round = 0, l_step = 0;  // position of the next load
-    auto issue = [&](int d) {
-        const int blk = blk_begin + l_round * DEC_WARPS + warp;
-        const int ci = l_step * 4 + tig;
-        const bool ok = blk < blk_end && ci < Cs;
-        const int ra = blk * 16 + g, rb = ra + 8;
-        const size_t col = (size_t)(cb + ci) * 16;
-#pragma unroll
-        for (int w = 0; w < NW; ++w) {
-            const uint8_t *base = w == 0 ? p.wp : p.wp2;
-            wa[w][d] = (ok && ra < p.N) ? ldg_stream(base + (size_t)ra * row_bytes + col) : make_uint4(0, 0, 0, 0);
-            wb[w][d] = (ok && rb < p.N) ? ldg_stream(base + (size_t)rb * row_bytes + col) : make_uint4(0, 0, 0, 0);
+    if (tid == 0) {
+        for (int s = 0; s < NS; ++s) {
+            mbar_init(&s_full[s], 1);
+            mbar_init(&s_done[s], DEC_CWARPS);
+            mbar_init(&s_empty[s], 1);
         }
-        if (++l_step == steps) { l_step = 0; ++l_round; }
-    };
-#pragma unroll
-    for (int d = 0; d < D; ++d) {
-        if (d < total) issue(d);
-        else {
-#pragma unroll
-            for (int w = 0; w < NW; ++w) wa[w][d] = wb[w][d] = make_uint4(0, 0, 0, 0);
-        }
+        mbar_init(&s_bst_free, DEC_CWARPS);
+        mbar_init(&s_x_issued, DEC_CWARPS);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-
-    // Let the next kernel on the stream start its own weight fetch, then wait for the
-    // kernel that produced our activations.  Both are no-ops without the launch attribute.
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-
-    // ---- activation quantisation, shared by the cluster ---------------------------------
-    if (tid < DEC_MAX_TOKENS) { s_key[tid] = 0; s_sumq[tid] = 0; }
+    if (tid < DEC_MAX_TOKENS) { s_key[tid] = 0; s_okey[tid] = 0; }
+    for (int i = tid; i < DEC_MAX_CWARPS * DEC_MAX_TOKENS; i += DEC_THREADS) (&s_sumq[0][0])[i] = 0;
+    if (tid < NS * 4) reinterpret_cast<unsigned *>(s_w + (size_t)(tid >> 2) * p.stage_stride + p.stage_bytes)[tid & 3] = 0;
     __syncthreads();
 
-    const unsigned groups_per_token = (unsigned)Cs * 4;   // 16-wide k groups in the slice
-    const unsigned n_groups = (unsigned)p.M * groups_per_token;
+    // ======================= producer warp: keep the ring full ===============================
+    // Weights do not depend on the previous kernel on the stream: no grid-dependency wait here.
+    if (warp == DEC_CWARPS) {
+        if (lane == 0) {
+            // alone on the stream the activation loads go first, so that they do not queue behind
+            // the weight stream; under programmatic dependent launch the weights go first, since
+            // the activations do not exist yet
+            if (!p.weights_first && !mbar_wait(&s_x_issued, 0)) return;
+            for (int i = 0; i < nb; ++i) {
+                const int s = i % NS;
+                if (i >= NS) {
+                    if (!mbar_wait(&s_empty[s], (unsigned)((i / NS) - 1) & 1u)) return;
+                } else if (i >= p.stages_free) {   // first use of a stage that overlaps the staging area
+                    if (!mbar_wait(&s_bst_free, 0)) return;
+                }
+                const int row0 = (b0 + i) * 16;
+                const unsigned bytes = (unsigned)min(16, p.N - row0) * row_bytes;
+                mbar_arrive_expect_tx(&s_full[s], NW * bytes);
+                unsigned char *stage = s_w + (size_t)s * p.stage_stride;
+                bulk_copy_g2s(stage, p.wp + (size_t)row0 * row_bytes, bytes, &s_full[s]);
+                if constexpr (DUAL) bulk_copy_g2s(stage + 16 * row_bytes, p.wp2 + (size_t)row0 * row_bytes, bytes, &s_full[s]);
+            }
+        }
+        return;
+    }
 
-    if constexpr (!IN_I8) {
-        for (unsigned gid0 = 0; gid0 < n_groups; gid0 += DEC_THREADS) {
-            const unsigned gid = gid0 + tid;
-            unsigned key = 0, m = 0;
-            if (gid < n_groups) {
-                m = gid / groups_per_token;
-                const unsigned l = gid - m * groups_per_token;
-                const float4 *src = reinterpret_cast<const float4 *>(p.x + (size_t)m * p.K + (size_t)cb * 64 + (size_t)l * 16);
+    // ======================= consumer warps =====================================================
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // activations come from the previous kernel
+    PHASE(2);
+
+    const int cw0 = (int)((long long)warp * p.chunks / DEC_CWARPS);
+    const int cw1 = (int)((long long)(warp + 1) * p.chunks / DEC_CWARPS);
+    const int Cw = cw1 - cw0;                              // chunks of this warp's K slice (<= 4*SW)
+    unsigned char *bst = s_bst + (size_t)warp * (SW * 4 * NT * 512);
+    const unsigned groups_per_token = (unsigned)Cw * 4;   // 16-wide k groups
+    const unsigned n_groups = (unsigned)p.M * groups_per_token;
+    const size_t k_base = (size_t)cw0 * 64;
+    const bool single_batch = n_groups <= 32u * U;         // the whole slice fits in one batch of registers
+
+    float4 f[U][4];                                         // fp32 activations in flight
+    auto load_batch = [&](unsigned base) {
 #pragma unroll
-                for (int v = 0; v < 4; ++v) {
-                    const float4 f = __ldg(src + v);
-                    key = max(max(key, abs_key(f.x)), max(abs_key(f.y), max(abs_key(f.z), abs_key(f.w))));
+        for (int u = 0; u < U; ++u) {
+            const unsigned gid = base + u * 32 + lane;
+            if (gid < n_groups) {
+                const unsigned m = gid / groups_per_token;
+                const unsigned l = gid - m * groups_per_token;
+                const float4 *src = reinterpret_cast<const float4 *>(p.x + (size_t)m * p.K + k_base + (size_t)l * 16);
+#pragma unroll
+                for (int v = 0; v < 4; ++v) f[u][v] = __ldg(src + v);
+            }
+        }
+    };
+
+    // ---- pass 1: per-token absmax, folded CTA-wide ------------------------------------------------
+    if constexpr (!IN_I8) {
+        if (p.amax_in) {
+            // the kernel that produced x left one partial maximum per CTA and token
+            if (single_batch) load_batch(0);               // overlap the fetch of x with the fold
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_x_issued);
+            const int total = p.n_amax_in * DEC_MAX_TOKENS;
+            unsigned key = 0;
+            for (int i = tid; i < total; i += DEC_CWARPS * 32) {   // 256 threads, stride keeps the token fixed
+                key = max(key, __ldg(p.amax_in + i));
+            }
+            if (key) atomicMax(&s_key[tid & (DEC_MAX_TOKENS - 1)], key);
+        } else {
+            unsigned cur_m = 0, cur_key = 0;   // running maximum of the token this lane is in
+            for (unsigned base = 0; base < n_groups; base += 32u * U) {
+                load_batch(base);
+                if (base == 0) {
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&s_x_issued);   // the weight stream may start
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const unsigned gid = base + u * 32 + lane;
+                    if (gid < n_groups) {
+                        const unsigned m = gid / groups_per_token;
+                        unsigned key = 0;
+#pragma unroll
+                        for (int v = 0; v < 4; ++v)
+                            key = max(max(key, abs_key(f[u][v].x)), max(abs_key(f[u][v].y), max(abs_key(f[u][v].z), abs_key(f[u][v].w))));
+                        if (m != cur_m) {
+                            if (cur_key) atomicMax(&s_key[cur_m], cur_key);
+                            cur_m = m;
+                            cur_key = 0;
+                        }
+                        cur_key = max(cur_key, key);
+                    }
                 }
             }
-            // a warp's 32 groups usually belong to one or two tokens: fold those in registers
-            const unsigned m_lo = __shfl_sync(0xffffffffu, m, 0);
-            const unsigned k_lo = __reduce_max_sync(0xffffffffu, m == m_lo ? key : 0u);
-            const unsigned k_hi = __reduce_max_sync(0xffffffffu, m == m_lo + 1 ? key : 0u);
-            if (lane == 0) {
-                if (k_lo) atomicMax(&s_key[m_lo], k_lo);
-                if (k_hi) atomicMax(&s_key[m_lo + 1], k_hi);
-            }
-            if (m > m_lo + 1 && key) atomicMax(&s_key[m], key);
+            if (cur_key) atomicMax(&s_key[cur_m], cur_key);
+            if (n_groups == 0 && lane == 0) mbar_arrive(&s_x_issued);
         }
-        __syncthreads();
-        unsigned key = 0;
-        if constexpr (S > 1) {
-            cg::cluster_group cluster = cg::this_cluster();
-            cluster.sync();   // every CTA of the cluster is running and has published its partial keys
-            if (tid < p.M) {
-#pragma unroll
-                for (int r = 0; r < S; ++r) key = max(key, *cluster.map_shared_rank(&s_key[tid], r));
-            }
-        } else {
-            if (tid < p.M) key = s_key[tid];
-        }
+        consumer_barrier<CW>();
         if (tid < p.M) {
-            const float absmax = __uint_as_float(key);
+            const float absmax = __uint_as_float(s_key[tid]);
             s_ascale[tid] = dequant_scale(absmax);
             s_qscale[tid] = quant_scale(absmax);
             if (p.a_scale_out && blockIdx.x == 0) p.a_scale_out[tid] = dequant_scale(absmax);
         }
-        __syncthreads();
+        consumer_barrier<CW>();
     } else {
-        if constexpr (S > 1) cg::this_cluster().sync();
         if (tid < p.M) s_ascale[tid] = 1.0f;
-        __syncthreads();
+        if (lane == 0) mbar_arrive(&s_x_issued);
     }
+    PHASE(3);
 
-    // pass 2: quantise this slice into fragment order
-    for (unsigned gid0 = 0; gid0 < n_groups; gid0 += DEC_THREADS) {
-        const unsigned gid = gid0 + tid;
-        unsigned m = 0;
-        int sum = 0;
-        if (gid < n_groups) {
-            m = gid / groups_per_token;
-            const unsigned l = gid - m * groups_per_token;   // 16-wide group inside the slice
-            int q[16];
-            if constexpr (IN_I8) {
-                const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(p.x_i8 + (size_t)m * p.K + (size_t)cb * 64 + (size_t)l * 16));
+    // ---- pass 2: quantise this warp's slice into fragment order ---------------------------------------
+    {
+        unsigned cur_m = 0;
+        int cur_sum = 0;
+        for (unsigned base = 0; base < n_groups; base += 32u * U) {
+            if constexpr (!IN_I8) {
+                if (!single_batch) load_batch(base);       // second read: L1/L2 resident
+            }
 #pragma unroll
-                for (int e = 0; e < 16; ++e) q[e] = (int)(int8_t)((word_of(raw, e >> 2) >> (8 * (e & 3))) & 0xffu);
-            } else {
-                const float scale = s_qscale[m];
-                const float4 *src = reinterpret_cast<const float4 *>(p.x + (size_t)m * p.K + (size_t)cb * 64 + (size_t)l * 16);
+            for (int u = 0; u < U; ++u) {
+                const unsigned gid = base + u * 32 + lane;
+                if (gid < n_groups) {
+                    const unsigned m = gid / groups_per_token;
+                    const unsigned l = gid - m * groups_per_token;
+                    int q[16];
+                    if constexpr (IN_I8) {
+                        const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(p.x_i8 + (size_t)m * p.K + k_base + (size_t)l * 16));
 #pragma unroll
-                for (int v = 0; v < 4; ++v) {
-                    const float4 f = __ldg(src + v);
-                    q[4 * v + 0] = quantize_one(f.x, scale);
-                    q[4 * v + 1] = quantize_one(f.y, scale);
-                    q[4 * v + 2] = quantize_one(f.z, scale);
-                    q[4 * v + 3] = quantize_one(f.w, scale);
-                }
-                if (p.q_out && cluster_id == 0) {
-                    uint4 canon;
-                    canon.x = (q[0] & 0xff) | ((q[1] & 0xff) << 8) | ((q[2] & 0xff) << 16) | ((unsigned)(q[3] & 0xff) << 24);
-                    canon.y = (q[4] & 0xff) | ((q[5] & 0xff) << 8) | ((q[6] & 0xff) << 16) | ((unsigned)(q[7] & 0xff) << 24);
-                    canon.z = (q[8] & 0xff) | ((q[9] & 0xff) << 8) | ((q[10] & 0xff) << 16) | ((unsigned)(q[11] & 0xff) << 24);
-                    canon.w = (q[12] & 0xff) | ((q[13] & 0xff) << 8) | ((q[14] & 0xff) << 16) | ((unsigned)(q[15] & 0xff) << 24);
-                    *reinterpret_cast<uint4 *>(p.q_out + (size_t)m * p.K + (size_t)cb * 64 + (size_t)l * 16) = canon;
+                        for (int e = 0; e < 16; ++e) q[e] = (int)(int8_t)((word_of(raw, e >> 2) >> (8 * (e & 3))) & 0xffu);
+                    } else {
+                        const float scale = s_qscale[m];
+                        // a huge absmax makes scale subnormal or zero; the fast path assumes neither
+                        const bool fast = scale >= 1e-30f && scale <= 1e30f;
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            if (fast) {
+                                q[4 * v + 0] = quantize_fast(f[u][v].x, scale);
+                                q[4 * v + 1] = quantize_fast(f[u][v].y, scale);
+                                q[4 * v + 2] = quantize_fast(f[u][v].z, scale);
+                                q[4 * v + 3] = quantize_fast(f[u][v].w, scale);
+                            } else {
+                                q[4 * v + 0] = quantize_one(f[u][v].x, scale);
+                                q[4 * v + 1] = quantize_one(f[u][v].y, scale);
+                                q[4 * v + 2] = quantize_one(f[u][v].z, scale);
+                                q[4 * v + 3] = quantize_one(f[u][v].w, scale);
+                            }
+                        }
+                        if (p.q_out && blockIdx.x == 0) {
+                            uint4 canon;
+                            canon.x = (q[0] & 0xff) | ((q[1] & 0xff) << 8) | ((q[2] & 0xff) << 16) | ((unsigned)(q[3] & 0xff) << 24);
+                            canon.y = (q[4] & 0xff) | ((q[5] & 0xff) << 8) | ((q[6] & 0xff) << 16) | ((unsigned)(q[7] & 0xff) << 24);
+                            canon.z = (q[8] & 0xff) | ((q[9] & 0xff) << 8) | ((q[10] & 0xff) << 16) | ((unsigned)(q[11] & 0xff) << 24);
+                            canon.w = (q[12] & 0xff) | ((q[13] & 0xff) << 8) | ((q[14] & 0xff) << 16) | ((unsigned)(q[15] & 0xff) << 24);
+                            *reinterpret_cast<uint4 *>(p.q_out + (size_t)m * p.K + k_base + (size_t)l * 16) = canon;
+                        }
+                    }
+                    // word j holds k = j, j+4, j+8, j+12 of the group: the bytes that the mask
+                    // 0x03030303 << 2j selects from a packed weight word
+                    uint4 frag;
+                    frag.x = (q[0] & 0xff) | ((q[4] & 0xff) << 8) | ((q[8] & 0xff) << 16) | ((unsigned)(q[12] & 0xff) << 24);
+                    frag.y = (q[1] & 0xff) | ((q[5] & 0xff) << 8) | ((q[9] & 0xff) << 16) | ((unsigned)(q[13] & 0xff) << 24);
+                    frag.z = (q[2] & 0xff) | ((q[6] & 0xff) << 8) | ((q[10] & 0xff) << 16) | ((unsigned)(q[14] & 0xff) << 24);
+                    frag.w = (q[3] & 0xff) | ((q[7] & 0xff) << 8) | ((q[11] & 0xff) << 16) | ((unsigned)(q[15] & 0xff) << 24);
+                    int sum = 0;
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) sum += q[e];
+                    if (m != cur_m) {
+                        if (cur_sum) atomicAdd(&s_sumq[warp][cur_m], cur_sum);
+                        cur_m = m;
+                        cur_sum = 0;
+                    }
+                    cur_sum += sum;
+                    // slice-relative chunk c = l/4 is read by lanes with tig = c%4 in step c/4; i = l%4 is
+                    // the 16-wide group inside the chunk; token m sits in tile m/8, fragment row m%8
+                    const unsigned c = l >> 2, i = l & 3;
+                    const unsigned step = c >> 2, ctig = c & 3;
+                    const unsigned off = (((step * 4 + i) * NT + (m >> 3)) * 32 + (m & 7) * 4 + ctig) * 16;
+                    *reinterpret_cast<uint4 *>(bst + off) = frag;
                 }
             }
-            // word j holds k = j, j+4, j+8, j+12 of the group: the bytes the mask
-            // 0x03030303 << 2j selects from a packed weight word
-            uint4 frag;
-            frag.x = (q[0] & 0xff) | ((q[4] & 0xff) << 8) | ((q[8] & 0xff) << 16) | ((unsigned)(q[12] & 0xff) << 24);
-            frag.y = (q[1] & 0xff) | ((q[5] & 0xff) << 8) | ((q[9] & 0xff) << 16) | ((unsigned)(q[13] & 0xff) << 24);
-            frag.z = (q[2] & 0xff) | ((q[6] & 0xff) << 8) | ((q[10] & 0xff) << 16) | ((unsigned)(q[14] & 0xff) << 24);
-            frag.w = (q[3] & 0xff) | ((q[7] & 0xff) << 8) | ((q[11] & 0xff) << 16) | ((unsigned)(q[15] & 0xff) << 24);
-#pragma unroll
-            for (int e = 0; e < 16; ++e) sum += q[e];
-            // slice-relative chunk c = l/4 is read by lanes with tig = c%4 in step c/4;
-            // i = l%4 is the 16-wide group inside the chunk; token m sits in tile m/8, row m%8
-            const unsigned c = l >> 2, i = l & 3;
-            const unsigned step = c >> 2, ctig = c & 3;
-            const unsigned off = (((step * 4 + i) * NT + (m >> 3)) * 32 + (m & 7) * 4 + ctig) * 16;
-            *reinterpret_cast<uint4 *>(s_act + off) = frag;
         }
-        const unsigned m_lo = __shfl_sync(0xffffffffu, m, 0);
-        const int s_lo = __reduce_add_sync(0xffffffffu, m == m_lo ? sum : 0);
-        const int s_hi = __reduce_add_sync(0xffffffffu, m == m_lo + 1 ? sum : 0);
-        if (lane == 0) {
-            if (s_lo) atomicAdd(&s_sumq[m_lo], s_lo);
-            if (s_hi) atomicAdd(&s_sumq[m_lo + 1], s_hi);
-        }
-        if (m > m_lo + 1 && sum) atomicAdd(&s_sumq[m], sum);
+        if (cur_sum) atomicAdd(&s_sumq[warp][cur_m], cur_sum);
     }
-    __syncthreads();
+    __syncwarp();
 
-    // ---- main loop -------------------------------------------------------------------------
-    int acc[NW][NT][4][4];   // [matrix][token tile][j class][fragment register]
-    auto clear_acc = [&]() {
+    // activations of this warp's slice: registers for the whole kernel when asked for
+    uint4 breg[BREG ? SW : 1][4][NT];
+    if constexpr (BREG) {
+#pragma unroll
+        for (int s2 = 0; s2 < SW; ++s2)
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int t = 0; t < NT; ++t)
+                    breg[s2][i][t] = *reinterpret_cast<const uint4 *>(bst + ((size_t)((s2 * 4 + i) * NT + t) * 32 + lane) * 16);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_bst_free);   // the staging area may be overwritten by weights
+    }
+    int sq[NT][2];
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+        sq[t][0] = s_sumq[warp][8 * t + 2 * tig];
+        sq[t][1] = s_sumq[warp][8 * t + 2 * tig + 1];
+    }
+    PHASE(4);
+
+    // ---- main loop over this CTA's blocks -----------------------------------------------------------------
+    // Byte offsets of this lane's 16-byte chunks inside a stage; a chunk beyond the slice reads the
+    // stage's zero tail instead.  Rows past N of the last block hold stale bytes: they only feed
+    // accumulators of rows that are never written.
+    unsigned off_a[NW][SW], off_b[NW][SW];
+#pragma unroll
+    for (int w = 0; w < NW; ++w)
+#pragma unroll
+        for (int s2 = 0; s2 < SW; ++s2) {
+            const int ci = s2 * 4 + tig;
+            const unsigned col = (unsigned)(cw0 + ci) * 16;
+            off_a[w][s2] = ci < Cw ? (unsigned)(w * 16 + g) * row_bytes + col : p.stage_bytes;
+            off_b[w][s2] = ci < Cw ? (unsigned)(w * 16 + g + 8) * row_bytes + col : p.stage_bytes;
+        }
+
+    for (int i = 0; i < nb; ++i) {
+        const int s = i % NS;
+        const unsigned parity = (unsigned)(i / NS) & 1u;
+        if (i == 8) PHASE(5);
+        if (!mbar_wait(&s_full[s], parity)) return;
+        if (i == 8) PHASE(6);
+        const int blk = b0 + i;
+        const int row_a = blk * 16 + g, row_b = row_a + 8;
+        const unsigned char *stage = s_w + (size_t)s * p.stage_stride;
+
+        int acc[NW][NT][NP][4][4];   // [matrix][token tile][chain][j class][fragment register]
 #pragma unroll
         for (int w = 0; w < NW; ++w)
 #pragma unroll
             for (int t = 0; t < NT; ++t)
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
+                for (int c = 0; c < NP; ++c)
 #pragma unroll
-                    for (int r = 0; r < 4; ++r) acc[w][t][j][r] = 0;
-    };
-    clear_acc();
+                    for (int j = 0; j < 4; ++j)
+#pragma unroll
+                        for (int r = 0; r < 4; ++r) acc[w][t][c][j][r] = 0;
 
-    int c_round = 0, c_step = 0;   // position of the step being consumed
-    for (int it0 = 0; it0 < total; it0 += D) {
 #pragma unroll
-        for (int d = 0; d < D; ++d) {
-            if (it0 + d < total) {
-                // B fragments: 16 bytes per (16-wide group, token tile), conflict-free
+        for (int s2 = 0; s2 < SW; ++s2) {
+            if (s2 * 4 < Cw) {   // warp-uniform: this step holds at least one chunk of the slice
                 uint4 bw[4][NT];
 #pragma unroll
-                for (int i = 0; i < 4; ++i)
+                for (int i2 = 0; i2 < 4; ++i2)
 #pragma unroll
-                    for (int t = 0; t < NT; ++t)
-                        bw[i][t] = *reinterpret_cast<const uint4 *>(s_act + ((size_t)((c_step * 4 + i) * NT + t) * 32 + lane) * 16);
+                    for (int t = 0; t < NT; ++t) {
+                        if constexpr (BREG) bw[i2][t] = breg[s2][i2][t];
+                        else bw[i2][t] = *reinterpret_cast<const uint4 *>(bst + ((size_t)((s2 * 4 + i2) * NT + t) * 32 + lane) * 16);
+                    }
 #pragma unroll
                 for (int w = 0; w < NW; ++w) {
+                    const uint4 wa = *reinterpret_cast<const uint4 *>(stage + off_a[w][s2]);
+                    const uint4 wb = *reinterpret_cast<const uint4 *>(stage + off_b[w][s2]);
 #pragma unroll
                     for (int pr = 0; pr < 2; ++pr) {
-                        const unsigned a_lo0 = word_of(wa[w][d], 2 * pr), a_lo1 = word_of(wa[w][d], 2 * pr + 1);
-                        const unsigned a_hi0 = word_of(wb[w][d], 2 * pr), a_hi1 = word_of(wb[w][d], 2 * pr + 1);
+                        const unsigned a_lo0 = word_of(wa, 2 * pr), a_lo1 = word_of(wa, 2 * pr + 1);
+                        const unsigned a_hi0 = word_of(wb, 2 * pr), a_hi1 = word_of(wb, 2 * pr + 1);
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
                             const unsigned mask = 0x03030303u << (2 * j);
 #pragma unroll
                             for (int t = 0; t < NT; ++t)
-                                mma_u8s8(acc[w][t][j], a_lo0 & mask, a_hi0 & mask, a_lo1 & mask, a_hi1 & mask,
+                                mma_u8s8(acc[w][t][pr % NP][j], a_lo0 & mask, a_hi0 & mask, a_lo1 & mask, a_hi1 & mask,
                                          word_of(bw[2 * pr][t], j), word_of(bw[2 * pr + 1][t], j));
                         }
                     }
                 }
-
-                const bool tile_done = (c_step == steps - 1);
-                const int blk = blk_begin + c_round * DEC_WARPS + warp;   // this warp's block in the round
-                if (++c_step == steps) { c_step = 0; ++c_round; }
-
-                // refill this slot before the (possibly long) tile epilogue
-                if (it0 + d + D < total) issue(d);
-
-                if (tile_done) {
-                    // exact partial sums of sum_k (code-1)*q over this CTA's K slice
-                    int part[NTD][4];
-#pragma unroll
-                    for (int w = 0; w < NW; ++w)
-#pragma unroll
-                        for (int t = 0; t < NT; ++t) {
-                            const int sq0 = s_sumq[8 * t + 2 * tig], sq1 = s_sumq[8 * t + 2 * tig + 1];
-#pragma unroll
-                            for (int r = 0; r < 4; ++r) {
-                                const int v = acc[w][t][0][r] + (acc[w][t][1][r] >> 2) + (acc[w][t][2][r] >> 4) +
-                                              (acc[w][t][3][r] >> 6);
-                                part[w * NT + t][r] = v - ((r & 1) ? sq1 : sq0);
-                            }
-                        }
-                    clear_acc();
-
-                    int fin_blk = blk;      // block this warp finalises
-                    bool fin = true;
-                    if constexpr (S > 1) {
-                        cg::cluster_group cluster = cg::this_cluster();
-                        const int buf = (c_round + 1) & 1;   // parity of the round just finished
-                        // owner of warp w's block is rank w % S, slot w / S
-                        uint4 *dst = cluster.map_shared_rank(s_red, warp % S) +
-                                     ((((size_t)buf * S + rank) * (DEC_WARPS / S) + warp / S) * NTD) * 32 + lane;
-#pragma unroll
-                        for (int u = 0; u < NTD; ++u)
-                            dst[u * 32] = make_uint4((unsigned)part[u][0], (unsigned)part[u][1], (unsigned)part[u][2], (unsigned)part[u][3]);
-                        cluster.sync();
-                        fin = warp < DEC_WARPS / S;
-                        if (fin) {
-                            const int src_warp = warp * S + rank;   // the warp index whose block we own
-                            fin_blk = blk - warp + src_warp;
-#pragma unroll
-                            for (int u = 0; u < NTD; ++u)
-#pragma unroll
-                                for (int r = 0; r < 4; ++r) part[u][r] = 0;
-#pragma unroll
-                            for (int r2 = 0; r2 < S; ++r2) {
-                                const uint4 *src = s_red + ((((size_t)buf * S + r2) * (DEC_WARPS / S) + warp) * NTD) * 32 + lane;
-#pragma unroll
-                                for (int u = 0; u < NTD; ++u) {
-                                    const uint4 v = src[u * 32];
-                                    part[u][0] += (int)v.x; part[u][1] += (int)v.y; part[u][2] += (int)v.z; part[u][3] += (int)v.w;
-                                }
-                            }
-                        }
-                    }
-
-                    if (fin && fin_blk < blk_end) {
-                        const int row_a = fin_blk * 16 + g, row_b = row_a + 8;
-#pragma unroll
-                        for (int t = 0; t < NT; ++t)
-#pragma unroll
-                            for (int r = 0; r < 4; ++r) {
-                                const int m = 8 * t + 2 * tig + (r & 1);
-                                const int row = (r & 2) ? row_b : row_a;
-                                if (m < p.M && row < p.N) {
-                                    const size_t o = (size_t)m * p.ldy + row;
-                                    if constexpr (DUAL) {
-                                        const float a = s_ascale[m];
-                                        const float gate = __fmul_rn((float)part[t][r], __fmul_rn(p.w_scale, a));
-                                        const float up = __fmul_rn((float)part[NT + t][r], __fmul_rn(p.w_scale2, a));
-                                        const float rl = fmaxf(gate, 0.0f);
-                                        p.y[o] = __fmul_rn(up, __fmul_rn(rl, rl));
-                                    } else {
-                                        if (p.acc_out) p.acc_out[o] = part[t][r];
-                                        if (p.y) p.y[o] = __fmul_rn((float)part[t][r], __fmul_rn(p.w_scale, s_ascale[m]));
-                                    }
-                                }
-                            }
-                    }
-                }
             }
         }
-    }
 
-    // no CTA may leave while a peer can still read or write its shared memory
-    if constexpr (S > 1) cg::this_cluster().sync();
+        if (i == 8) PHASE(7);
+        // exact partial sums of sum_k (code-1)*q over this warp's K slice, left in this warp's slot
+        int4 *red = reinterpret_cast<int4 *>(s_red) + (size_t)s * (DEC_CWARPS * NTD * 32);
+#pragma unroll
+        for (int w = 0; w < NW; ++w)
+#pragma unroll
+            for (int t = 0; t < NT; ++t) {
+                int v[4];
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    v[r] = -sq[t][r & 1];
+#pragma unroll
+                    for (int c = 0; c < NP; ++c)
+                        v[r] += acc[w][t][c][0][r] + (acc[w][t][c][1][r] >> 2) + (acc[w][t][c][2][r] >> 4) + (acc[w][t][c][3][r] >> 6);
+                }
+                red[(warp * NTD + w * NT + t) * 32 + lane] = make_int4(v[0], v[1], v[2], v[3]);
+            }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_done[s]);   // release: this warp's sums are in, its reads of the stage are over
+
+        // the warps take turns to finish a block: wait until all partial sums are in, add them up
+        if (((i + (int)blockIdx.x) & (DEC_CWARPS - 1)) == warp) {
+            if (!mbar_wait(&s_done[s], parity)) return;
+            int tot[NTD][4];
+#pragma unroll
+            for (int u = 0; u < NTD; ++u) {
+                tot[u][0] = tot[u][1] = tot[u][2] = tot[u][3] = 0;
+#pragma unroll
+                for (int w2 = 0; w2 < DEC_CWARPS; ++w2) {
+                    const int4 v = red[(w2 * NTD + u) * 32 + lane];
+                    tot[u][0] += v.x; tot[u][1] += v.y; tot[u][2] += v.z; tot[u][3] += v.w;
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_empty[s]);   // release: the stage and its sums may be reused
+#pragma unroll
+            for (int t = 0; t < NT; ++t)
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    const int m = 8 * t + 2 * tig + (r & 1);
+                    const int row = (r & 2) ? row_b : row_a;
+                    if (m < p.M && row < p.N) {
+                        const size_t o = (size_t)m * p.ldy + row;
+                        float out;
+                        if constexpr (DUAL) {
+                            const float a = s_ascale[m];
+                            const float gate = __fmul_rn((float)tot[t][r], __fmul_rn(p.w_scale, a));
+                            const float up = __fmul_rn((float)tot[NT + t][r], __fmul_rn(p.w_scale2, a));
+                            const float rl = fmaxf(gate, 0.0f);
+                            out = __fmul_rn(up, __fmul_rn(rl, rl));
+                            p.y[o] = out;
+                        } else {
+                            if (p.acc_out) p.acc_out[o] = tot[t][r];
+                            out = __fmul_rn((float)tot[t][r], __fmul_rn(p.w_scale, s_ascale[m]));
+                            if (p.y) p.y[o] = out;
+                        }
+                        if (p.amax_out) {
+                            const unsigned key = abs_key(out);
+                            if (key > s_okey[m]) atomicMax(&s_okey[m], key);
+                        }
+                    }
+                }
+        }
+    }
+    if (p.amax_out) {   // this CTA's share of the per-token absmax of what the launch wrote
+        consumer_barrier<CW>();
+        if (tid < DEC_MAX_TOKENS) p.amax_out[(size_t)blockIdx.x * DEC_MAX_TOKENS + tid] = s_okey[tid];
+    }
+    PHASE(1);
 }
 
-// ---- launcher ---------------------------------------------------------------------------------
+#ifdef BITNET_PHASE_TIMERS
+extern "C" int bitnet_debug_read_phases(unsigned long long *host)
+{
+    return (int)cudaMemcpyFromSymbol(host, g_phase_ns, sizeof(g_phase_ns));
+}
+#endif
+
+// ---- launcher -----------------------------------------------------------------------------------------
+
+static int steps_needed(size_t K, int cw) { return (int)(((K / 64 + cw - 1) / cw + 3) / 4); }
+
+static bool shape_fits(size_t M, size_t K, bool dual)
+{
+    const int sw = steps_needed(K, 8);   // the eight-warp kernels are the ones every shape can fall back to
+    const int nt = M > 8 ? 2 : 1;
+    if (dual) return sw <= 2;
+    return nt == 1 ? sw <= 8 : sw <= 4;
+}
 
 bool decode_supports(size_t M, size_t K, size_t N)
 {
-    return M >= 1 && M <= DEC_MAX_TOKENS && K >= 64 && K % 64 == 0 && K <= 65536 && N >= 1 && N <= (1u << 30);
+    return M >= 1 && M <= DEC_MAX_TOKENS && K >= 64 && K % 64 == 0 && N >= 1 && N <= (1u << 30) && shape_fits(M, K, false);
 }
 
-struct DecodeChoice { int S; };
+bool decode_supports_dual(size_t M, size_t K, size_t N) { return decode_supports(M, K, N) && shape_fits(M, K, true); }
 
-template <int NT, int S, bool IN_I8, bool DUAL>
-static bitnet_status_t launch_one(const DecodeParams &p, uint32_t flags, cudaStream_t stream)
+// CTAs a decode launch over N output features uses (also the number of absmax partials it writes).
+int decode_grid(size_t N)
 {
-    auto kernel = decode_kernel<NT, S, IN_I8, DUAL>;
-    constexpr int NTD = NT * (DUAL ? 2 : 1);
-    const size_t smem = (size_t)p.steps * 4 * NT * 512 + (S > 1 ? (size_t)2 * DEC_WARPS * NTD * 512 : 0);
-    static size_t smem_set = 0;   // per instantiation
+    const int n_blocks = (int)((N + 15) / 16);
+    const int sms = device_sm_count();
+    return n_blocks < sms ? n_blocks : sms;
+}
+
+template <int CW, int NT, int SW, bool BREG, bool IN_I8, bool DUAL>
+static bitnet_status_t launch_one(DecodeParams p, uint32_t flags, cudaStream_t stream)
+{
+    auto kernel = decode_kernel<CW, NT, SW, BREG, IN_I8, DUAL>;
+    constexpr int NW = DUAL ? 2 : 1;
+    const unsigned row_bytes = (unsigned)p.K / 4;
+    const unsigned real_stage = NW * 16 * row_bytes;
+    p.stage_bytes = real_stage;
+    p.stage_stride = real_stage + 128;
+    const size_t bst_bytes = (size_t)CW * SW * 4 * NT * 512;
+    const size_t red_per_stage = (size_t)CW * NW * NT * 512;   // one slot of partial sums per consumer warp
+    const size_t budget = 208 * 1024;
+
+    const int grid = decode_grid((size_t)p.N);
+    const int max_blocks = (p.n_blocks + grid - 1) / grid;
+    int want = p.stages > 0 ? p.stages : DEC_MAX_STAGES;
+    if (want > DEC_MAX_STAGES) want = DEC_MAX_STAGES;
+    if (want > max_blocks) want = max_blocks;
+
+    int stages = want, stages_free = want;
+    size_t bst_offset = 0, smem = 0;
+    if ((size_t)want * (p.stage_stride + red_per_stage) + bst_bytes <= budget) {
+        // everything fits side by side
+        bst_offset = (size_t)want * p.stage_stride;
+        smem = bst_offset + bst_bytes + (size_t)want * red_per_stage;
+    } else if (BREG) {
+        // let the ring grow over the staging area; those stages open once the activations
+        // are in registers
+        while (stages > 1 && (size_t)stages * (p.stage_stride + red_per_stage) > budget) --stages;
+        size_t ring = (size_t)stages * p.stage_stride;
+        if (ring < bst_bytes + p.stage_stride) ring = bst_bytes + p.stage_stride;   // at least one stage stays free
+        bst_offset = ring - bst_bytes;
+        stages_free = (int)(bst_offset / p.stage_stride);
+        if (stages_free > stages) stages_free = stages;
+        smem = ring + (size_t)stages * red_per_stage;
+    } else {
+        while (stages > 1 && (size_t)stages * (p.stage_stride + red_per_stage) + bst_bytes > budget) --stages;
+        stages_free = stages;
+        bst_offset = (size_t)stages * p.stage_stride;
+        smem = bst_offset + bst_bytes + (size_t)stages * red_per_stage;
+    }
+    if (smem > 227 * 1024 || stages_free < 1)
+        return fail(BITNET_ERR_UNSUPPORTED_OPERATION, "decode kernel: K=%d needs %zu bytes of shared memory", p.K, smem);
+    p.stages = stages;
+    p.stages_free = stages_free;
+    p.bst_offset = (unsigned)bst_offset;
+    p.red_offset = (unsigned)(smem - (size_t)stages * red_per_stage);
+
+    static size_t smem_set = 0;   // per instantiation; one launching thread per process
     if (smem > 48 * 1024 && smem > smem_set) {
         BITNET_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         smem_set = smem;
     }
-    if (smem > 227 * 1024) return fail(BITNET_ERR_UNSUPPORTED_OPERATION, "decode kernel: K=%d needs %zu bytes of shared memory", p.K, smem);
 
     cudaLaunchConfig_t cfg = {};
-    cudaLaunchAttribute attrs[2];
+    cudaLaunchAttribute attrs[1];
     int n_attrs = 0;
-    if (S > 1) {
-        attrs[n_attrs].id = cudaLaunchAttributeClusterDimension;
-        attrs[n_attrs].val.clusterDim.x = S;
-        attrs[n_attrs].val.clusterDim.y = 1;
-        attrs[n_attrs].val.clusterDim.z = 1;
-        ++n_attrs;
-    }
     if (flags & BITNET_FLAG_PDL) {
         attrs[n_attrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attrs[n_attrs].val.programmaticStreamSerializationAllowed = 1;
         ++n_attrs;
     }
-    cfg.blockDim = dim3(DEC_THREADS);
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((CW + 1) * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cfg.attrs = attrs;
     cfg.numAttrs = n_attrs;
-
-    // resident clusters: ask the occupancy calculator once per (instantiation, smem size)
-    static std::map<size_t, int> resident;   // not thread-safe by design: one launching thread per process
-    auto it = resident.find(smem);
-    if (it == resident.end()) {
-        int n = 0;
-        if (S > 1) {
-            cfg.gridDim = dim3(S * 64);
-            cudaLaunchAttribute cattr = attrs[0];
-            cudaLaunchConfig_t qcfg = cfg;
-            qcfg.attrs = &cattr;
-            qcfg.numAttrs = 1;
-            BITNET_CUDA(cudaOccupancyMaxActiveClusters(&n, kernel, &qcfg));
-        } else {
-            int per_sm = 0;
-            BITNET_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, DEC_THREADS, smem));
-            n = per_sm * device_sm_count();
-        }
-        if (n < 1) return fail(BITNET_ERR_KERNEL_EXECUTION, "decode kernel cannot be resident (S=%d, smem=%zu)", S, smem);
-        it = resident.emplace(smem, n).first;
-    }
-    const int cached_clusters = it->second;
-    int n_clusters = cached_clusters < p.n_blocks ? cached_clusters : p.n_blocks;
-    cfg.gridDim = dim3((unsigned)(n_clusters * S));
     BITNET_CUDA(cudaLaunchKernelEx(&cfg, kernel, p));
     return BITNET_OK;
 }
 
 template <int NT, bool IN_I8, bool DUAL>
-static bitnet_status_t launch_s(int S, const DecodeParams &p, uint32_t flags, cudaStream_t stream)
+static bitnet_status_t launch_sw(bool wide, bool breg, const DecodeParams &p, uint32_t flags, cudaStream_t stream)
 {
-    switch (S) {
-        case 1: return launch_one<NT, 1, IN_I8, DUAL>(p, flags, stream);
-        case 2: return launch_one<NT, 2, IN_I8, DUAL>(p, flags, stream);
-        case 4: return launch_one<NT, 4, IN_I8, DUAL>(p, flags, stream);
-        case 8: return launch_one<NT, 8, IN_I8, DUAL>(p, flags, stream);
+    if (wide) {
+        // sixteen consumer warps, activations in registers: one CTA per SM streaming many blocks
+        if constexpr (NT == 1 && !DUAL) {
+            const int sw = steps_needed((size_t)p.K, 16);
+            if (sw <= 1) return launch_one<16, 1, 1, true, IN_I8, false>(p, flags, stream);
+            if (sw <= 2) return launch_one<16, 1, 2, true, IN_I8, false>(p, flags, stream);
+        }
     }
-    return fail(BITNET_ERR_INVALID_CONFIG, "cluster_k must be 1, 2, 4 or 8 (got %d)", S);
-}
-
-// K-split factor: enough CTAs to fill the machine twice over, without slicing K thinner
-// than one loop step (4 chunks) per CTA.
-static int choose_cluster_k(const DecodeParams &p)
-{
-    const int sms = device_sm_count();
-    const int row_ctas = (p.n_blocks + DEC_WARPS - 1) / DEC_WARPS;   // CTAs if K is not split
-    int S = 1;
-    while (S < 8 && row_ctas * S < 2 * sms && p.chunks / (S * 2) >= 4) S *= 2;
-    return S;
+    const int sw = steps_needed((size_t)p.K, 8);
+#define BITNET_DECODE_CASE(SWV)                                                                   \
+    return breg ? launch_one<8, NT, SWV, true, IN_I8, DUAL>(p, flags, stream)                    \
+                : launch_one<8, NT, SWV, false, IN_I8, DUAL>(p, flags, stream)
+    if (sw <= 1) { BITNET_DECODE_CASE(1); }
+    if (sw <= 2) { BITNET_DECODE_CASE(2); }
+    if constexpr (!DUAL) {
+        if (sw <= 4) { BITNET_DECODE_CASE(4); }
+        if constexpr (NT == 1) {
+            if (sw <= 8) return launch_one<8, NT, 8, false, IN_I8, DUAL>(p, flags, stream);
+        }
+    }
+#undef BITNET_DECODE_CASE
+    return fail(BITNET_ERR_UNSUPPORTED_OPERATION, "decode kernel: K=%d is too wide for this token count", p.K);
 }
 
 bitnet_status_t launch_decode(const ForwardArgs &a, cudaStream_t stream)
 {
-    if (!decode_supports(a.M, a.K, a.N))
-        return fail(BITNET_ERR_UNSUPPORTED_OPERATION, "decode kernel needs 1 <= M <= 16 and K %% 64 == 0 (M=%zu K=%zu N=%zu)", a.M, a.K, a.N);
     const bool in_i8 = a.x_i8 != nullptr;
     const bool dual = a.wp2 != nullptr;
+    if (!decode_supports(a.M, a.K, a.N) || (dual && !shape_fits(a.M, a.K, true)))
+        return fail(BITNET_ERR_UNSUPPORTED_OPERATION,
+                    "decode kernel needs 1 <= M <= 16, K %% 64 == 0 and K <= 16384 (8192 for M > 8, 4096 for a gate/up pair) (M=%zu K=%zu N=%zu)",
+                    a.M, a.K, a.N);
     auto misaligned = [](const void *ptr, size_t al) { return (reinterpret_cast<uintptr_t>(ptr) & (al - 1)) != 0; };
     if (misaligned(a.wp, 16) || (dual && misaligned(a.wp2, 16)))
         return fail(BITNET_ERR_INVALID_CONFIG, "packed weights must be 16-byte aligned");
@@ -505,16 +713,31 @@ bitnet_status_t launch_decode(const ForwardArgs &a, cudaStream_t stream)
     p.M = (int)a.M; p.K = (int)a.K; p.N = (int)a.N; p.ldy = a.ldy ? a.ldy : a.N;
     p.chunks = (int)(a.K / 64);
     p.n_blocks = (int)((a.N + 15) / 16);
-    int S = a.cluster_k > 0 ? a.cluster_k : choose_cluster_k(p);
-    if (S > p.chunks) S = 1;
+    p.stages = a.stages;
+    p.amax_in = a.amax_in; p.n_amax_in = a.n_amax_in; p.amax_out = a.amax_out;
+    p.weights_first = (a.flags & BITNET_FLAG_PDL) ? 1 : 0;
     const int NT = a.M > 8 ? 2 : 1;
-    // the int8 activations of a CTA's K slice must fit in shared memory
-    while (S < 8 && (size_t)(((p.chunks + S - 1) / S + 3) / 4) * 4 * NT * 512 > 160 * 1024) S *= 2;
-    p.steps = ((p.chunks + S - 1) / S + 3) / 4;
-
-    if (in_i8) return launch_s<1, true, false>(S, p, a.flags, stream);
-    if (dual) return NT == 1 ? launch_s<1, false, true>(S, p, a.flags, stream) : launch_s<2, false, true>(S, p, a.flags, stream);
-    return NT == 1 ? launch_s<1, false, false>(S, p, a.flags, stream) : launch_s<2, false, false>(S, p, a.flags, stream);
+    // keep the activations in registers when a CTA streams enough blocks to repay the registers,
+    // and use the sixteen-warp kernel when it streams many (K up to 8192)
+    const int grid = decode_grid(a.N);
+    const int blocks_per_cta = (p.n_blocks + grid - 1) / grid;
+    const bool breg = NT == 1 && !dual && blocks_per_cta >= 4;
+    const bool wide = breg && blocks_per_cta >= 6 && steps_needed(a.K, 16) <= 2 && a.stages >= 0;
+    if (in_i8) return launch_sw<1, true, false>(wide, breg, p, a.flags, stream);
+    if (dual) return NT == 1 ? launch_sw<1, false, true>(false, false, p, a.flags, stream) : launch_sw<2, false, true>(false, false, p, a.flags, stream);
+    return NT == 1 ? launch_sw<1, false, false>(wide, breg, p, a.flags, stream) : launch_sw<2, false, false>(false, false, p, a.flags, stream);
 }
 
 }  // namespace bitnet
+
+// Flags raised by device-side bounded waits since the last call (bit 0: a decode-kernel
+// barrier wait ran out).  Synchronises the device.
+extern "C" bitnet_status_t bitnet_device_error_flags(uint32_t *flags_out)
+{
+    if (!flags_out) return bitnet::fail(BITNET_ERR_NULL_POINTER, "bitnet_device_error_flags: null output");
+    unsigned v = 0, zero = 0;
+    BITNET_CUDA(cudaMemcpyFromSymbol(&v, bitnet::g_decode_error_flags, sizeof(v)));
+    if (v) BITNET_CUDA(cudaMemcpyToSymbol(bitnet::g_decode_error_flags, &zero, sizeof(zero)));
+    *flags_out = v;
+    return BITNET_OK;
+}

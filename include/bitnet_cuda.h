@@ -81,7 +81,7 @@ typedef struct bitnet_forward_opts {
     float *a_scale_out_dev; /* optional [M]: absmax/127 per token (1 when the row is all zero) */
     int32_t *acc_out_dev;   /* optional [M,N]: the int32 accumulators */
     size_t ldy;             /* row stride of y (and acc_out) in elements; 0 means N */
-    int32_t cluster_k;      /* decode kernel: CTAs per cluster splitting K (0 = choose) */
+    int32_t stages;         /* decode kernel: depth of the shared-memory weight ring (0 = choose) */
     int32_t reserved;
 } bitnet_forward_opts;
 
@@ -97,6 +97,11 @@ typedef struct bitnet_device_info {
 } bitnet_device_info;
 
 bitnet_status_t bitnet_device_count(int32_t *count);                  /* lib.rs:56-64 device_count() */
+/* Device-side waits are bounded; one that runs out raises a flag instead of hanging.
+ * Returns and clears the flags (bit 0: a decode-kernel stage wait gave up, its outputs are
+ * incomplete).  Synchronises the device.  The reference has no counterpart: its kernel has
+ * no waits. */
+bitnet_status_t bitnet_device_error_flags(uint32_t *flags_out);
 bitnet_status_t bitnet_query_device(int32_t device_id, bitnet_device_info *out);
 
 /* ---- the hot path --------------------------------------------------------------- */
