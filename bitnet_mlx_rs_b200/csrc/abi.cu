@@ -181,7 +181,7 @@ extern "C" bitnet_status_t bitnet_bitlinear_workspace_size(size_t M, size_t K, s
     *bytes = 0;
     if (M == 0 || N == 0) return BITNET_OK;
     switch (resolve_path(path, M, K, N)) {
-        case BITNET_PATH_DECODE: *bytes = 0; return BITNET_OK;
+        case BITNET_PATH_DECODE: *bytes = decode_image_bytes(M, K, N, false); return BITNET_OK;
         case BITNET_PATH_PREFILL: *bytes = prefill_workspace_bytes(M, K, N); return BITNET_OK;
         case BITNET_PATH_GENERIC: *bytes = quant_workspace_bytes(M, K); return BITNET_OK;
     }
@@ -209,8 +209,14 @@ extern "C" bitnet_status_t bitnet_bitlinear_forward(const uint8_t *weights_dev, 
     cudaStream_t s = as_stream(stream);
 
     switch (path) {
-        case BITNET_PATH_DECODE:
+        case BITNET_PATH_DECODE: {
+            const size_t need = decode_image_bytes(M, K, N, false);
+            if (need && workspace_dev && workspace_bytes >= need && (reinterpret_cast<uintptr_t>(workspace_dev) & 255) == 0) {
+                a.image_ws = workspace_dev;     // without workspace the kernel quantises by itself
+                a.image_ws_bytes = workspace_bytes;
+            }
             return launch_decode(a, s);
+        }
         case BITNET_PATH_PREFILL: {
             if (!prefill_supports(M, K, N))
                 return fail(BITNET_ERR_UNSUPPORTED_OPERATION, "prefill kernel does not cover M=%zu K=%zu N=%zu", M, K, N);
@@ -247,6 +253,7 @@ extern "C" bitnet_status_t bitnet_ffn_workspace_size(size_t M, size_t hidden, si
     BITNET_TRY(bitnet_bitlinear_workspace_size(M, ffn, hidden, p2, &w2));
     size_t need = kAmaxBytes + (w1 > w2 ? w1 : w2);
     if (p1 != BITNET_PATH_DECODE || !decode_supports_dual(M, hidden, ffn)) need += 2 * ffn_pair_bytes(M, ffn);
+    else need += decode_image_bytes(M, hidden, ffn, true) + decode_image_bytes(M, ffn, hidden, false);
     *bytes = need;
     return BITNET_OK;
 }
@@ -284,6 +291,9 @@ extern "C" bitnet_status_t bitnet_ffn_forward(const uint8_t *w_gate_dev, float s
         a.x = x_dev; a.y = h_dev; a.M = M; a.K = hidden; a.N = ffn; a.ldy = ffn;
         a.flags = o.flags; a.stages = o.stages;
         a.amax_out = chain_amax ? amax : nullptr;
+        a.image_ws = ws + off; a.image_ws_bytes = decode_image_bytes(M, hidden, ffn, true);
+        if (a.image_ws_bytes == 0) a.image_ws = nullptr;
+        off += a.image_ws_bytes;
         BITNET_TRY(launch_decode(a, s));
     } else {
         float *gate = reinterpret_cast<float *>(ws + off);
@@ -300,6 +310,9 @@ extern "C" bitnet_status_t bitnet_ffn_forward(const uint8_t *w_gate_dev, float s
         a.wp = w_down_dev; a.w_scale = s_down; a.x = h_dev; a.y = y_dev;
         a.M = M; a.K = ffn; a.N = hidden; a.ldy = hidden; a.flags = o.flags; a.stages = o.stages;
         a.amax_in = amax; a.n_amax_in = decode_grid(ffn);
+        a.image_ws = ws + off; a.image_ws_bytes = decode_image_bytes(M, ffn, hidden, false);
+        if (a.image_ws_bytes == 0) a.image_ws = nullptr;
+        off += a.image_ws_bytes;
         return launch_decode(a, s);
     }
     bitnet_forward_opts po = {};

@@ -26,6 +26,8 @@
 // (bitnet-inference/src/engine/ternary_operations.rs:117-172, :283-338) on the packed
 // layout of BitPacked2BitPacker (bitnet-quant/src/quantization/packing.rs:352-394);
 // replaces w2a8_gemv_kernel (bitnet-cuda/src/kernels/w2a8_gemv.cu:100-182).
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace bitnet {
@@ -49,6 +51,9 @@ constexpr int DEC_MAX_CWARPS = 16;                     // consumer warps: 8 (two
 constexpr int DEC_MAX_STAGES = 8;
 constexpr int DEC_MAX_TOKENS = 16;
 constexpr unsigned DEC_WAIT_LIMIT = 1u << 22;          // polls before a wait gives up
+// A quantised-activation image starts with this header: int32 sums [16 warps][16 tokens], then
+// fp32 absmax/127 [16 tokens], padded; the fragment-ordered int8 data follows.
+constexpr unsigned DEC_IMG_HDR = 1152;
 
 // Set when a bounded wait ran out (bit 0) -- read with bitnet_device_error_flags().
 __device__ unsigned g_decode_error_flags;
@@ -75,6 +80,8 @@ struct DecodeParams {
     int n_amax_in;
     unsigned *amax_out;        // optional: this CTA's per-token absmax keys of what it wrote, [gridDim.x][16]
     int weights_first;         // 1: start the weight stream at once (the activations are not ready yet anyway)
+    const unsigned char *image;   // optional: activations already quantised by decode_quantize_kernel
+    unsigned image_bytes;
     unsigned bst_offset; // where the activation staging area starts in dynamic shared memory
     unsigned red_offset; // where the K-split sums start
 };
@@ -154,6 +161,21 @@ __device__ __forceinline__ int quantize_fast(float x, float scale)
     return (t == t) ? q : 0;                            // NaN quantises to 0, like the oracle
 }
 
+// The rare slow path (absmax so large or small that 127/absmax leaves the normal range) stays
+// out of line: these kernels run their prologue once per CTA, so its code size is paid in
+// instruction fetches.
+__device__ __noinline__ int quantize_one_slow(float x, float scale) { return quantize_one(x, scale); }
+
+__device__ __forceinline__ int quantize_any(float x, float scale, bool fast)
+{
+#ifdef BITNET_NO_SLOW_PATH
+    (void)fast;
+    return quantize_fast(x, scale);
+#else
+    return fast ? quantize_fast(x, scale) : quantize_one_slow(x, scale);
+#endif
+}
+
 // Dynamic shared memory: the weight ring [stages x stage_bytes], the activation staging
 // area (eight warp-private regions of SW*4*NT*512 bytes; with BREG and little shared memory
 // it overlaps the last ring stages, which the producer then fills only after every warp has
@@ -175,7 +197,7 @@ decode_kernel(const DecodeParams p)
 
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ __align__(8) unsigned long long s_full[DEC_MAX_STAGES], s_done[DEC_MAX_STAGES], s_empty[DEC_MAX_STAGES];
-    __shared__ __align__(8) unsigned long long s_bst_free, s_x_issued;
+    __shared__ __align__(8) unsigned long long s_bst_free, s_x_issued, s_img;
     __shared__ unsigned s_key[DEC_MAX_TOKENS], s_okey[DEC_MAX_TOKENS];
     __shared__ float s_ascale[DEC_MAX_TOKENS], s_qscale[DEC_MAX_TOKENS];
     __shared__ int s_sumq[DEC_MAX_CWARPS][DEC_MAX_TOKENS];
@@ -205,6 +227,7 @@ decode_kernel(const DecodeParams p)
         }
         mbar_init(&s_bst_free, DEC_CWARPS);
         mbar_init(&s_x_issued, DEC_CWARPS);
+        mbar_init(&s_img, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (tid < DEC_MAX_TOKENS) { s_key[tid] = 0; s_okey[tid] = 0; }
@@ -245,7 +268,7 @@ decode_kernel(const DecodeParams p)
     const int cw0 = (int)((long long)warp * p.chunks / DEC_CWARPS);
     const int cw1 = (int)((long long)(warp + 1) * p.chunks / DEC_CWARPS);
     const int Cw = cw1 - cw0;                              // chunks of this warp's K slice (<= 4*SW)
-    unsigned char *bst = s_bst + (size_t)warp * (SW * 4 * NT * 512);
+    unsigned char *bst = s_bst + DEC_IMG_HDR + (size_t)warp * (SW * 4 * NT * 512);
     const unsigned groups_per_token = (unsigned)Cw * 4;   // 16-wide k groups
     const unsigned n_groups = (unsigned)p.M * groups_per_token;
     const size_t k_base = (size_t)cw0 * 64;
@@ -266,134 +289,142 @@ decode_kernel(const DecodeParams p)
         }
     };
 
-    // ---- pass 1: per-token absmax, folded CTA-wide ------------------------------------------------
-    if constexpr (!IN_I8) {
-        if (p.amax_in) {
-            // the kernel that produced x left one partial maximum per CTA and token
-            if (single_batch) load_batch(0);               // overlap the fetch of x with the fold
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&s_x_issued);
-            const int total = p.n_amax_in * DEC_MAX_TOKENS;
-            unsigned key = 0;
-            for (int i = tid; i < total; i += DEC_CWARPS * 32) {   // 256 threads, stride keeps the token fixed
-                key = max(key, __ldg(p.amax_in + i));
-            }
-            if (key) atomicMax(&s_key[tid & (DEC_MAX_TOKENS - 1)], key);
-        } else {
-            unsigned cur_m = 0, cur_key = 0;   // running maximum of the token this lane is in
-            for (unsigned base = 0; base < n_groups; base += 32u * U) {
-                load_batch(base);
-                if (base == 0) {
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&s_x_issued);   // the weight stream may start
+    if (p.image) {
+        // ---- the activations were quantised once for all CTAs: fetch the ready-made image -------------
+        if (tid == 0) {
+            mbar_arrive_expect_tx(&s_img, p.image_bytes);
+            bulk_copy_g2s(s_bst, p.image, p.image_bytes, &s_img);
+        }
+        if (lane == 0) mbar_arrive(&s_x_issued);   // the weight stream may start
+        if (!mbar_wait(&s_img, 0)) return;
+        if (tid < DEC_CWARPS * DEC_MAX_TOKENS) (&s_sumq[0][0])[tid] = reinterpret_cast<const int *>(s_bst)[tid];
+        if (tid < DEC_MAX_TOKENS) s_ascale[tid] = reinterpret_cast<const float *>(s_bst + DEC_MAX_CWARPS * DEC_MAX_TOKENS * 4)[tid];
+        consumer_barrier<CW>();
+        PHASE(3);
+    } else {
+        // ---- pass 1: per-token absmax, folded CTA-wide ------------------------------------------------
+        if constexpr (!IN_I8) {
+            if (p.amax_in) {
+                // the kernel that produced x left one partial maximum per CTA and token
+                if (single_batch) load_batch(0);               // overlap the fetch of x with the fold
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&s_x_issued);
+                const int total = p.n_amax_in * DEC_MAX_TOKENS;
+                unsigned key = 0;
+                for (int i = tid; i < total; i += DEC_CWARPS * 32) {   // 256 threads, stride keeps the token fixed
+                    key = max(key, __ldg(p.amax_in + i));
                 }
-#pragma unroll
+                if (key) atomicMax(&s_key[tid & (DEC_MAX_TOKENS - 1)], key);
+            } else {
+                unsigned cur_m = 0, cur_key = 0;   // running maximum of the token this lane is in
+                for (unsigned base = 0; base < n_groups; base += 32u * U) {
+                    load_batch(base);
+                    if (base == 0) {
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&s_x_issued);   // the weight stream may start
+                    }
+    #pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        const unsigned gid = base + u * 32 + lane;
+                        if (gid < n_groups) {
+                            const unsigned m = gid / groups_per_token;
+                            unsigned key = 0;
+    #pragma unroll
+                            for (int v = 0; v < 4; ++v)
+                                key = max(max(key, abs_key(f[u][v].x)), max(abs_key(f[u][v].y), max(abs_key(f[u][v].z), abs_key(f[u][v].w))));
+                            if (m != cur_m) {
+                                if (cur_key) atomicMax(&s_key[cur_m], cur_key);
+                                cur_m = m;
+                                cur_key = 0;
+                            }
+                            cur_key = max(cur_key, key);
+                        }
+                    }
+                }
+                if (cur_key) atomicMax(&s_key[cur_m], cur_key);
+                if (n_groups == 0 && lane == 0) mbar_arrive(&s_x_issued);
+            }
+            consumer_barrier<CW>();
+            if (tid < p.M) {
+                const float absmax = __uint_as_float(s_key[tid]);
+                s_ascale[tid] = dequant_scale(absmax);
+                s_qscale[tid] = quant_scale(absmax);
+                if (p.a_scale_out && blockIdx.x == 0) p.a_scale_out[tid] = dequant_scale(absmax);
+            }
+            consumer_barrier<CW>();
+        } else {
+            if (tid < p.M) s_ascale[tid] = 1.0f;
+            if (lane == 0) mbar_arrive(&s_x_issued);
+        }
+        PHASE(3);
+
+        // ---- pass 2: quantise this warp's slice into fragment order ---------------------------------------
+        {
+            unsigned cur_m = 0;
+            int cur_sum = 0;
+            for (unsigned base = 0; base < n_groups; base += 32u * U) {
+                if constexpr (!IN_I8) {
+                    if (!single_batch) load_batch(base);       // second read: L1/L2 resident
+                }
+    #pragma unroll
                 for (int u = 0; u < U; ++u) {
                     const unsigned gid = base + u * 32 + lane;
                     if (gid < n_groups) {
                         const unsigned m = gid / groups_per_token;
-                        unsigned key = 0;
-#pragma unroll
-                        for (int v = 0; v < 4; ++v)
-                            key = max(max(key, abs_key(f[u][v].x)), max(abs_key(f[u][v].y), max(abs_key(f[u][v].z), abs_key(f[u][v].w))));
-                        if (m != cur_m) {
-                            if (cur_key) atomicMax(&s_key[cur_m], cur_key);
-                            cur_m = m;
-                            cur_key = 0;
-                        }
-                        cur_key = max(cur_key, key);
-                    }
-                }
-            }
-            if (cur_key) atomicMax(&s_key[cur_m], cur_key);
-            if (n_groups == 0 && lane == 0) mbar_arrive(&s_x_issued);
-        }
-        consumer_barrier<CW>();
-        if (tid < p.M) {
-            const float absmax = __uint_as_float(s_key[tid]);
-            s_ascale[tid] = dequant_scale(absmax);
-            s_qscale[tid] = quant_scale(absmax);
-            if (p.a_scale_out && blockIdx.x == 0) p.a_scale_out[tid] = dequant_scale(absmax);
-        }
-        consumer_barrier<CW>();
-    } else {
-        if (tid < p.M) s_ascale[tid] = 1.0f;
-        if (lane == 0) mbar_arrive(&s_x_issued);
-    }
-    PHASE(3);
-
-    // ---- pass 2: quantise this warp's slice into fragment order ---------------------------------------
-    {
-        unsigned cur_m = 0;
-        int cur_sum = 0;
-        for (unsigned base = 0; base < n_groups; base += 32u * U) {
-            if constexpr (!IN_I8) {
-                if (!single_batch) load_batch(base);       // second read: L1/L2 resident
-            }
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const unsigned gid = base + u * 32 + lane;
-                if (gid < n_groups) {
-                    const unsigned m = gid / groups_per_token;
-                    const unsigned l = gid - m * groups_per_token;
-                    int q[16];
-                    if constexpr (IN_I8) {
-                        const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(p.x_i8 + (size_t)m * p.K + k_base + (size_t)l * 16));
-#pragma unroll
-                        for (int e = 0; e < 16; ++e) q[e] = (int)(int8_t)((word_of(raw, e >> 2) >> (8 * (e & 3))) & 0xffu);
-                    } else {
-                        const float scale = s_qscale[m];
-                        // a huge absmax makes scale subnormal or zero; the fast path assumes neither
-                        const bool fast = scale >= 1e-30f && scale <= 1e30f;
-#pragma unroll
-                        for (int v = 0; v < 4; ++v) {
-                            if (fast) {
-                                q[4 * v + 0] = quantize_fast(f[u][v].x, scale);
-                                q[4 * v + 1] = quantize_fast(f[u][v].y, scale);
-                                q[4 * v + 2] = quantize_fast(f[u][v].z, scale);
-                                q[4 * v + 3] = quantize_fast(f[u][v].w, scale);
-                            } else {
-                                q[4 * v + 0] = quantize_one(f[u][v].x, scale);
-                                q[4 * v + 1] = quantize_one(f[u][v].y, scale);
-                                q[4 * v + 2] = quantize_one(f[u][v].z, scale);
-                                q[4 * v + 3] = quantize_one(f[u][v].w, scale);
+                        const unsigned l = gid - m * groups_per_token;
+                        int q[16];
+                        if constexpr (IN_I8) {
+                            const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(p.x_i8 + (size_t)m * p.K + k_base + (size_t)l * 16));
+    #pragma unroll
+                            for (int e = 0; e < 16; ++e) q[e] = (int)(int8_t)((word_of(raw, e >> 2) >> (8 * (e & 3))) & 0xffu);
+                        } else {
+                            const float scale = s_qscale[m];
+                            // a huge absmax makes scale subnormal or zero; the fast path assumes neither
+                            const bool fast = scale >= 1e-30f && scale <= 1e30f;
+    #pragma unroll
+                            for (int v = 0; v < 4; ++v) {
+                                q[4 * v + 0] = quantize_any(f[u][v].x, scale, fast);
+                                q[4 * v + 1] = quantize_any(f[u][v].y, scale, fast);
+                                q[4 * v + 2] = quantize_any(f[u][v].z, scale, fast);
+                                q[4 * v + 3] = quantize_any(f[u][v].w, scale, fast);
+                            }
+                            if (p.q_out && blockIdx.x == 0) {
+                                uint4 canon;
+                                canon.x = (q[0] & 0xff) | ((q[1] & 0xff) << 8) | ((q[2] & 0xff) << 16) | ((unsigned)(q[3] & 0xff) << 24);
+                                canon.y = (q[4] & 0xff) | ((q[5] & 0xff) << 8) | ((q[6] & 0xff) << 16) | ((unsigned)(q[7] & 0xff) << 24);
+                                canon.z = (q[8] & 0xff) | ((q[9] & 0xff) << 8) | ((q[10] & 0xff) << 16) | ((unsigned)(q[11] & 0xff) << 24);
+                                canon.w = (q[12] & 0xff) | ((q[13] & 0xff) << 8) | ((q[14] & 0xff) << 16) | ((unsigned)(q[15] & 0xff) << 24);
+                                *reinterpret_cast<uint4 *>(p.q_out + (size_t)m * p.K + k_base + (size_t)l * 16) = canon;
                             }
                         }
-                        if (p.q_out && blockIdx.x == 0) {
-                            uint4 canon;
-                            canon.x = (q[0] & 0xff) | ((q[1] & 0xff) << 8) | ((q[2] & 0xff) << 16) | ((unsigned)(q[3] & 0xff) << 24);
-                            canon.y = (q[4] & 0xff) | ((q[5] & 0xff) << 8) | ((q[6] & 0xff) << 16) | ((unsigned)(q[7] & 0xff) << 24);
-                            canon.z = (q[8] & 0xff) | ((q[9] & 0xff) << 8) | ((q[10] & 0xff) << 16) | ((unsigned)(q[11] & 0xff) << 24);
-                            canon.w = (q[12] & 0xff) | ((q[13] & 0xff) << 8) | ((q[14] & 0xff) << 16) | ((unsigned)(q[15] & 0xff) << 24);
-                            *reinterpret_cast<uint4 *>(p.q_out + (size_t)m * p.K + k_base + (size_t)l * 16) = canon;
+                        // word j holds k = j, j+4, j+8, j+12 of the group: the bytes that the mask
+                        // 0x03030303 << 2j selects from a packed weight word
+                        uint4 frag;
+                        frag.x = (q[0] & 0xff) | ((q[4] & 0xff) << 8) | ((q[8] & 0xff) << 16) | ((unsigned)(q[12] & 0xff) << 24);
+                        frag.y = (q[1] & 0xff) | ((q[5] & 0xff) << 8) | ((q[9] & 0xff) << 16) | ((unsigned)(q[13] & 0xff) << 24);
+                        frag.z = (q[2] & 0xff) | ((q[6] & 0xff) << 8) | ((q[10] & 0xff) << 16) | ((unsigned)(q[14] & 0xff) << 24);
+                        frag.w = (q[3] & 0xff) | ((q[7] & 0xff) << 8) | ((q[11] & 0xff) << 16) | ((unsigned)(q[15] & 0xff) << 24);
+                        int sum = 0;
+    #pragma unroll
+                        for (int e = 0; e < 16; ++e) sum += q[e];
+                        if (m != cur_m) {
+                            if (cur_sum) atomicAdd(&s_sumq[warp][cur_m], cur_sum);
+                            cur_m = m;
+                            cur_sum = 0;
                         }
+                        cur_sum += sum;
+                        // slice-relative chunk c = l/4 is read by lanes with tig = c%4 in step c/4; i = l%4 is
+                        // the 16-wide group inside the chunk; token m sits in tile m/8, fragment row m%8
+                        const unsigned c = l >> 2, i = l & 3;
+                        const unsigned step = c >> 2, ctig = c & 3;
+                        const unsigned off = (((step * 4 + i) * NT + (m >> 3)) * 32 + (m & 7) * 4 + ctig) * 16;
+                        *reinterpret_cast<uint4 *>(bst + off) = frag;
                     }
-                    // word j holds k = j, j+4, j+8, j+12 of the group: the bytes that the mask
-                    // 0x03030303 << 2j selects from a packed weight word
-                    uint4 frag;
-                    frag.x = (q[0] & 0xff) | ((q[4] & 0xff) << 8) | ((q[8] & 0xff) << 16) | ((unsigned)(q[12] & 0xff) << 24);
-                    frag.y = (q[1] & 0xff) | ((q[5] & 0xff) << 8) | ((q[9] & 0xff) << 16) | ((unsigned)(q[13] & 0xff) << 24);
-                    frag.z = (q[2] & 0xff) | ((q[6] & 0xff) << 8) | ((q[10] & 0xff) << 16) | ((unsigned)(q[14] & 0xff) << 24);
-                    frag.w = (q[3] & 0xff) | ((q[7] & 0xff) << 8) | ((q[11] & 0xff) << 16) | ((unsigned)(q[15] & 0xff) << 24);
-                    int sum = 0;
-#pragma unroll
-                    for (int e = 0; e < 16; ++e) sum += q[e];
-                    if (m != cur_m) {
-                        if (cur_sum) atomicAdd(&s_sumq[warp][cur_m], cur_sum);
-                        cur_m = m;
-                        cur_sum = 0;
-                    }
-                    cur_sum += sum;
-                    // slice-relative chunk c = l/4 is read by lanes with tig = c%4 in step c/4; i = l%4 is
-                    // the 16-wide group inside the chunk; token m sits in tile m/8, fragment row m%8
-                    const unsigned c = l >> 2, i = l & 3;
-                    const unsigned step = c >> 2, ctig = c & 3;
-                    const unsigned off = (((step * 4 + i) * NT + (m >> 3)) * 32 + (m & 7) * 4 + ctig) * 16;
-                    *reinterpret_cast<uint4 *>(bst + off) = frag;
                 }
             }
+            if (cur_sum) atomicAdd(&s_sumq[warp][cur_m], cur_sum);
         }
-        if (cur_sum) atomicAdd(&s_sumq[warp][cur_m], cur_sum);
+        PHASE(5);
     }
     __syncwarp();
 
@@ -410,6 +441,7 @@ decode_kernel(const DecodeParams p)
         __syncwarp();
         if (lane == 0) mbar_arrive(&s_bst_free);   // the staging area may be overwritten by weights
     }
+    PHASE(6);
     int sq[NT][2];
 #pragma unroll
     for (int t = 0; t < NT; ++t) {
@@ -436,9 +468,7 @@ decode_kernel(const DecodeParams p)
     for (int i = 0; i < nb; ++i) {
         const int s = i % NS;
         const unsigned parity = (unsigned)(i / NS) & 1u;
-        if (i == 8) PHASE(5);
         if (!mbar_wait(&s_full[s], parity)) return;
-        if (i == 8) PHASE(6);
         const int blk = b0 + i;
         const int row_a = blk * 16 + g, row_b = row_a + 8;
         const unsigned char *stage = s_w + (size_t)s * p.stage_stride;
@@ -487,7 +517,7 @@ decode_kernel(const DecodeParams p)
             }
         }
 
-        if (i == 8) PHASE(7);
+        if (i == 0) PHASE(7);
         // exact partial sums of sum_k (code-1)*q over this warp's K slice, left in this warp's slot
         int4 *red = reinterpret_cast<int4 *>(s_red) + (size_t)s * (DEC_CWARPS * NTD * 32);
 #pragma unroll
@@ -565,6 +595,106 @@ extern "C" int bitnet_debug_read_phases(unsigned long long *host)
 }
 #endif
 
+// Quantises x[M,K] once for every CTA of the decode kernel that follows: one CTA per token,
+// one read of the row (it stays in registers between the absmax fold and the rounding), and
+// the int8 values land in global memory as the exact shared-memory image the decode kernel's
+// warps want (header: per-warp-slice sums and absmax/127; then fragment-ordered bytes), so that
+// kernel fetches it with a single bulk copy.  cw/sw/nt describe the consuming instantiation.
+// Semantics: TernaryProcessor::quantize_activations (ternary_operations.rs:130-163).
+__global__ void __launch_bounds__(512) decode_quantize_kernel(const float *__restrict__ x, int M, int K, int cw, int sw, int nt,
+                                                              unsigned char *__restrict__ image,
+                                                              const unsigned *__restrict__ amax_in, int n_amax_in,
+                                                              int8_t *__restrict__ q_out, float *__restrict__ a_scale_out)
+{
+    __shared__ unsigned s_wkey[16];
+    __shared__ int s_sum[DEC_MAX_CWARPS];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the decode kernel may start fetching weights
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int m = blockIdx.x, tid = threadIdx.x;
+    const int n_groups = K / 16;
+    const float *row = x + (size_t)m * K;
+    if (tid < DEC_MAX_CWARPS) s_sum[tid] = 0;
+
+    float4 f[2][4];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const int G = tid + u * 512;
+        if (G < n_groups) {
+            const float4 *src = reinterpret_cast<const float4 *>(row + (size_t)G * 16);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) f[u][v] = __ldg(src + v);
+        }
+    }
+    unsigned key = 0;
+    if (amax_in) {
+        for (int i = tid; i < n_amax_in; i += 512) key = max(key, __ldg(amax_in + (size_t)i * DEC_MAX_TOKENS + m));
+    } else {
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+            if (tid + u * 512 < n_groups) {
+#pragma unroll
+                for (int v = 0; v < 4; ++v)
+                    key = max(max(key, abs_key(f[u][v].x)), max(abs_key(f[u][v].y), max(abs_key(f[u][v].z), abs_key(f[u][v].w))));
+            }
+    }
+    key = __reduce_max_sync(0xffffffffu, key);
+    if ((tid & 31) == 0) s_wkey[tid >> 5] = key;
+    __syncthreads();
+    key = 0;
+#pragma unroll
+    for (int w = 0; w < 16; ++w) key = max(key, s_wkey[w]);
+    const float absmax = __uint_as_float(key);
+    const float scale = quant_scale(absmax);
+    const bool fast = scale >= 1e-30f && scale <= 1e30f;
+    const int C = K / 64;
+    const unsigned region = (unsigned)sw * 4 * nt * 512;
+
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const int G = tid + u * 512;
+        if (G < n_groups) {
+            int q[16];
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                q[4 * v + 0] = fast ? quantize_fast(f[u][v].x, scale) : quantize_one(f[u][v].x, scale);
+                q[4 * v + 1] = fast ? quantize_fast(f[u][v].y, scale) : quantize_one(f[u][v].y, scale);
+                q[4 * v + 2] = fast ? quantize_fast(f[u][v].z, scale) : quantize_one(f[u][v].z, scale);
+                q[4 * v + 3] = fast ? quantize_fast(f[u][v].w, scale) : quantize_one(f[u][v].w, scale);
+            }
+            if (q_out) {
+                uint4 canon;
+                canon.x = (q[0] & 0xff) | ((q[1] & 0xff) << 8) | ((q[2] & 0xff) << 16) | ((unsigned)(q[3] & 0xff) << 24);
+                canon.y = (q[4] & 0xff) | ((q[5] & 0xff) << 8) | ((q[6] & 0xff) << 16) | ((unsigned)(q[7] & 0xff) << 24);
+                canon.z = (q[8] & 0xff) | ((q[9] & 0xff) << 8) | ((q[10] & 0xff) << 16) | ((unsigned)(q[11] & 0xff) << 24);
+                canon.w = (q[12] & 0xff) | ((q[13] & 0xff) << 8) | ((q[14] & 0xff) << 16) | ((unsigned)(q[15] & 0xff) << 24);
+                *reinterpret_cast<uint4 *>(q_out + (size_t)m * K + (size_t)G * 16) = canon;
+            }
+            uint4 frag;
+            frag.x = (q[0] & 0xff) | ((q[4] & 0xff) << 8) | ((q[8] & 0xff) << 16) | ((unsigned)(q[12] & 0xff) << 24);
+            frag.y = (q[1] & 0xff) | ((q[5] & 0xff) << 8) | ((q[9] & 0xff) << 16) | ((unsigned)(q[13] & 0xff) << 24);
+            frag.z = (q[2] & 0xff) | ((q[6] & 0xff) << 8) | ((q[10] & 0xff) << 16) | ((unsigned)(q[14] & 0xff) << 24);
+            frag.w = (q[3] & 0xff) | ((q[7] & 0xff) << 8) | ((q[11] & 0xff) << 16) | ((unsigned)(q[15] & 0xff) << 24);
+            int sum = 0;
+#pragma unroll
+            for (int e = 0; e < 16; ++e) sum += q[e];
+            // which consumer warp owns this chunk, and where in its region the group goes
+            const int chunk = G >> 2, i = G & 3;
+            const int w = (int)((((long long)chunk + 1) * cw - 1) / C);
+            const int c_rel = chunk - (int)((long long)w * C / cw);
+            const unsigned step = (unsigned)c_rel >> 2, ctig = (unsigned)c_rel & 3;
+            const unsigned off = DEC_IMG_HDR + (unsigned)w * region + (((step * 4 + i) * nt + (m >> 3)) * 32 + (m & 7) * 4 + ctig) * 16;
+            *reinterpret_cast<uint4 *>(image + off) = frag;
+            if (sum) atomicAdd(&s_sum[w], sum);
+        }
+    }
+    __syncthreads();
+    if (tid < cw) reinterpret_cast<int *>(image)[tid * DEC_MAX_TOKENS + m] = s_sum[tid];
+    if (tid == 0) {
+        reinterpret_cast<float *>(image + DEC_MAX_CWARPS * DEC_MAX_TOKENS * 4)[m] = dequant_scale(absmax);
+        if (a_scale_out) a_scale_out[m] = dequant_scale(absmax);
+    }
+}
+
 // ---- launcher -----------------------------------------------------------------------------------------
 
 static int steps_needed(size_t K, int cw) { return (int)(((K / 64 + cw - 1) / cw + 3) / 4); }
@@ -601,7 +731,8 @@ static bitnet_status_t launch_one(DecodeParams p, uint32_t flags, cudaStream_t s
     const unsigned real_stage = NW * 16 * row_bytes;
     p.stage_bytes = real_stage;
     p.stage_stride = real_stage + 128;
-    const size_t bst_bytes = (size_t)CW * SW * 4 * NT * 512;
+    const size_t bst_bytes = DEC_IMG_HDR + (size_t)CW * SW * 4 * NT * 512;   // image header + fragment data
+    if (p.image) p.image_bytes = (unsigned)bst_bytes;
     const size_t red_per_stage = (size_t)CW * NW * NT * 512;   // one slot of partial sums per consumer warp
     const size_t budget = 208 * 1024;
 
@@ -641,7 +772,7 @@ static bitnet_status_t launch_one(DecodeParams p, uint32_t flags, cudaStream_t s
     p.red_offset = (unsigned)(smem - (size_t)stages * red_per_stage);
 
     static size_t smem_set = 0;   // per instantiation; one launching thread per process
-    if (smem > 48 * 1024 && smem > smem_set) {
+    if (smem > 40 * 1024 && smem > smem_set) {   // static shared memory counts against the default 48 KB too
         BITNET_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         smem_set = smem;
     }
@@ -664,31 +795,72 @@ static bitnet_status_t launch_one(DecodeParams p, uint32_t flags, cudaStream_t s
     return BITNET_OK;
 }
 
-template <int NT, bool IN_I8, bool DUAL>
-static bitnet_status_t launch_sw(bool wide, bool breg, const DecodeParams &p, uint32_t flags, cudaStream_t stream)
+struct DecodePlan {
+    int cw, sw, nt;      // consumer warps, steps per warp (template value), token tiles
+    bool breg, wide;
+};
+
+static int round_sw(int sw) { return sw <= 1 ? 1 : (sw <= 2 ? 2 : (sw <= 4 ? 4 : 8)); }
+
+static DecodePlan decode_plan(size_t M, size_t K, size_t N, bool dual)
 {
-    if (wide) {
+    DecodePlan pl;
+    pl.nt = M > 8 ? 2 : 1;
+    const int n_blocks = (int)((N + 15) / 16);
+    const int grid = decode_grid(N);
+    const int blocks_per_cta = (n_blocks + grid - 1) / grid;
+    // keep the activations in registers when a CTA streams enough blocks to repay the registers,
+    // and use the sixteen-warp kernel when it streams many (K up to 8192)
+    pl.breg = pl.nt == 1 && !dual && blocks_per_cta >= 4;
+    pl.wide = pl.breg && blocks_per_cta >= 6 && steps_needed(K, 16) <= 2;
+    pl.cw = pl.wide ? 16 : 8;
+    pl.sw = round_sw(steps_needed(K, pl.cw));
+    return pl;
+}
+
+template <int NT, bool IN_I8, bool DUAL>
+static bitnet_status_t launch_sw(const DecodePlan &pl, const DecodeParams &p, uint32_t flags, cudaStream_t stream)
+{
+    if (pl.wide) {
         // sixteen consumer warps, activations in registers: one CTA per SM streaming many blocks
         if constexpr (NT == 1 && !DUAL) {
-            const int sw = steps_needed((size_t)p.K, 16);
-            if (sw <= 1) return launch_one<16, 1, 1, true, IN_I8, false>(p, flags, stream);
-            if (sw <= 2) return launch_one<16, 1, 2, true, IN_I8, false>(p, flags, stream);
+            if (pl.sw == 1) return launch_one<16, 1, 1, true, IN_I8, false>(p, flags, stream);
+            if (pl.sw == 2) return launch_one<16, 1, 2, true, IN_I8, false>(p, flags, stream);
         }
     }
-    const int sw = steps_needed((size_t)p.K, 8);
 #define BITNET_DECODE_CASE(SWV)                                                                   \
-    return breg ? launch_one<8, NT, SWV, true, IN_I8, DUAL>(p, flags, stream)                    \
-                : launch_one<8, NT, SWV, false, IN_I8, DUAL>(p, flags, stream)
-    if (sw <= 1) { BITNET_DECODE_CASE(1); }
-    if (sw <= 2) { BITNET_DECODE_CASE(2); }
+    return pl.breg ? launch_one<8, NT, SWV, true, IN_I8, DUAL>(p, flags, stream)                 \
+                   : launch_one<8, NT, SWV, false, IN_I8, DUAL>(p, flags, stream)
+    if (pl.sw == 1) { BITNET_DECODE_CASE(1); }
+    if (pl.sw == 2) { BITNET_DECODE_CASE(2); }
     if constexpr (!DUAL) {
-        if (sw <= 4) { BITNET_DECODE_CASE(4); }
+        if (pl.sw == 4) { BITNET_DECODE_CASE(4); }
         if constexpr (NT == 1) {
-            if (sw <= 8) return launch_one<8, NT, 8, false, IN_I8, DUAL>(p, flags, stream);
+            if (pl.sw == 8) return launch_one<8, NT, 8, false, IN_I8, DUAL>(p, flags, stream);
         }
     }
 #undef BITNET_DECODE_CASE
     return fail(BITNET_ERR_UNSUPPORTED_OPERATION, "decode kernel: K=%d is too wide for this token count", p.K);
+}
+
+// Token count from which the activations are quantised by their own small launch instead of
+// by every CTA of the decode kernel (whose redundant quantiser work grows with M).
+static size_t split_min_tokens()
+{
+    static long v = -1;
+    if (v < 0) {
+        const char *e = getenv("BITNET_DECODE_SPLIT_MIN_M");
+        v = e ? atol(e) : 2;
+        if (v < 1) v = 1;
+    }
+    return (size_t)v;
+}
+
+size_t decode_image_bytes(size_t M, size_t K, size_t N, bool dual)
+{
+    if (M < split_min_tokens()) return 0;
+    const DecodePlan pl = decode_plan(M, K, N, dual);
+    return align_up(DEC_IMG_HDR + (size_t)pl.cw * pl.sw * 4 * pl.nt * 512, 256);
 }
 
 bitnet_status_t launch_decode(const ForwardArgs &a, cudaStream_t stream)
@@ -716,16 +888,38 @@ bitnet_status_t launch_decode(const ForwardArgs &a, cudaStream_t stream)
     p.stages = a.stages;
     p.amax_in = a.amax_in; p.n_amax_in = a.n_amax_in; p.amax_out = a.amax_out;
     p.weights_first = (a.flags & BITNET_FLAG_PDL) ? 1 : 0;
-    const int NT = a.M > 8 ? 2 : 1;
-    // keep the activations in registers when a CTA streams enough blocks to repay the registers,
-    // and use the sixteen-warp kernel when it streams many (K up to 8192)
-    const int grid = decode_grid(a.N);
-    const int blocks_per_cta = (p.n_blocks + grid - 1) / grid;
-    const bool breg = NT == 1 && !dual && blocks_per_cta >= 4;
-    const bool wide = breg && blocks_per_cta >= 6 && steps_needed(a.K, 16) <= 2 && a.stages >= 0;
-    if (in_i8) return launch_sw<1, true, false>(wide, breg, p, a.flags, stream);
-    if (dual) return NT == 1 ? launch_sw<1, false, true>(false, false, p, a.flags, stream) : launch_sw<2, false, true>(false, false, p, a.flags, stream);
-    return NT == 1 ? launch_sw<1, false, false>(wide, breg, p, a.flags, stream) : launch_sw<2, false, false>(false, false, p, a.flags, stream);
+    const DecodePlan pl = decode_plan(a.M, a.K, a.N, dual);
+
+    if (!in_i8 && a.image_ws && a.M >= split_min_tokens()) {
+        // quantise once, then let every CTA fetch the result
+        const size_t need = decode_image_bytes(a.M, a.K, a.N, dual);
+        if (a.image_ws_bytes < need || misaligned(a.image_ws, 16))
+            return fail(BITNET_ERR_WORKSPACE, "decode path needs %zu bytes of 16-byte aligned workspace", need);
+        cudaLaunchConfig_t cfg = {};
+        cudaLaunchAttribute attrs[1];
+        cfg.gridDim = dim3((unsigned)a.M);
+        cfg.blockDim = dim3(512);
+        cfg.stream = stream;
+        cfg.attrs = attrs;
+        if (a.flags & BITNET_FLAG_PDL) {
+            attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attrs[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.numAttrs = 1;
+        }
+        BITNET_CUDA(cudaLaunchKernelEx(&cfg, decode_quantize_kernel, a.x, (int)a.M, (int)a.K, pl.cw, pl.sw, pl.nt,
+                                       static_cast<unsigned char *>(a.image_ws), a.amax_in, a.n_amax_in, a.q_out,
+                                       a.a_scale_out));
+        p.image = static_cast<const unsigned char *>(a.image_ws);
+        p.q_out = nullptr; p.a_scale_out = nullptr; p.amax_in = nullptr;
+        p.weights_first = 1;   // the image does not exist before the quantiser ends: fetch weights meanwhile
+        // the decode kernel must be allowed to start while the quantiser runs
+        const uint32_t flags = a.flags | BITNET_FLAG_PDL;
+        if (dual) return pl.nt == 1 ? launch_sw<1, false, true>(pl, p, flags, stream) : launch_sw<2, false, true>(pl, p, flags, stream);
+        return pl.nt == 1 ? launch_sw<1, false, false>(pl, p, flags, stream) : launch_sw<2, false, false>(pl, p, flags, stream);
+    }
+    if (in_i8) return launch_sw<1, true, false>(pl, p, a.flags, stream);
+    if (dual) return pl.nt == 1 ? launch_sw<1, false, true>(pl, p, a.flags, stream) : launch_sw<2, false, true>(pl, p, a.flags, stream);
+    return pl.nt == 1 ? launch_sw<1, false, false>(pl, p, a.flags, stream) : launch_sw<2, false, false>(pl, p, a.flags, stream);
 }
 
 }  // namespace bitnet
