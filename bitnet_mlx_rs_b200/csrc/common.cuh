@@ -71,6 +71,7 @@ bitnet_status_t launch_gate_relu2(const float *up, const float *gate, float *h, 
 bool prefill_supports(size_t M, size_t K, size_t N);
 size_t prefill_workspace_bytes(size_t M, size_t K, size_t N);
 bitnet_status_t launch_prefill(const ForwardArgs &a, void *workspace, size_t workspace_bytes, cudaStream_t stream);
+bitnet_status_t prefill_take_error_flags(unsigned *flags);
 
 int device_sm_count();
 

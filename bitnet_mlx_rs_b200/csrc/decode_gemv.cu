@@ -925,13 +925,15 @@ bitnet_status_t launch_decode(const ForwardArgs &a, cudaStream_t stream)
 }  // namespace bitnet
 
 // Flags raised by device-side bounded waits since the last call (bit 0: a decode-kernel
-// barrier wait ran out).  Synchronises the device.
+// barrier wait ran out, bit 1: a GEMM-kernel wait).  Synchronises the device.
 extern "C" bitnet_status_t bitnet_device_error_flags(uint32_t *flags_out)
 {
     if (!flags_out) return bitnet::fail(BITNET_ERR_NULL_POINTER, "bitnet_device_error_flags: null output");
     unsigned v = 0, zero = 0;
     BITNET_CUDA(cudaMemcpyFromSymbol(&v, bitnet::g_decode_error_flags, sizeof(v)));
     if (v) BITNET_CUDA(cudaMemcpyToSymbol(bitnet::g_decode_error_flags, &zero, sizeof(zero)));
-    *flags_out = v;
+    unsigned pf = 0;
+    BITNET_TRY(bitnet::prefill_take_error_flags(&pf));
+    *flags_out = v | pf;
     return BITNET_OK;
 }

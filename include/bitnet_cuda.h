@@ -98,8 +98,8 @@ typedef struct bitnet_device_info {
 
 bitnet_status_t bitnet_device_count(int32_t *count);                  /* lib.rs:56-64 device_count() */
 /* Device-side waits are bounded; one that runs out raises a flag instead of hanging.
- * Returns and clears the flags (bit 0: a decode-kernel stage wait gave up, its outputs are
- * incomplete).  Synchronises the device.  The reference has no counterpart: its kernel has
+ * Returns and clears the flags (bit 0: a decode-kernel stage wait gave up, bit 1: a GEMM-kernel wait;
+ * the outputs of that launch are incomplete).  Synchronises the device.  The reference has no counterpart: its kernel has
  * no waits. */
 bitnet_status_t bitnet_device_error_flags(uint32_t *flags_out);
 bitnet_status_t bitnet_query_device(int32_t device_id, bitnet_device_info *out);

@@ -1,0 +1,74 @@
+"""Parity of the tensor-core (prefill) path with the CPU oracle, through the C ABI.
+int8 activations, scales and int32 accumulators bit-exact; fp32 outputs within 1e-5 relative."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from bitnet_mlx_rs_b200 import ops
+
+pytestmark = pytest.mark.gpu
+GOLDEN = Path(__file__).resolve().parent / "golden"
+RTOL = 1e-5
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def case(seed, M, K, N):
+    return oracle.gen_ternary_packed(seed, 1, N * K), oracle.gen_weight_scale(seed, 1, K), oracle.gen_activations(seed, 2, (M, K))
+
+
+@pytest.mark.parametrize("M,K,N", [(128, 128, 256), (256, 256, 128), (1, 128, 8), (130, 384, 700), (300, 1024, 513),
+                                   (17, 2560, 640), (512, 640, 2560)])
+def test_prefill_matches_oracle(M, K, N):
+    wp, ws, x = case(500 + M, M, K, N)
+    ref = oracle.bitlinear_forward(wp, ws, x, N)
+    y, dbg = ops.bitlinear_forward(dev(wp), ws, dev(x), N, debug=True, path="prefill")
+    assert ops.device_error_flags() == 0
+    assert np.array_equal(dbg["q"].cpu().numpy(), ref["q"])
+    assert np.array_equal(dbg["a_scale"].cpu().numpy(), ref["a_scale"])
+    assert np.array_equal(dbg["acc"].cpu().numpy(), ref["acc"])
+    np.testing.assert_allclose(y.cpu().numpy(), ref["y"], rtol=RTOL, atol=0)
+    assert np.array_equal(y.cpu().numpy(), ref["y"])
+
+
+def test_prefill_golden_fixture():
+    z = np.load(GOLDEN / "prefill_m256_k256_n128.npz")
+    y, dbg = ops.bitlinear_forward(dev(z["wp"]), float(z["w_scale"]), dev(z["x"]), int(z["N"]), debug=True, path="prefill")
+    assert np.array_equal(dbg["acc"].cpu().numpy(), z["acc"])
+    np.testing.assert_allclose(y.cpu().numpy(), z["y"], rtol=RTOL, atol=0)
+
+
+def test_auto_dispatch_uses_tensor_cores_for_many_tokens():
+    M, K, N = 200, 256, 96
+    wp, ws, x = case(9, M, K, N)
+    y = ops.bitlinear_forward(dev(wp), ws, dev(x), N)
+    assert np.array_equal(y.cpu().numpy(), oracle.bitlinear_forward(wp, ws, x, N)["y"])
+
+
+@pytest.mark.parametrize("K,N", [(2560, 2560), (2560, 640), (2560, 6912), (6912, 2560)])
+def test_prefill_layer_shapes_at_2048_tokens(K, N):
+    # one projection of the 2B decoder layer at M = 2048: the oracle checks sampled token rows against
+    # sampled feature rows exactly; the decode kernel (already checked against the oracle) cross-checks
+    # a block of 16 tokens on all features; a checksum identity covers everything else
+    M = 2048
+    wp, ws, x = case(600 + N // 64 + K // 64, M, K, N)
+    dwp, dx = dev(wp), dev(x)
+    y, dbg = ops.bitlinear_forward(dwp, ws, dx, N, debug=True, path="prefill")
+    assert ops.device_error_flags() == 0
+    rows = [0, 1, 127, 128, 1000, 2047]
+    for f0 in (0, N // 2 - 32, N - 64):
+        sl = wp[f0 * K // 4:(f0 + 64) * K // 4]
+        ref = oracle.bitlinear_forward(sl, ws, x[rows], 64)
+        assert np.array_equal(dbg["acc"][rows][:, f0:f0 + 64].cpu().numpy(), ref["acc"])
+        np.testing.assert_allclose(y[rows][:, f0:f0 + 64].cpu().numpy(), ref["y"], rtol=RTOL, atol=0)
+    y16, d16 = ops.bitlinear_forward(dwp, ws, dx[512:528].contiguous(), N, debug=True, path="decode")
+    assert torch.equal(d16["acc"], dbg["acc"][512:528])
+    assert torch.equal(y16, y[512:528])
+    w = ops.unpack_ternary(dwp, N * K).reshape(N, K)
+    colsum = w.sum(dim=0, dtype=torch.float64)
+    assert torch.equal(dbg["acc"].sum(dim=1, dtype=torch.float64), dbg["q"].to(torch.float64) @ colsum)
