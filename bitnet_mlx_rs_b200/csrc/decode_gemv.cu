@@ -116,6 +116,9 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned pari
             : "r"(addr), "r"(parity)
             : "memory");
         if (done) return true;
+#ifndef BITNET_NO_BACKOFF
+        __nanosleep(n < 16 ? 32 : 128);   // a waiting warp must not take issue slots from the working ones
+#endif
     }
     atomicOr(&g_decode_error_flags, 1u);
     return false;

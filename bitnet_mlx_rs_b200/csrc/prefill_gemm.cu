@@ -6,13 +6,14 @@
 //   2. prefill_gemm_kernel: persistent CTAs, one 128-token x 256-feature tile at a time.
 //        warp 0      TMA producer: the int8 activation tile (128 x 128 bytes, 128-byte swizzle) and
 //                    the PACKED weight tile (256 rows x 32 bytes) per 128-wide k slice
-//        warps 2-5   expand packed weights to int8 codes {0,1,2} in shared memory, straight into
+//        warps 2-9   expand packed weights to int8 codes {0,1,2} in shared memory, straight into
 //                    the swizzled K-major layout the tensor core reads: (w >> 2j) & 0x03030303
 //                    yields the four bytes k = j, j+4, j+8, j+12 of a group, i.e. word j of the
 //                    transposed group order the activations were stored in
+//                    (two groups of four warps take the k slices in turn)
 //        warp 1      issues tcgen05.mma kind::i8 (M=128, N=256, K=32; s8 x u8 -> s32) with the
 //                    accumulator in tensor memory; two accumulators alternate between tiles
-//        warps 6-9   epilogue: tcgen05.ld the accumulator, subtract the row sum
+//        warps 10-13 epilogue: tcgen05.ld the accumulator, subtract the row sum
 //                    (sum_k (code-1) q = sum_k code q - sum_k q), scale, store y
 //      Every barrier wait is bounded; a wait that runs out raises an error flag and the CTA
 //      drains and frees its tensor memory.
@@ -32,18 +33,35 @@ namespace bitnet {
 __device__ unsigned g_prefill_error_flags;
 
 constexpr int PF_BM = 128, PF_BN = 256, PF_BK = 128;   // tile: tokens x features x k (bytes of int8)
-constexpr int PF_STAGES = 3;
+constexpr int PF_STAGES = 4;                       // TMA ring: activations + packed weights (latency hiding)
+constexpr int PF_BSTAGES = 3;                      // ring of expanded weight tiles
 constexpr int PF_A_BYTES = PF_BM * PF_BK;          // 16 KB
 constexpr int PF_WP_BYTES = PF_BN * PF_BK / 4;     // 8 KB packed
 constexpr int PF_B_BYTES = PF_BN * PF_BK;          // 32 KB expanded
-constexpr int PF_STAGE_BYTES = PF_A_BYTES + PF_WP_BYTES + PF_B_BYTES;
-constexpr int PF_THREADS = 320;                    // 10 warps
+constexpr int PF_STAGE_BYTES = PF_A_BYTES + PF_WP_BYTES;
+constexpr int PF_EXP_WARPS = 8;                    // warps that expand packed weights
+constexpr int PF_GROUPS = 2;                       // expander groups working on alternate k slices
+constexpr int PF_THREADS = (2 + PF_EXP_WARPS + 4) * 32;   // producer, MMA, expanders, epilogue
 constexpr unsigned PF_WAIT_LIMIT = 1u << 22;
-constexpr size_t PF_SMEM = (size_t)PF_STAGES * PF_STAGE_BYTES + 1024;   // + alignment slack
+constexpr int PF_EPI_BYTES = 4 * 32 * 32 * 4;       // per epilogue warp a 32x32 fp32 transpose buffer
+constexpr size_t PF_SMEM = (size_t)PF_STAGES * PF_STAGE_BYTES + (size_t)PF_BSTAGES * PF_B_BYTES + PF_EPI_BYTES + 1024;   // + alignment slack
 
 // ---- quantiser for the GEMM path ----------------------------------------------------------------
 
-// One CTA per token row.  q_perm[m, 16G + 4j + i] = q[m, 16G + 4i + j]; rowsum[m] = sum_k q[m,k].
+// Same exact rounding as common.cuh's quantize_one for |x*scale| <= 2^22 (trunc(|t| + c) with c the
+// largest float below 0.5 equals roundf(|t|) for every float; adding 2^23 toward zero leaves the
+// integer in the low mantissa bits); NaN quantises to 0.
+__device__ __forceinline__ int pf_quantize_fast(float x, float scale)
+{
+    const float t = __fmul_rn(x, scale);
+    const float a = fminf(__fadd_rn(fabsf(t), 0.49999997f), 127.0f);
+    const int mag = __float_as_int(__fadd_rz(a, 8388608.0f)) & 0xff;
+    const int neg = __float_as_int(t) >> 31;
+    return (t == t) ? (mag ^ neg) - neg : 0;
+}
+
+// One CTA per token row, one read of the row when it fits the registers (K <= 8192).
+// q_perm[m, 16G + 4j + i] = q[m, 16G + 4i + j]; rowsum[m] = sum_k q[m,k].
 // Semantics: TernaryProcessor::quantize_activations (ternary_operations.rs:130-163).
 __global__ void __launch_bounds__(256) quantize_rows_perm_kernel(const float *__restrict__ x, size_t K,
                                                                  int8_t *__restrict__ q_perm, float *__restrict__ a_scale,
@@ -56,14 +74,35 @@ __global__ void __launch_bounds__(256) quantize_rows_perm_kernel(const float *__
     const float *row = x + m * K;
     const int tid = threadIdx.x;
     const size_t n_groups = K / 16;
+    const bool resident = n_groups <= 512;   // two 16-wide groups per thread stay in registers
 
+    float4 f[2][4];
     unsigned key = 0;
-    for (size_t G = tid; G < n_groups; G += 256) {
-        const float4 *src = reinterpret_cast<const float4 *>(row + G * 16);
+    if (resident) {
 #pragma unroll
-        for (int v = 0; v < 4; ++v) {
-            const float4 f = __ldg(src + v);
-            key = max(max(key, abs_key(f.x)), max(abs_key(f.y), max(abs_key(f.z), abs_key(f.w))));
+        for (int u = 0; u < 2; ++u) {
+            const size_t G = tid + u * 256;
+            if (G < n_groups) {
+                const float4 *src = reinterpret_cast<const float4 *>(row + G * 16);
+#pragma unroll
+                for (int v = 0; v < 4; ++v) f[u][v] = __ldg(src + v);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+            if ((size_t)(tid + u * 256) < n_groups) {
+#pragma unroll
+                for (int v = 0; v < 4; ++v)
+                    key = max(max(key, abs_key(f[u][v].x)), max(abs_key(f[u][v].y), max(abs_key(f[u][v].z), abs_key(f[u][v].w))));
+            }
+    } else {
+        for (size_t G = tid; G < n_groups; G += 256) {
+            const float4 *src = reinterpret_cast<const float4 *>(row + G * 16);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                const float4 g4 = __ldg(src + v);
+                key = max(max(key, abs_key(g4.x)), max(abs_key(g4.y), max(abs_key(g4.z), abs_key(g4.w))));
+            }
         }
     }
     key = __reduce_max_sync(0xffffffffu, key);
@@ -74,18 +113,37 @@ __global__ void __launch_bounds__(256) quantize_rows_perm_kernel(const float *__
     for (int w = 0; w < 8; ++w) key = max(key, s_key[w]);
     const float absmax = __uint_as_float(key);
     const float scale = quant_scale(absmax);
+    // a huge or tiny absmax makes the scale leave the normal range; the fast rounding assumes it has not
+    const bool fast = scale >= 1e-30f && scale <= 1e30f;
 
     int sum = 0;
-    for (size_t G = tid; G < n_groups; G += 256) {
-        const float4 *src = reinterpret_cast<const float4 *>(row + G * 16);
+    const size_t rounds = resident ? 2 : (n_groups + 255) / 256;
+    for (size_t u = 0; u < rounds; ++u) {
+        const size_t G = tid + u * 256;
+        if (G >= n_groups) break;
+        float4 g4[4];
+        if (resident) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) g4[v] = u == 0 ? f[0][v] : f[1][v];
+        } else {
+            const float4 *src = reinterpret_cast<const float4 *>(row + G * 16);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) g4[v] = __ldg(src + v);
+        }
         int q[16];
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
-            const float4 f = __ldg(src + v);
-            q[4 * v + 0] = quantize_one(f.x, scale);
-            q[4 * v + 1] = quantize_one(f.y, scale);
-            q[4 * v + 2] = quantize_one(f.z, scale);
-            q[4 * v + 3] = quantize_one(f.w, scale);
+            if (fast) {
+                q[4 * v + 0] = pf_quantize_fast(g4[v].x, scale);
+                q[4 * v + 1] = pf_quantize_fast(g4[v].y, scale);
+                q[4 * v + 2] = pf_quantize_fast(g4[v].z, scale);
+                q[4 * v + 3] = pf_quantize_fast(g4[v].w, scale);
+            } else {
+                q[4 * v + 0] = quantize_one(g4[v].x, scale);
+                q[4 * v + 1] = quantize_one(g4[v].y, scale);
+                q[4 * v + 2] = quantize_one(g4[v].z, scale);
+                q[4 * v + 3] = quantize_one(g4[v].w, scale);
+            }
         }
 #pragma unroll
         for (int e = 0; e < 16; ++e) sum += q[e];
@@ -117,6 +175,21 @@ __global__ void __launch_bounds__(256) quantize_rows_perm_kernel(const float *__
     }
 }
 
+#ifdef BITNET_PHASE_TIMERS
+__device__ unsigned long long g_pf_ts[8][128];   // [role/point][iteration] of CTA 0
+#define PF_TS(point, it)                                                         \
+    do {                                                                         \
+        if (blockIdx.x == 0 && (it) < 128) {                                     \
+            unsigned long long t_;                                               \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));               \
+            g_pf_ts[point][it] = t_;                                             \
+        }                                                                        \
+    } while (0)
+extern "C" int bitnet_debug_read_pf(unsigned long long *host) { return (int)cudaMemcpyFromSymbol(host, g_pf_ts, sizeof(g_pf_ts)); }
+#else
+#define PF_TS(point, it) do { } while (0)
+#endif
+
 // ---- PTX wrappers -------------------------------------------------------------------------------
 
 __device__ __forceinline__ unsigned pf_smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -147,9 +220,20 @@ __device__ __forceinline__ bool pf_mbar_wait(unsigned long long *bar, unsigned p
             : "r"(addr), "r"(parity)
             : "memory");
         if (done) return true;
+#ifndef BITNET_NO_BACKOFF
+        __nanosleep(n < 16 ? 32 : 128);   // a waiting warp must not take issue slots from the working ones
+#endif
     }
     atomicOr(&g_prefill_error_flags, 2u);
     return false;
+}
+// One lane polls for the whole warp (keeps barrier polling off the shared-memory pipe).
+__device__ __forceinline__ bool pf_warp_wait(unsigned long long *bar, unsigned parity)
+{
+    unsigned ok = 1;
+    if ((threadIdx.x & 31) == 0) ok = pf_mbar_wait(bar, parity) ? 1u : 0u;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    return ok != 0;
 }
 __device__ __forceinline__ void pf_tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, unsigned long long *bar)
 {
@@ -210,21 +294,26 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
 prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const PrefillParams p)
 {
     extern __shared__ unsigned char pf_smem_raw[];
-    __shared__ __align__(8) unsigned long long s_full_tma[PF_STAGES], s_full_b[PF_STAGES], s_empty[PF_STAGES];
+    __shared__ __align__(8) unsigned long long s_full_tma[PF_STAGES], s_empty[PF_STAGES];
+    __shared__ __align__(8) unsigned long long s_full_b[PF_BSTAGES], s_empty_b[PF_BSTAGES];
     __shared__ __align__(8) unsigned long long s_acc_full[2], s_acc_empty[2];
     __shared__ unsigned s_tmem_base;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(pf_smem_raw) + 1023) & ~uintptr_t(1023));
-    auto stage_a = [&](int s) { return smem + (size_t)s * PF_STAGE_BYTES; };
-    auto stage_b = [&](int s) { return smem + (size_t)s * PF_STAGE_BYTES + PF_A_BYTES; };
-    auto stage_wp = [&](int s) { return smem + (size_t)s * PF_STAGE_BYTES + PF_A_BYTES + PF_B_BYTES; };
+    // expanded weight tiles first (1024-byte aligned for the swizzle), then the TMA ring
+    auto stage_b = [&](int sb) { return smem + (size_t)sb * PF_B_BYTES; };
+    auto stage_a = [&](int s) { return smem + (size_t)PF_BSTAGES * PF_B_BYTES + (size_t)s * PF_STAGE_BYTES; };
+    auto stage_wp = [&](int s) { return smem + (size_t)PF_BSTAGES * PF_B_BYTES + (size_t)s * PF_STAGE_BYTES + PF_A_BYTES; };
 
     if (tid == 0) {
         for (int s = 0; s < PF_STAGES; ++s) {
             pf_mbar_init(&s_full_tma[s], 1);
-            pf_mbar_init(&s_full_b[s], 4);
             pf_mbar_init(&s_empty[s], 1);
+        }
+        for (int sb = 0; sb < PF_BSTAGES; ++sb) {
+            pf_mbar_init(&s_full_b[sb], PF_EXP_WARPS / PF_GROUPS);
+            pf_mbar_init(&s_empty_b[sb], 1);
         }
         for (int b = 0; b < 2; ++b) {
             pf_mbar_init(&s_acc_full[b], 1);
@@ -253,7 +342,9 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 for (int kt = 0; kt < p.k_tiles; ++kt, ++it) {
                     const int s = it % PF_STAGES;
                     const unsigned ph = (unsigned)(it / PF_STAGES) & 1u;
+                    PF_TS(0, it);
                     if (!pf_mbar_wait(&s_empty[s], ph ^ 1u)) { ok = false; break; }
+                    PF_TS(1, it);
                     pf_mbar_expect_tx(&s_full_tma[s], PF_A_BYTES + PF_WP_BYTES);
                     pf_tma_load_2d(stage_a(s), &map_a, kt * PF_BK, m_tile * PF_BM, &s_full_tma[s]);
                     pf_tma_load_2d(stage_wp(s), &map_w, kt * (PF_BK / 4), n_tile * PF_BN, &s_full_tma[s]);
@@ -274,45 +365,58 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 for (int kt = 0; kt < p.k_tiles; ++kt, ++it) {
                     const int s = it % PF_STAGES;
                     const unsigned ph = (unsigned)(it / PF_STAGES) & 1u;
-                    if (!pf_mbar_wait(&s_full_tma[s], ph) || !pf_mbar_wait(&s_full_b[s], ph)) { ok = false; break; }
+                    const int sb = it % PF_BSTAGES;
+                    const unsigned phb = (unsigned)(it / PF_BSTAGES) & 1u;
+                    if (!pf_mbar_wait(&s_full_b[sb], phb)) { ok = false; break; }   // implies the TMA data of the slice landed
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const unsigned long long a_desc = pf_smem_desc(pf_smem_u32(stage_a(s)));
-                    const unsigned long long b_desc = pf_smem_desc(pf_smem_u32(stage_b(s)));
+                    const unsigned long long b_desc = pf_smem_desc(pf_smem_u32(stage_b(sb)));
 #pragma unroll
                     for (int ks = 0; ks < PF_BK / 32; ++ks)   // 32 bytes of k per instruction: +2 in 16-byte units
                         pf_mma_i8(tmem_d, a_desc + 2ull * ks, b_desc + 2ull * ks, PF_IDESC, (kt | ks) != 0 ? 1u : 0u);
-                    pf_commit(&s_empty[s]);   // the stage is free once these MMAs have read it
+                    pf_commit(&s_empty[s]);     // both rings' slots are free once these MMAs have read them
+                    pf_commit(&s_empty_b[sb]);
+                    (void)ph;
                 }
                 if (ok) pf_commit(&s_acc_full[buf]);
             }
         }
-    } else if (warp < 6) {
-        // ===================== weight expanders (128 threads) =====================
-        const int e = tid - 64;
+    } else if (warp < 2 + PF_EXP_WARPS) {
+        // ===================== weight expanders: PF_GROUPS groups take the k slices in turn =====================
+        // One group's wait -> expand -> publish chain is longer than the MMAs of a slice; two chains
+        // side by side keep the tensor core fed.
+        constexpr int GROUP_THREADS = PF_EXP_WARPS * 32 / PF_GROUPS;
+        const int group = (warp - 2) / (PF_EXP_WARPS / PF_GROUPS);
+        const int e = (tid - 64) - group * GROUP_THREADS;
         int it = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < n_tiles_total && ok; t += gridDim.x) {
-            for (int kt = 0; kt < p.k_tiles; ++kt, ++it) {
+            for (int kt = 0; kt < p.k_tiles && ok; ++kt, ++it) {
+                if (it % PF_GROUPS != group) continue;
                 const int s = it % PF_STAGES;
                 const unsigned ph = (unsigned)(it / PF_STAGES) & 1u;
-                if (!pf_mbar_wait(&s_full_tma[s], ph)) { ok = false; break; }
-                const unsigned *wp = reinterpret_cast<const unsigned *>(stage_wp(s));
-                unsigned char *bx = stage_b(s);
-#pragma unroll 4
-                for (int r = 0; r < (PF_BN * PF_BK / 16) / 128; ++r) {   // 2048 words of 16 weights / 128 threads
-                    const int idx = e + r * 128;
-                    const int n = idx >> 3, g = idx & 7;
-                    const unsigned w = wp[idx];
-                    uint4 v;
-                    v.x = w & 0x03030303u;
-                    v.y = (w >> 2) & 0x03030303u;
-                    v.z = (w >> 4) & 0x03030303u;
-                    v.w = (w >> 6) & 0x03030303u;
-                    *reinterpret_cast<uint4 *>(bx + n * 128 + ((g ^ (n & 7)) << 4)) = v;
+                const int sb = it % PF_BSTAGES;
+                const unsigned phb = (unsigned)(it / PF_BSTAGES) & 1u;
+                if (!pf_warp_wait(&s_full_tma[s], ph) || !pf_warp_wait(&s_empty_b[sb], phb ^ 1u)) { ok = false; break; }
+                // word idx = e + r*GROUP_THREADS covers row n = idx/8, 16-wide group g = idx%8; both g and
+                // n%8 are fixed per thread, so source and (swizzled) destination just step by constants
+                const unsigned *wp = reinterpret_cast<const unsigned *>(stage_wp(s)) + e;
+                unsigned char *bx = stage_b(sb) + (e >> 3) * 128 + (((e & 7) ^ ((e >> 3) & 7)) << 4);
+                {
+#pragma unroll
+                    for (int r = 0; r < (PF_BN * PF_BK / 16) / GROUP_THREADS; ++r) {   // 2048 words of 16 weights
+                        const unsigned w = wp[r * GROUP_THREADS];
+                        uint4 v;
+                        v.x = w & 0x03030303u;
+                        v.y = (w >> 2) & 0x03030303u;
+                        v.z = (w >> 4) & 0x03030303u;
+                        v.w = (w >> 6) & 0x03030303u;
+                        *reinterpret_cast<uint4 *>(bx + r * (GROUP_THREADS / 8) * 128) = v;
+                    }
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the tensor core
                 __syncwarp();
-                if (lane == 0) pf_mbar_arrive(&s_full_b[s]);
+                if (lane == 0) pf_mbar_arrive(&s_full_b[sb]);
             }
         }
     } else {
@@ -324,43 +428,60 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const int n_tile = t / p.m_tiles, m_tile = t % p.m_tiles;
             const int buf = tc & 1;
             const unsigned acc_ph = (unsigned)(tc >> 1) & 1u;
-            if (!pf_mbar_wait(&s_acc_full[buf], acc_ph)) { ok = false; break; }
+            if (!pf_warp_wait(&s_acc_full[buf], acc_ph)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int m = m_tile * PF_BM + quarter * 32 + lane;
             const bool row_ok = m < p.M;
             const int rs = row_ok ? p.rowsum[m] : 0;
             const float scale = row_ok ? __fmul_rn(p.w_scale, p.a_scale[m]) : 0.0f;
             const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)buf * PF_BN;
+            // each lane holds one token row of the accumulator; rows are far apart in y, so a 32x32
+            // block goes through shared memory (XOR-swizzled 16-byte chunks, conflict-free both ways)
+            // and leaves as full 128-byte row segments
+            unsigned char *epi = smem + (size_t)PF_BSTAGES * PF_B_BYTES + (size_t)PF_STAGES * PF_STAGE_BYTES + (size_t)(warp & 3) * 4096;
+            const int m_base = m_tile * PF_BM + quarter * 32;
 #pragma unroll 1
             for (int c = 0; c < PF_BN / 32; ++c) {
                 unsigned r[32];
                 pf_tmem_ld32(taddr + (unsigned)c * 32, r);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 const int n0 = n_tile * PF_BN + c * 32;
-                if (row_ok && n0 < p.N) {
-                    float *yrow = p.y + (size_t)m * p.ldy + n0;
-                    int32_t *arow = p.acc_out ? p.acc_out + (size_t)m * p.ldy + n0 : nullptr;
-                    if (n0 + 32 <= p.N && ((reinterpret_cast<uintptr_t>(yrow) & 15) == 0)) {
+                if (n0 >= p.N) continue;   // warp-uniform
+                if (p.acc_out && row_ok) {
+                    int32_t *arow = p.acc_out + (size_t)m * p.ldy + n0;
 #pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            float4 o;
-                            o.x = __fmul_rn((float)((int)r[j + 0] - rs), scale);
-                            o.y = __fmul_rn((float)((int)r[j + 1] - rs), scale);
-                            o.z = __fmul_rn((float)((int)r[j + 2] - rs), scale);
-                            o.w = __fmul_rn((float)((int)r[j + 3] - rs), scale);
-                            *reinterpret_cast<float4 *>(yrow + j) = o;
+                    for (int j = 0; j < 32; ++j)
+                        if (n0 + j < p.N) arow[j] = (int)r[j] - rs;
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    float4 o;
+                    o.x = __fmul_rn((float)((int)r[4 * j + 0] - rs), scale);
+                    o.y = __fmul_rn((float)((int)r[4 * j + 1] - rs), scale);
+                    o.z = __fmul_rn((float)((int)r[4 * j + 2] - rs), scale);
+                    o.w = __fmul_rn((float)((int)r[4 * j + 3] - rs), scale);
+                    *reinterpret_cast<float4 *>(epi + lane * 128 + ((j ^ (lane & 7)) << 4)) = o;
+                }
+                __syncwarp();
+                const bool vec_ok = n0 + 32 <= p.N && (p.ldy % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15) == 0);
+#pragma unroll
+                for (int it2 = 0; it2 < 8; ++it2) {
+                    const int rr = it2 * 4 + (lane >> 3), ch = lane & 7;
+                    const float4 o = *reinterpret_cast<const float4 *>(epi + rr * 128 + ((ch ^ (rr & 7)) << 4));
+                    const int mm = m_base + rr;
+                    if (mm < p.M) {
+                        float *dst = p.y + (size_t)mm * p.ldy + n0 + ch * 4;
+                        if (vec_ok) {
+                            *reinterpret_cast<float4 *>(dst) = o;
+                        } else {
+                            if (n0 + ch * 4 + 0 < p.N) dst[0] = o.x;
+                            if (n0 + ch * 4 + 1 < p.N) dst[1] = o.y;
+                            if (n0 + ch * 4 + 2 < p.N) dst[2] = o.z;
+                            if (n0 + ch * 4 + 3 < p.N) dst[3] = o.w;
                         }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (n0 + j < p.N) yrow[j] = __fmul_rn((float)((int)r[j] - rs), scale);
-                    }
-                    if (arow) {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (n0 + j < p.N) arow[j] = (int)r[j] - rs;
                     }
                 }
+                __syncwarp();
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
