@@ -217,7 +217,9 @@ def run_cuda(args):
                 ops.ffn_forward(Wg[l], S[l][0], Wu[l], S[l][1], Wd[l], S[l][2], X[M][l], FFN, out=Y[M][l], h_out=Hb[M],
                                 pdl=pdl)
 
-    launches_per_step = 2 * LAYERS * len(TOKEN_COUNTS)
+    # per FFN block: M = 1 runs two launches (gate/up pair, down), each quantising its own input;
+    # M >= 2 adds one small quantiser launch in front of each (activations are quantised once, not per CTA)
+    launches_per_step = sum((2 if M < 2 else 4) for M in TOKEN_COUNTS) * LAYERS
 
     # parity spot check against the oracle on layer 0, M=8 (checker only, outside any timing)
     step(False)
@@ -377,13 +379,53 @@ def single_kernel_figures(torch, ops, gen, peak):
         gbs = call_bytes(M, K, N) / us / 1e3
         out[name] = {"us": us, "gbs": gbs, "frac_of_peak": gbs / peak, "weight_copies": copies}
         del W
+    out["cfg3_prefill_layer_m2048"] = prefill_layer_figures(torch, ops, gen)
     return out
+
+
+def prefill_layer_figures(torch, ops, gen):
+    """The seven BitLinear projections of one 2B decoder layer at M = 2048 tokens through the
+    tensor-core path (quantiser launch + tcgen05 GEMM each), replayed from a CUDA graph."""
+    M = 2048
+    shapes = {"q": (2560, 2560), "k": (2560, 640), "v": (2560, 640), "o": (2560, 2560),
+              "gate": (2560, 6912), "up": (2560, 6912), "down": (6912, 2560)}
+    W = {k: gen_packed_on_device(torch, N * K, gen) for k, (K, N) in shapes.items()}
+    X = {k: gen_activations_on_device(torch, (M, K), gen) for k, (K, N) in shapes.items()}
+    Y = {k: torch.empty((M, N), device="cuda") for k, (K, N) in shapes.items()}
+
+    def layer():
+        for k, (K, N) in shapes.items():
+            ops.bitlinear_forward(W[k], 0.01, X[k], N, out=Y[k], path="prefill")
+
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        layer()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            layer()
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 10
+    e0.record()
+    for _ in range(reps):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / reps
+    int_ops = sum(2.0 * M * K * N for (K, N) in shapes.values())
+    tops = int_ops / us / 1e6
+    return {"us": us, "tops": tops, "int_ops": int_ops, "bound": "tensor",
+            "frac_of_nominal_int8_peak_4500": tops / 4500.0,
+            "note": "no measured int8 peak on this pool; 4500 TOPS is the nominal dense figure"}
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--eager", action="store_true", help="launch kernels one by one instead of replaying a CUDA graph")

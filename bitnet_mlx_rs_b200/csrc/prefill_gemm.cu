@@ -530,14 +530,24 @@ static bitnet_status_t encode_map(CUtensorMap *map, const void *base, uint64_t i
     const cuuint64_t strides[1] = {row_stride_bytes};
     const cuuint32_t box[2] = {box_inner, box_rows};
     const cuuint32_t elem[2] = {1, 1};
-    const CUresult r = cuTensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box,
-                                              elem, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
-        const char *msg = nullptr;
-        cuGetErrorString(r, &msg);
-        return fail(BITNET_ERR_CUDA_DRIVER, "cuTensorMapEncodeTiled failed: %s", msg ? msg : "unknown");
+    // the driver entry point is looked up through the runtime, so the library does not link
+    // against libcuda and still loads on a machine without a driver
+    typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                 const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = nullptr;
+    if (!encode) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        BITNET_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+        if (!fn || qres != cudaDriverEntryPointSuccess)
+            return fail(BITNET_ERR_CUDA_DRIVER, "cuTensorMapEncodeTiled is not available from this driver");
+        encode = reinterpret_cast<EncodeFn>(fn);
     }
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, elem,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(BITNET_ERR_CUDA_DRIVER, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
     return BITNET_OK;
 }
 
