@@ -61,6 +61,7 @@ SIGNATURES = {
     "launch_w2a8_gemv_optimized": (None, [vp, vp, vp, sz, sz, vp]),
     "bitnet_bitlinear_forward": (i32, [vp, f32, vp, vp, sz, sz, sz, _P(ForwardOpts), vp, sz, vp]),
     "bitnet_bitlinear_workspace_size": (i32, [sz, sz, sz, i32, _P(sz)]),
+    "bitnet_bitlinear_forward_static": (i32, [vp, f32, vp, vp, sz, sz, sz, vp]),
     "bitnet_quantize_activations": (i32, [vp, sz, sz, vp, vp, vp]),
     "bitnet_ffn_forward": (i32, [vp, f32, vp, f32, vp, f32, vp, vp, vp, sz, sz, sz, _P(ForwardOpts), vp, sz, vp]),
     "bitnet_ffn_workspace_size": (i32, [sz, sz, sz, i32, _P(sz)]),

@@ -53,6 +53,7 @@ struct ForwardArgs {
     // decode path scratch for the quantised-activation image (decode_image_bytes); optional
     void *image_ws;
     size_t image_ws_bytes;
+    bool force_split;    // quantise through the image even for a single token
 };
 
 bitnet_status_t launch_decode(const ForwardArgs &a, cudaStream_t stream);
@@ -60,6 +61,7 @@ bool decode_supports(size_t M, size_t K, size_t N);
 bool decode_supports_dual(size_t M, size_t K, size_t N);   // gate and up in one launch
 int decode_grid(size_t N);                                  // CTAs of a decode launch over N output features
 size_t decode_image_bytes(size_t M, size_t K, size_t N, bool dual);   // 0 when the kernel quantises by itself
+size_t decode_image_bytes_always(size_t M, size_t K, size_t N, bool dual);   // size of the image if one is used
 
 bitnet_status_t launch_quantize_rows(const float *x, size_t M, size_t K, int8_t *q, float *a_scale,
                                      cudaStream_t stream);

@@ -859,6 +859,12 @@ static size_t split_min_tokens()
     return (size_t)v;
 }
 
+size_t decode_image_bytes_always(size_t M, size_t K, size_t N, bool dual)
+{
+    const DecodePlan pl = decode_plan(M, K, N, dual);
+    return align_up(DEC_IMG_HDR + (size_t)pl.cw * pl.sw * 4 * pl.nt * 512, 256);
+}
+
 size_t decode_image_bytes(size_t M, size_t K, size_t N, bool dual)
 {
     if (M < split_min_tokens()) return 0;
@@ -893,9 +899,9 @@ bitnet_status_t launch_decode(const ForwardArgs &a, cudaStream_t stream)
     p.weights_first = (a.flags & BITNET_FLAG_PDL) ? 1 : 0;
     const DecodePlan pl = decode_plan(a.M, a.K, a.N, dual);
 
-    if (!in_i8 && a.image_ws && a.M >= split_min_tokens()) {
+    if (!in_i8 && a.image_ws && (a.force_split || a.M >= split_min_tokens())) {
         // quantise once, then let every CTA fetch the result
-        const size_t need = decode_image_bytes(a.M, a.K, a.N, dual);
+        const size_t need = decode_image_bytes_always(a.M, a.K, a.N, dual);
         if (a.image_ws_bytes < need || misaligned(a.image_ws, 16))
             return fail(BITNET_ERR_WORKSPACE, "decode path needs %zu bytes of 16-byte aligned workspace", need);
         cudaLaunchConfig_t cfg = {};

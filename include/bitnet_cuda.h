@@ -139,6 +139,20 @@ bitnet_status_t bitnet_bitlinear_forward(const uint8_t *weights_dev, float w_sca
 bitnet_status_t bitnet_bitlinear_workspace_size(size_t M, size_t K, size_t N, int32_t path,
                                                 size_t *bytes);
 
+/* The same forward for the decode shapes (1 <= M <= 16, K % 64 == 0, K <= 16384, or 8192 when
+ * M > 8) with no workspace argument and no allocation of any kind: its scratch is a fixed
+ * 136 KiB array built into the library, resident on every GPU that loads it.  It has no
+ * counterpart in the reference; it exists for callers that run inside a memory budget fixed at
+ * start-up, or that are called while their host forbids allocation calls, and so can neither
+ * cudaMalloc nor lend a buffer.  Other shapes are refused with BITNET_ERR_UNSUPPORTED_OPERATION
+ * (or BITNET_ERR_WORKSPACE if the scratch would not fit).  All calls on a device share the
+ * array: calls that may overlap on the GPU race on it.  The first call on a device resolves
+ * the array's address and should be made before any stream capture. */
+bitnet_status_t bitnet_bitlinear_forward_static(const uint8_t *weights_dev, float w_scale,
+                                                const float *x_dev, float *y_dev,
+                                                size_t M, size_t K, size_t N,
+                                                bitnet_stream_t stream);
+
 /* Per-token absmax int8 quantisation on its own
  * (TernaryProcessor::quantize_activations, ternary_operations.rs:117-172):
  * q = clamp(round_half_away(x * (127/absmax)), -128, 127), a_scale = absmax/127. */
