@@ -36,7 +36,11 @@ public:
                         bytes, pool_size_);
         void *p = nullptr;
         BITNET_CUDA(cudaMalloc(&p, bytes ? bytes : 1));
-        const cudaError_t err = cudaMemset(p, 0, bytes);
+        // cudaMemset on device memory may return before the fill has run, and the compute
+        // streams here are non-blocking (not ordered with the default stream): finish the fill
+        // before anyone can touch the buffer
+        cudaError_t err = cudaMemset(p, 0, bytes);
+        if (err == cudaSuccess) err = cudaStreamSynchronize(cudaStreamLegacy);
         if (err != cudaSuccess) {
             cudaFree(p);
             return check_cuda(err, "cudaMemset");

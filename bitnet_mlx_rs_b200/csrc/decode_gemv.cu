@@ -76,9 +76,9 @@ struct DecodeParams {
     int stages_free;     // stages that do not overlap the activation staging area
     unsigned stage_bytes;   // one block of one matrix is 16 * K/4 contiguous bytes; a stage holds NW of them
     unsigned stage_stride;  // stage_bytes plus a 128-byte tail whose first 16 bytes stay zero
-    const unsigned *amax_in;   // optional: per-token absmax keys left by the producer kernel, [n_amax_in][16]
+    const unsigned *amax_in;   // optional: per-token absmax keys left by the producer kernel, [16 tokens][256 CTA slots]
     int n_amax_in;
-    unsigned *amax_out;        // optional: this CTA's per-token absmax keys of what it wrote, [gridDim.x][16]
+    unsigned *amax_out;        // optional: this CTA's per-token absmax keys of what it wrote, same layout
     int weights_first;         // 1: start the weight stream at once (the activations are not ready yet anyway)
     const unsigned char *image;   // optional: activations already quantised by decode_quantize_kernel
     unsigned image_bytes;
@@ -312,12 +312,22 @@ decode_kernel(const DecodeParams p)
                 if (single_batch) load_batch(0);               // overlap the fetch of x with the fold
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&s_x_issued);
-                const int total = p.n_amax_in * DEC_MAX_TOKENS;
-                unsigned key = 0;
-                for (int i = tid; i < total; i += DEC_CWARPS * 32) {   // 256 threads, stride keeps the token fixed
-                    key = max(key, __ldg(p.amax_in + i));
+                // keys are stored [token][256 CTA slots]; only the real tokens are read, four
+                // independent loads at a time
+                const int total = p.M * p.n_amax_in;
+                for (int i0 = tid; i0 < total; i0 += 4 * DEC_CWARPS * 32) {
+                    unsigned k4[4];
+                    int tok[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int i = i0 + u * DEC_CWARPS * 32;
+                        tok[u] = i < total ? i / p.n_amax_in : 0;
+                        k4[u] = i < total ? __ldg(p.amax_in + tok[u] * 256 + (i - tok[u] * p.n_amax_in)) : 0u;
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        if (k4[u]) atomicMax(&s_key[tok[u]], k4[u]);
                 }
-                if (key) atomicMax(&s_key[tid & (DEC_MAX_TOKENS - 1)], key);
             } else {
                 unsigned cur_m = 0, cur_key = 0;   // running maximum of the token this lane is in
                 for (unsigned base = 0; base < n_groups; base += 32u * U) {
@@ -586,7 +596,7 @@ decode_kernel(const DecodeParams p)
     }
     if (p.amax_out) {   // this CTA's share of the per-token absmax of what the launch wrote
         consumer_barrier<CW>();
-        if (tid < DEC_MAX_TOKENS) p.amax_out[(size_t)blockIdx.x * DEC_MAX_TOKENS + tid] = s_okey[tid];
+        if (tid < DEC_MAX_TOKENS) p.amax_out[(size_t)tid * 256 + blockIdx.x] = s_okey[tid];   // [token][CTA slot]
     }
     PHASE(1);
 }
@@ -630,7 +640,7 @@ __global__ void __launch_bounds__(512) decode_quantize_kernel(const float *__res
     }
     unsigned key = 0;
     if (amax_in) {
-        for (int i = tid; i < n_amax_in; i += 512) key = max(key, __ldg(amax_in + (size_t)i * DEC_MAX_TOKENS + m));
+        for (int i = tid; i < n_amax_in; i += 512) key = max(key, __ldg(amax_in + (size_t)m * 256 + i));
     } else {
 #pragma unroll
         for (int u = 0; u < 2; ++u)
@@ -846,17 +856,18 @@ static bitnet_status_t launch_sw(const DecodePlan &pl, const DecodeParams &p, ui
     return fail(BITNET_ERR_UNSUPPORTED_OPERATION, "decode kernel: K=%d is too wide for this token count", p.K);
 }
 
-// Token count from which the activations are quantised by their own small launch instead of
-// by every CTA of the decode kernel (whose redundant quantiser work grows with M).
-static size_t split_min_tokens()
+// Activation count (M*K) above which the activations are quantised by their own small launch
+// instead of by every CTA of the decode kernel: the redundant per-CTA quantiser work grows with
+// M*K, while the extra launch costs a fixed couple of microseconds in the dependency chain.
+static bool use_split(size_t M, size_t K)
 {
     static long v = -1;
     if (v < 0) {
-        const char *e = getenv("BITNET_DECODE_SPLIT_MIN_M");
-        v = e ? atol(e) : 2;
-        if (v < 1) v = 1;
+        const char *e = getenv("BITNET_DECODE_SPLIT_MIN_ELEMS");
+        v = e ? atol(e) : 8192;
+        if (v < 0) v = 0;
     }
-    return (size_t)v;
+    return M * K > (size_t)v;
 }
 
 size_t decode_image_bytes_always(size_t M, size_t K, size_t N, bool dual)
@@ -867,7 +878,7 @@ size_t decode_image_bytes_always(size_t M, size_t K, size_t N, bool dual)
 
 size_t decode_image_bytes(size_t M, size_t K, size_t N, bool dual)
 {
-    if (M < split_min_tokens()) return 0;
+    if (!use_split(M, K)) return 0;
     const DecodePlan pl = decode_plan(M, K, N, dual);
     return align_up(DEC_IMG_HDR + (size_t)pl.cw * pl.sw * 4 * pl.nt * 512, 256);
 }
@@ -899,7 +910,7 @@ bitnet_status_t launch_decode(const ForwardArgs &a, cudaStream_t stream)
     p.weights_first = (a.flags & BITNET_FLAG_PDL) ? 1 : 0;
     const DecodePlan pl = decode_plan(a.M, a.K, a.N, dual);
 
-    if (!in_i8 && a.image_ws && (a.force_split || a.M >= split_min_tokens())) {
+    if (!in_i8 && a.image_ws && (a.force_split || use_split(a.M, a.K))) {
         // quantise once, then let every CTA fetch the result
         const size_t need = decode_image_bytes_always(a.M, a.K, a.N, dual);
         if (a.image_ws_bytes < need || misaligned(a.image_ws, 16))
