@@ -5,7 +5,8 @@ Workload (N=1): the BitNet b1.58 2B-shaped FFN decode GEMVs -- gate/up 2560->691
 squared-ReLU gating, down 6912->2560 with per-token re-quantisation -- at M in {1,4,8}
 tokens over 30 distinct layers' weights (398 MB packed, larger than L2), seeded synthetic
 ternary weights (P(0)=0.4, P(+-1)=0.3) and N(0,1) activations with 0.1 % x20 outliers.
-One step = 3 token counts x 30 layers x one FFN block = 180 kernel launches.
+One step = 3 token counts x 30 layers x one FFN block = 300 kernel launches
+(2 per block at M = 1, 4 at M > 1 where a small quantiser launch precedes each decode launch).
 
 metric  = algorithmic HBM GB/s: bytes N*K/4 + 4*M*K + 4*M*N per BitLinear call, summed
           over the step, divided by device time (CUDA events, max over ranks).

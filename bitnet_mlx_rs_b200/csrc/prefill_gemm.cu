@@ -32,19 +32,28 @@ namespace bitnet {
 // Set (bit 1) when a bounded wait of the GEMM kernel ran out -- read with bitnet_device_error_flags().
 __device__ unsigned g_prefill_error_flags;
 
-constexpr int PF_BM = 128, PF_BN = 256, PF_BK = 128;   // tile: tokens x features x k (bytes of int8)
-constexpr int PF_STAGES = 4;                       // TMA ring: activations + packed weights (latency hiding)
-constexpr int PF_BSTAGES = 3;                      // ring of expanded weight tiles
-constexpr int PF_A_BYTES = PF_BM * PF_BK;          // 16 KB
-constexpr int PF_WP_BYTES = PF_BN * PF_BK / 4;     // 8 KB packed
-constexpr int PF_B_BYTES = PF_BN * PF_BK;          // 32 KB expanded
-constexpr int PF_STAGE_BYTES = PF_A_BYTES + PF_WP_BYTES;
+constexpr int PF_BF = 128;                         // output features per tile (the MMA's M: tensor-memory lanes)
+constexpr int PF_BT = 192;                         // tokens per tile (the MMA's N)
+constexpr int PF_BK = 128;                         // k per slice (bytes of int8)
+constexpr int PF_PAIR = 2;                         // k slices per hand-over between the roles (one barrier round per pair)
+constexpr int PF_RING = 3;                         // activation pairs in flight (the ring holds PF_RING * PF_PAIR slices)
+constexpr int PF_WRING = 6;                        // packed-weight pairs in flight: twice as far ahead, so that a pair's
+                                                   // weights are expanded before its activations land
+constexpr int PF_XSTAGES = PF_RING * PF_PAIR, PF_WSTAGES = PF_WRING * PF_PAIR;
+constexpr int PF_ASLOTS = 2;                       // expanded-weight pairs in tensor memory
+constexpr int PF_X_BYTES = PF_BT * PF_BK;          // 24 KB
+constexpr int PF_WP_BYTES = PF_BF * PF_BK / 4;     // 4 KB packed
 constexpr int PF_EXP_WARPS = 8;                    // warps that expand packed weights
 constexpr int PF_GROUPS = 2;                       // expander groups working on alternate k slices
 constexpr int PF_THREADS = (2 + PF_EXP_WARPS + 4) * 32;   // producer, MMA, expanders, epilogue
-constexpr unsigned PF_WAIT_LIMIT = 1u << 22;
-constexpr int PF_EPI_BYTES = 4 * 32 * 32 * 4;       // per epilogue warp a 32x32 fp32 transpose buffer
-constexpr size_t PF_SMEM = (size_t)PF_STAGES * PF_STAGE_BYTES + (size_t)PF_BSTAGES * PF_B_BYTES + PF_EPI_BYTES + 1024;   // + alignment slack
+constexpr unsigned PF_WAIT_LIMIT = 1u << 20;
+constexpr int PF_TMEM_A0 = 2 * PF_BT;              // tensor-memory columns: two accumulators, then the weight ring
+constexpr int PF_A_COLS = PF_BK / 4;               // 32 columns hold 128 bytes of k per lane
+static_assert(PF_TMEM_A0 + PF_ASLOTS * PF_PAIR * PF_A_COLS <= 512, "tensor memory has 512 columns");
+constexpr int PF_OUT_BYTES = 32 * PF_BF * 4;        // epilogue staging: 32 tokens x 128 features fp32, two of them
+constexpr size_t PF_RING_BYTES = (size_t)PF_XSTAGES * PF_X_BYTES + (size_t)PF_WSTAGES * PF_WP_BYTES;
+constexpr size_t PF_SMEM = PF_RING_BYTES + 2 * PF_OUT_BYTES + 1024;   // + alignment slack
+constexpr size_t PF_SLOT_BYTES = (size_t)PF_BF * PF_BT * 4;   // one partial accumulator tile
 
 // ---- quantiser for the GEMM path ----------------------------------------------------------------
 
@@ -66,8 +75,12 @@ __device__ __forceinline__ int pf_quantize_fast(float x, float scale)
 __global__ void __launch_bounds__(256) quantize_rows_perm_kernel(const float *__restrict__ x, size_t K,
                                                                  int8_t *__restrict__ q_perm, float *__restrict__ a_scale,
                                                                  int *__restrict__ rowsum, int8_t *__restrict__ q_out,
-                                                                 float *__restrict__ a_scale_out)
+                                                                 float *__restrict__ a_scale_out, unsigned *__restrict__ counters,
+                                                                 int n_counters)
 {
+    // the GEMM that follows counts the parts of split tiles in these; they start at zero
+    if (blockIdx.x == 0)
+        for (int i = threadIdx.x; i < n_counters; i += 256) counters[i] = 0u;
     __shared__ unsigned s_key[8];
     __shared__ int s_sum[8];
     const size_t m = blockIdx.x;
@@ -176,13 +189,14 @@ __global__ void __launch_bounds__(256) quantize_rows_perm_kernel(const float *__
 }
 
 #ifdef BITNET_PHASE_TIMERS
-__device__ unsigned long long g_pf_ts[8][128];   // [role/point][iteration] of CTA 0
+#ifndef PF_TS_CTA
+#define PF_TS_CTA 0
+#endif
+__device__ unsigned long long g_pf_ts[16][128];   // [role/point][iteration] of CTA 0
 #define PF_TS(point, it)                                                         \
     do {                                                                         \
-        if (blockIdx.x == 0 && (it) < 128) {                                     \
-            unsigned long long t_;                                               \
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));               \
-            g_pf_ts[point][it] = t_;                                             \
+        if (blockIdx.x == PF_TS_CTA && (it) < 128) {                                  \
+            g_pf_ts[point][it] = (unsigned long long)clock64();                                           \
         }                                                                        \
     } while (0)
 extern "C" int bitnet_debug_read_pf(unsigned long long *host) { return (int)cudaMemcpyFromSymbol(host, g_pf_ts, sizeof(g_pf_ts)); }
@@ -207,9 +221,20 @@ __device__ __forceinline__ void pf_mbar_expect_tx(unsigned long long *bar, unsig
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(pf_smem_u32(bar)), "r"(bytes) : "memory");
 }
 // Bounded wait; false (and the error flag) when the phase did not complete in time.
-__device__ __forceinline__ bool pf_mbar_wait(unsigned long long *bar, unsigned parity)
+__device__ __forceinline__ bool pf_mbar_wait(unsigned long long *bar, unsigned parity, bool backoff_req = true)
 {
     const unsigned addr = pf_smem_u32(bar);
+    {   // the usual case: the phase completed long ago -- a plain test, not the potentially suspending wait
+        unsigned done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
     for (unsigned n = 0; n < PF_WAIT_LIMIT; ++n) {
         unsigned done;
         asm volatile(
@@ -220,9 +245,7 @@ __device__ __forceinline__ bool pf_mbar_wait(unsigned long long *bar, unsigned p
             : "r"(addr), "r"(parity)
             : "memory");
         if (done) return true;
-#ifndef BITNET_NO_BACKOFF
-        __nanosleep(n < 16 ? 32 : 128);   // a waiting warp must not take issue slots from the working ones
-#endif
+        (void)backoff_req; __nanosleep(n < 16 ? 32 : 128);   // a waiting warp must not take issue slots from the working ones
     }
     atomicOr(&g_prefill_error_flags, 2u);
     return false;
@@ -276,52 +299,118 @@ __device__ __forceinline__ void pf_tmem_ld32(unsigned taddr, unsigned (&r)[32])
         : "memory");
 }
 
+__device__ __forceinline__ void pf_mma_i8_ts(unsigned tmem_d, unsigned tmem_a, unsigned long long b_desc, unsigned idesc,
+                                             unsigned accumulate)
+{
+    // A (expanded weights) comes from tensor memory, B (activations) from shared memory
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void pf_tmem_st32(unsigned taddr, const unsigned (&r)[32])
+{
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+        "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+        "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+// Barrier among the four epilogue warps that also ANDs a predicate (all leave a loop together).
+__device__ __forceinline__ bool pf_epi_all(bool ok)
+{
+    unsigned out;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.b32 q, %1, 0;\n\t"
+        "barrier.cta.red.and.pred p, 1, 128, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(out)
+        : "r"(ok ? 1u : 0u)
+        : "memory");
+    return out != 0;
+}
+
+__device__ __forceinline__ void pf_tma_store_2d(const CUtensorMap *map, int x, int y, const void *src)
+{
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+                 "r"(pf_smem_u32(src)), "r"(x), "r"(y)
+                 : "memory");
+}
 struct PrefillParams {
     float *y;
     int32_t *acc_out;
     const float *a_scale;
     const int *rowsum;
+    int *slots;          // partial accumulator tiles, two per CTA, [token][feature] int32
+    unsigned *counters;  // per tile: k slices contributed so far (zero at launch)
     float w_scale;
     int M, K, N;
     size_t ldy;
     int m_tiles, n_tiles, k_tiles;
+    int tma_store;       // y can be written with TMA (16-byte aligned rows), else plain stores
 };
 
-// instruction descriptor: D = s32, A = s8 (activations), B = u8 (codes), both K-major, N = 256, M = 128
-constexpr unsigned PF_IDESC = (2u << 4) | (1u << 7) | (0u << 10) | ((unsigned)(PF_BN >> 3) << 17) | ((unsigned)(PF_BM >> 4) << 24);
+// instruction descriptor: D = s32, A = u8 (codes, tensor memory), B = s8 (activations, K-major), N = tokens, M = 128
+constexpr unsigned PF_IDESC = (2u << 4) | (0u << 7) | (1u << 10) | ((unsigned)(PF_BT >> 3) << 17) | ((unsigned)(PF_BF >> 4) << 24);
+
+// The work of the whole GEMM is the sequence of (tile, k slice) units, tile-major; CTA c takes
+// the contiguous range [U*c/G, U*(c+1)/G), so every CTA has the same number of k slices whatever
+// the tile count.  A segment is the part of one tile inside a range.
+struct PfSegment {
+    int tile, kb, ke;
+};
+__device__ __forceinline__ long long pf_range_start(long long units, int c, int ctas) { return units * c / ctas; }
+__device__ __forceinline__ bool pf_next_segment(long long &u, long long u_end, int k_tiles, PfSegment &sg)
+{
+    if (u >= u_end) return false;
+    sg.tile = (int)(u / k_tiles);
+    sg.kb = (int)(u - (long long)sg.tile * k_tiles);
+    const long long rest = u_end - u;
+    const int left = k_tiles - sg.kb;
+    sg.ke = sg.kb + (int)(rest < left ? rest : left);
+    u += sg.ke - sg.kb;
+    return true;
+}
 
 __global__ void __launch_bounds__(PF_THREADS, 1)
-prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const PrefillParams p)
+prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                    const __grid_constant__ CUtensorMap map_y, const PrefillParams p)
 {
     extern __shared__ unsigned char pf_smem_raw[];
-    __shared__ __align__(8) unsigned long long s_full_tma[PF_STAGES], s_empty[PF_STAGES];
-    __shared__ __align__(8) unsigned long long s_full_b[PF_BSTAGES], s_empty_b[PF_BSTAGES];
+    __shared__ __align__(8) unsigned long long s_full_x[PF_RING];        // a pair's activations have landed
+    __shared__ __align__(8) unsigned long long s_full_w[PF_WRING];       // a pair's packed weights have landed
+    __shared__ __align__(8) unsigned long long s_full_a[PF_ASLOTS];      // a pair's weights are expanded in tensor memory
+    __shared__ __align__(8) unsigned long long s_done[PF_RING];          // the MMAs of a pair have read their operands
     __shared__ __align__(8) unsigned long long s_acc_full[2], s_acc_empty[2];
     __shared__ unsigned s_tmem_base;
+    __shared__ unsigned s_prev_count;
+    __shared__ __align__(16) int2 s_tab[PF_BT];   // per token of the tile: row sum, scale bits
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(pf_smem_raw) + 1023) & ~uintptr_t(1023));
-    // expanded weight tiles first (1024-byte aligned for the swizzle), then the TMA ring
-    auto stage_b = [&](int sb) { return smem + (size_t)sb * PF_B_BYTES; };
-    auto stage_a = [&](int s) { return smem + (size_t)PF_BSTAGES * PF_B_BYTES + (size_t)s * PF_STAGE_BYTES; };
-    auto stage_wp = [&](int s) { return smem + (size_t)PF_BSTAGES * PF_B_BYTES + (size_t)s * PF_STAGE_BYTES + PF_A_BYTES; };
+    // activation stages start 1024-byte aligned (the 128-byte swizzle needs it); the packed weights follow
+    auto stage_x = [&](int s) { return smem + (size_t)s * PF_X_BYTES; };
+    auto stage_wp = [&](int s) { return smem + (size_t)PF_XSTAGES * PF_X_BYTES + (size_t)s * PF_WP_BYTES; };
 
     if (tid == 0) {
-        for (int s = 0; s < PF_STAGES; ++s) {
-            pf_mbar_init(&s_full_tma[s], 1);
-            pf_mbar_init(&s_empty[s], 1);
-        }
-        for (int sb = 0; sb < PF_BSTAGES; ++sb) {
-            pf_mbar_init(&s_full_b[sb], PF_EXP_WARPS / PF_GROUPS);
-            pf_mbar_init(&s_empty_b[sb], 1);
-        }
+        for (int r = 0; r < PF_RING; ++r) pf_mbar_init(&s_full_x[r], 1);
+        for (int r = 0; r < PF_WRING; ++r) pf_mbar_init(&s_full_w[r], 1);
+        for (int sa = 0; sa < PF_ASLOTS; ++sa) pf_mbar_init(&s_full_a[sa], PF_EXP_WARPS / PF_GROUPS);
+        for (int r = 0; r < PF_RING; ++r) pf_mbar_init(&s_done[r], 1);
         for (int b = 0; b < 2; ++b) {
             pf_mbar_init(&s_acc_full[b], 1);
             pf_mbar_init(&s_acc_empty[b], 4);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {   // one warp allocates all 512 tensor-memory columns: two 128x256 s32 accumulators
+    if (warp == 1) {   // all 512 tensor-memory columns: two 128 x 192 s32 accumulators + the weight slots
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(pf_smem_u32(&s_tmem_base)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -329,169 +418,328 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const unsigned tmem_base = s_tmem_base;
+    if (tid == 0) PF_TS(15, 0);
 
-    const int n_tiles_total = p.m_tiles * p.n_tiles;
+    const long long units = (long long)p.m_tiles * p.n_tiles * p.k_tiles;
+    const long long u_begin = pf_range_start(units, (int)blockIdx.x, (int)gridDim.x);
+    const long long u_end = pf_range_start(units, (int)blockIdx.x + 1, (int)gridDim.x);
+    const int n_slices = (int)(u_end - u_begin);   // k slices of this CTA, numbered it = 0.. across its segments
+    // Slices are handed between the roles in pairs (pair pp = it / 2): one barrier round per pair
+    // keeps the single MMA-issuing thread's waits and commits off the critical path.
 
     if (warp == 0) {
         // ===================== TMA producer =====================
         if (lane == 0) {
-            int it = 0;
-            bool ok = true;
-            for (int t = blockIdx.x; t < n_tiles_total && ok; t += gridDim.x) {
-                const int n_tile = t / p.m_tiles, m_tile = t % p.m_tiles;
-                for (int kt = 0; kt < p.k_tiles; ++kt, ++it) {
-                    const int s = it % PF_STAGES;
-                    const unsigned ph = (unsigned)(it / PF_STAGES) & 1u;
-                    PF_TS(0, it);
-                    if (!pf_mbar_wait(&s_empty[s], ph ^ 1u)) { ok = false; break; }
-                    PF_TS(1, it);
-                    pf_mbar_expect_tx(&s_full_tma[s], PF_A_BYTES + PF_WP_BYTES);
-                    pf_tma_load_2d(stage_a(s), &map_a, kt * PF_BK, m_tile * PF_BM, &s_full_tma[s]);
-                    pf_tma_load_2d(stage_wp(s), &map_w, kt * (PF_BK / 4), n_tile * PF_BN, &s_full_tma[s]);
+            const int n_pairs = (n_slices + PF_PAIR - 1) / PF_PAIR;
+            // two cursors walk this CTA's slices (unit u_begin + it -> tile, k position) without
+            // divisions: one for the activations, one for the packed weights that run ahead
+            struct Cursor {
+                int n_tile, m_tile, kt;
+            };
+            auto cursor_at = [&](long long uu) {
+                Cursor c;
+                const long long tile = uu / p.k_tiles;
+                c.kt = (int)(uu - tile * p.k_tiles);
+                c.n_tile = (int)(tile / p.m_tiles);
+                c.m_tile = (int)(tile - (long long)c.n_tile * p.m_tiles);
+                return c;
+            };
+            auto advance = [&](Cursor &c) {
+                if (++c.kt == p.k_tiles) {
+                    c.kt = 0;
+                    if (++c.m_tile == p.m_tiles) {
+                        c.m_tile = 0;
+                        ++c.n_tile;
+                    }
                 }
+            };
+            Cursor cx = cursor_at(u_begin), cw = cx;
+            auto load_w = [&](int q) {   // packed weights of pair q (called for q = 0, 1, 2, ... in order)
+                const int cnt = n_slices - q * PF_PAIR < PF_PAIR ? n_slices - q * PF_PAIR : PF_PAIR;
+                if (cnt <= 0) return;
+                pf_mbar_expect_tx(&s_full_w[q % PF_WRING], (unsigned)cnt * PF_WP_BYTES);
+                for (int h = 0; h < cnt; ++h) {
+                    pf_tma_load_2d(stage_wp((q * PF_PAIR + h) % PF_WSTAGES), &map_w, cw.kt * (PF_BK / 4), cw.n_tile * PF_BF,
+                                   &s_full_w[q % PF_WRING]);
+                    advance(cw);
+                }
+            };
+            for (int q = 0; q < PF_RING; ++q) load_w(q);
+            for (int pp = 0; pp < n_pairs; ++pp) {
+                const int cnt = n_slices - pp * PF_PAIR < PF_PAIR ? n_slices - pp * PF_PAIR : PF_PAIR;
+                // the pair that used these stages PF_RING pairs ago has been consumed; its packed
+                // weights (PF_WRING pairs behind the ones loaded now) as well
+                PF_TS(0, pp);
+                if (!pf_mbar_wait(&s_done[pp % PF_RING], ((unsigned)(pp / PF_RING) & 1u) ^ 1u, false)) break;
+                PF_TS(1, pp);
+                pf_mbar_expect_tx(&s_full_x[pp % PF_RING], (unsigned)cnt * PF_X_BYTES);
+                for (int h = 0; h < cnt; ++h) {
+                    pf_tma_load_2d(stage_x((pp * PF_PAIR + h) % PF_XSTAGES), &map_x, cx.kt * PF_BK, cx.m_tile * PF_BT,
+                                   &s_full_x[pp % PF_RING]);
+                    advance(cx);
+                }
+                load_w(pp + PF_RING);
             }
         }
     } else if (warp == 1) {
         // ===================== MMA issuer =====================
         if (lane == 0) {
-            int it = 0, tc = 0;
+            int it = 0, sc = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < n_tiles_total && ok; t += gridDim.x, ++tc) {
-                const int buf = tc & 1;
-                const unsigned acc_ph = (unsigned)(tc >> 1) & 1u;
-                if (!pf_mbar_wait(&s_acc_empty[buf], acc_ph ^ 1u)) { ok = false; break; }   // epilogue drained this accumulator
+            long long u = u_begin;
+            PfSegment sg;
+            while (ok && pf_next_segment(u, u_end, p.k_tiles, sg)) {
+                const int buf = sc & 1;
+                const unsigned acc_ph = (unsigned)(sc >> 1) & 1u;
+                ++sc;
+                if (!pf_mbar_wait(&s_acc_empty[buf], acc_ph ^ 1u, false)) { ok = false; break; }   // epilogue drained this accumulator
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const unsigned tmem_d = tmem_base + (unsigned)buf * PF_BN;
-                for (int kt = 0; kt < p.k_tiles; ++kt, ++it) {
-                    const int s = it % PF_STAGES;
-                    const unsigned ph = (unsigned)(it / PF_STAGES) & 1u;
-                    const int sb = it % PF_BSTAGES;
-                    const unsigned phb = (unsigned)(it / PF_BSTAGES) & 1u;
-                    if (!pf_mbar_wait(&s_full_b[sb], phb)) { ok = false; break; }   // implies the TMA data of the slice landed
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const unsigned long long a_desc = pf_smem_desc(pf_smem_u32(stage_a(s)));
-                    const unsigned long long b_desc = pf_smem_desc(pf_smem_u32(stage_b(sb)));
+                const unsigned tmem_d = tmem_base + (unsigned)buf * PF_BT;
+                for (int kt = sg.kb; kt < sg.ke; ++kt, ++it) {
+                    const int s = it % PF_XSTAGES;
+                    const int pp = it / PF_PAIR, h = it % PF_PAIR;
+                    if (h == 0) {   // the pair's expanded weights are in tensor memory and its activations have landed
+                        PF_TS(8, pp);
+                        if (!pf_mbar_wait(&s_full_a[pp % PF_ASLOTS], (unsigned)(pp / PF_ASLOTS) & 1u, false)) { ok = false; break; }
+                        PF_TS(9, pp);
+                        if (!pf_mbar_wait(&s_full_x[pp % PF_RING], (unsigned)(pp / PF_RING) & 1u, false)) { ok = false; break; }
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        PF_TS(4, pp);
+                    }
+                    const unsigned tmem_a = tmem_base + (unsigned)(PF_TMEM_A0 + ((pp % PF_ASLOTS) * PF_PAIR + h) * PF_A_COLS);
+                    const unsigned long long b_desc = pf_smem_desc(pf_smem_u32(stage_x(s)));
 #pragma unroll
-                    for (int ks = 0; ks < PF_BK / 32; ++ks)   // 32 bytes of k per instruction: +2 in 16-byte units
-                        pf_mma_i8(tmem_d, a_desc + 2ull * ks, b_desc + 2ull * ks, PF_IDESC, (kt | ks) != 0 ? 1u : 0u);
-                    pf_commit(&s_empty[s]);     // both rings' slots are free once these MMAs have read them
-                    pf_commit(&s_empty_b[sb]);
-                    (void)ph;
+                    for (int ks = 0; ks < PF_BK / 32; ++ks)   // 32 bytes of k per instruction: 8 columns / +2 16-byte units
+                        pf_mma_i8_ts(tmem_d, tmem_a + 8u * ks, b_desc + 2ull * ks, PF_IDESC, (kt != sg.kb || ks != 0) ? 1u : 0u);
+                    if (h == PF_PAIR - 1 || it == n_slices - 1) {
+                        pf_commit(&s_done[pp % PF_RING]);   // TMA stages and the tensor-memory slot of the pair are free
+                        PF_TS(5, pp);
+                    }
                 }
                 if (ok) pf_commit(&s_acc_full[buf]);
             }
         }
     } else if (warp < 2 + PF_EXP_WARPS) {
-        // ===================== weight expanders: PF_GROUPS groups take the k slices in turn =====================
-        // One group's wait -> expand -> publish chain is longer than the MMAs of a slice; two chains
-        // side by side keep the tensor core fed.
-        constexpr int GROUP_THREADS = PF_EXP_WARPS * 32 / PF_GROUPS;
+        // ===================== weight expanders: PF_GROUPS groups take the pairs in turn =====================
+        // A thread owns one feature row of the tile: 32 packed bytes per slice become the 128 code
+        // bytes of its tensor-memory lane.  (w >> 2j) & 0x03030303 is word j of a 16-wide group in
+        // the transposed k order the activations were stored in.
         const int group = (warp - 2) / (PF_EXP_WARPS / PF_GROUPS);
-        const int e = (tid - 64) - group * GROUP_THREADS;
-        int it = 0;
+        const int quarter = warp & 3;            // the tensor-memory lanes this warp may touch
+        const int row = quarter * 32 + lane;
+        const int n_pairs = (n_slices + PF_PAIR - 1) / PF_PAIR;
         bool ok = true;
-        for (int t = blockIdx.x; t < n_tiles_total && ok; t += gridDim.x) {
-            for (int kt = 0; kt < p.k_tiles && ok; ++kt, ++it) {
-                if (it % PF_GROUPS != group) continue;
-                const int s = it % PF_STAGES;
-                const unsigned ph = (unsigned)(it / PF_STAGES) & 1u;
-                const int sb = it % PF_BSTAGES;
-                const unsigned phb = (unsigned)(it / PF_BSTAGES) & 1u;
-                if (!pf_warp_wait(&s_full_tma[s], ph) || !pf_warp_wait(&s_empty_b[sb], phb ^ 1u)) { ok = false; break; }
-                // word idx = e + r*GROUP_THREADS covers row n = idx/8, 16-wide group g = idx%8; both g and
-                // n%8 are fixed per thread, so source and (swizzled) destination just step by constants
-                const unsigned *wp = reinterpret_cast<const unsigned *>(stage_wp(s)) + e;
-                unsigned char *bx = stage_b(sb) + (e >> 3) * 128 + (((e & 7) ^ ((e >> 3) & 7)) << 4);
-                {
+        for (int pp = group; pp < n_pairs && ok; pp += PF_GROUPS) {
+            const int slot = pp % PF_ASLOTS;
+            // expand both slices of the pair into registers first: this part does not need the
+            // tensor-memory slot and overlaps the MMAs that still read it
+            unsigned r[PF_PAIR][32];
+            if (!pf_warp_wait(&s_full_w[pp % PF_WRING], (unsigned)(pp / PF_WRING) & 1u)) { ok = false; break; }
 #pragma unroll
-                    for (int r = 0; r < (PF_BN * PF_BK / 16) / GROUP_THREADS; ++r) {   // 2048 words of 16 weights
-                        const unsigned w = wp[r * GROUP_THREADS];
-                        uint4 v;
-                        v.x = w & 0x03030303u;
-                        v.y = (w >> 2) & 0x03030303u;
-                        v.z = (w >> 4) & 0x03030303u;
-                        v.w = (w >> 6) & 0x03030303u;
-                        *reinterpret_cast<uint4 *>(bx + r * (GROUP_THREADS / 8) * 128) = v;
-                    }
+            for (int h = 0; h < PF_PAIR; ++h) {
+                const int it = pp * PF_PAIR + h;
+                if (it >= n_slices) break;
+                const int s = it % PF_WSTAGES;
+                const uint4 *src = reinterpret_cast<const uint4 *>(stage_wp(s) + row * (PF_BK / 4));
+                const uint4 w0 = src[0], w1 = src[1];
+                const unsigned w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                    r[h][4 * g + 0] = w[g] & 0x03030303u;
+                    r[h][4 * g + 1] = (w[g] >> 2) & 0x03030303u;
+                    r[h][4 * g + 2] = (w[g] >> 4) & 0x03030303u;
+                    r[h][4 * g + 3] = (w[g] >> 6) & 0x03030303u;
                 }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the tensor core
-                __syncwarp();
-                if (lane == 0) pf_mbar_arrive(&s_full_b[sb]);
             }
+            if (!ok) break;
+            if (pp >= PF_ASLOTS) {   // the MMAs that read this slot (pair pp - PF_ASLOTS) are done
+                const int pd = pp - PF_ASLOTS;
+                if (!pf_warp_wait(&s_done[pd % PF_RING], (unsigned)(pd / PF_RING) & 1u)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            }
+            if (row == 0) PF_TS(2, pp);
+            const unsigned ta = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(PF_TMEM_A0 + slot * PF_PAIR * PF_A_COLS);
+            pf_tmem_st32(ta, r[0]);
+            if (pp * PF_PAIR + 1 < n_slices) pf_tmem_st32(ta + PF_A_COLS, r[1]);
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) pf_mbar_arrive(&s_full_a[slot]);
+            if (row == 0) PF_TS(3, pp);
         }
     } else {
-        // ===================== epilogue (128 threads, one accumulator row each) =====================
+        // ===================== epilogue (128 threads; a thread owns one feature row of the accumulator) =====================
+        // Accumulator lanes are features, columns are tokens, so a warp's 32 lanes hold 32 consecutive
+        // features of one token: chunks of 32 tokens x 128 features go through a shared-memory staging
+        // buffer ([token][feature], conflict-free) and leave as one TMA store each.
         const int quarter = warp & 3;   // the tensor-memory lanes a warp may touch: 32 * (warp % 4)
-        int tc = 0;
+        const int frow = quarter * 32 + lane;
+        const int et = tid - (2 + PF_EXP_WARPS) * 32;
+        const bool epi_leader = et == 0;
+        unsigned char *out_stage = smem + PF_RING_BYTES;
+        int sc = 0, n_staged = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < n_tiles_total && ok; t += gridDim.x, ++tc) {
-            const int n_tile = t / p.m_tiles, m_tile = t % p.m_tiles;
-            const int buf = tc & 1;
-            const unsigned acc_ph = (unsigned)(tc >> 1) & 1u;
-            if (!pf_warp_wait(&s_acc_full[buf], acc_ph)) { ok = false; break; }
+        long long u = u_begin;
+        PfSegment sg;
+
+        // stage one chunk (the thread's 32 values, raw bits) and send it: to y through the tensor map
+        // (tile coordinates x, yrow) or to a contiguous 16 KB piece of a partial-sum slot
+        auto send_chunk = [&](const unsigned (&v)[32], bool to_y, int x, int yrow, int *slot_piece) {
+            unsigned *st = reinterpret_cast<unsigned *>(out_stage + (size_t)(n_staged & 1) * PF_OUT_BYTES);
+            ++n_staged;
+            pf_epi_all(true);   // the leader has seen the copy that last read this buffer finish reading
+#pragma unroll
+            for (int j = 0; j < 32; ++j) st[j * PF_BF + frow] = v[j];
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            pf_epi_all(true);
+            if (epi_leader) {
+                if (to_y)
+                    pf_tma_store_2d(&map_y, x, yrow, st);
+                else
+                    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(slot_piece),
+                                 "r"(pf_smem_u32(st)), "r"(PF_OUT_BYTES)
+                                 : "memory");
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");   // the other buffer is free again
+            }
+        };
+
+        while (ok && pf_next_segment(u, u_end, p.k_tiles, sg)) {
+            const int n_tile = sg.tile / p.m_tiles, m_tile = sg.tile % p.m_tiles;
+            const int buf = sc & 1;
+            const unsigned acc_ph = (unsigned)(sc >> 1) & 1u;
+            ++sc;
+            const bool whole = sg.kb == 0 && sg.ke == p.k_tiles;
+            const int m0 = m_tile * PF_BT;
+            const int n = n_tile * PF_BF + frow;
+            const bool n_ok = n < p.N;
+            // per token of the tile: row sum and scale, read back below as broadcast 16-byte loads
+            pf_epi_all(true);   // nobody reads the previous tile's table any more
+            for (int j = et; j < PF_BT; j += 128) {
+                const int m = m0 + j;
+                int2 e = make_int2(0, 0);
+                if (m < p.M) {
+                    e.x = __ldg(p.rowsum + m);
+                    e.y = __float_as_int(__fmul_rn(p.w_scale, __ldg(p.a_scale + m)));
+                }
+                s_tab[j] = e;
+            }
+            ok = pf_epi_all(pf_warp_wait(&s_acc_full[buf], acc_ph));   // the four warps go on, or give up, together
+            if (!ok) break;
+            if (epi_leader) PF_TS(6, sc - 1);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int m = m_tile * PF_BM + quarter * 32 + lane;
-            const bool row_ok = m < p.M;
-            const int rs = row_ok ? p.rowsum[m] : 0;
-            const float scale = row_ok ? __fmul_rn(p.w_scale, p.a_scale[m]) : 0.0f;
-            const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)buf * PF_BN;
-            // each lane holds one token row of the accumulator; rows are far apart in y, so a 32x32
-            // block goes through shared memory (XOR-swizzled 16-byte chunks, conflict-free both ways)
-            // and leaves as full 128-byte row segments
-            unsigned char *epi = smem + (size_t)PF_BSTAGES * PF_B_BYTES + (size_t)PF_STAGES * PF_STAGE_BYTES + (size_t)(warp & 3) * 4096;
-            const int m_base = m_tile * PF_BM + quarter * 32;
+            const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)buf * PF_BT;
+
+            // a tile that is split between CTAs: publish this part, and whoever completes the
+            // tile's k range adds the published parts to its own (integer sums: order is irrelevant)
+            int c_lo = 0, c_hi = -1;   // the CTAs that hold parts of this tile (when it is split)
+            bool finish = true;
+            if (!whole) {
+                // claim first: the CTA whose claim completes the tile's k range finishes the tile and need not
+                // publish its own part; everyone else publishes and moves on
+                const unsigned len = (unsigned)(sg.ke - sg.kb);
+                if (epi_leader) s_prev_count = atomicAdd(p.counters + 2 * sg.tile, len);
+                pf_epi_all(true);
+                finish = s_prev_count + len == (unsigned)p.k_tiles;
+                pf_epi_all(true);   // s_prev_count may be rewritten only after everyone has read it
+                if (!finish) {
+                    const long long my_first_tile = u_begin / p.k_tiles;
+                    int *slot = p.slots + ((size_t)2 * blockIdx.x + (sg.tile != my_first_tile ? 1 : 0)) * (PF_BF * PF_BT);
 #pragma unroll 1
-            for (int c = 0; c < PF_BN / 32; ++c) {
-                unsigned r[32];
-                pf_tmem_ld32(taddr + (unsigned)c * 32, r);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                const int n0 = n_tile * PF_BN + c * 32;
-                if (n0 >= p.N) continue;   // warp-uniform
-                if (p.acc_out && row_ok) {
-                    int32_t *arow = p.acc_out + (size_t)m * p.ldy + n0;
-#pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        if (n0 + j < p.N) arow[j] = (int)r[j] - rs;
+                    for (int c = 0; c < PF_BT / 32; ++c) {
+                        unsigned r[32];
+                        pf_tmem_ld32(taddr + (unsigned)c * 32, r);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        send_chunk(r, false, 0, 0, slot + c * 32 * PF_BF);
+                    }
+                    if (epi_leader) {
+                        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // the slot is written
+                        asm volatile("fence.proxy.async;" ::: "memory");
+                        __threadfence();
+                        atomicAdd(p.counters + 2 * sg.tile + 1, len);
+                    }
+                } else {
+                    // the other parts were claimed before this one, so their CTAs are running and publish
+                    // without waiting for anybody: a short, bounded wait
+                    if (epi_leader) {
+                        const volatile unsigned *published = p.counters + 2 * sg.tile + 1;
+                        unsigned seen = 0;
+                        for (unsigned n = 0; n < PF_WAIT_LIMIT; ++n) {
+                            seen = *published;
+                            if (seen + len == (unsigned)p.k_tiles) break;
+                            __nanosleep(64);
+                        }
+                        if (seen + len != (unsigned)p.k_tiles) atomicOr(&g_prefill_error_flags, 2u);
+                        __threadfence();
+                    }
+                    pf_epi_all(true);
+                    const long long t_begin = (long long)sg.tile * p.k_tiles, t_end = t_begin + p.k_tiles;
+                    c_lo = (int)(((t_begin + 1) * gridDim.x - 1) / units);   // owners of the tile's first and last unit
+                    c_hi = (int)((t_end * gridDim.x - 1) / units);
                 }
+            }
+            if (finish) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    float4 o;
-                    o.x = __fmul_rn((float)((int)r[4 * j + 0] - rs), scale);
-                    o.y = __fmul_rn((float)((int)r[4 * j + 1] - rs), scale);
-                    o.z = __fmul_rn((float)((int)r[4 * j + 2] - rs), scale);
-                    o.w = __fmul_rn((float)((int)r[4 * j + 3] - rs), scale);
-                    *reinterpret_cast<float4 *>(epi + lane * 128 + ((j ^ (lane & 7)) << 4)) = o;
-                }
-                __syncwarp();
-                const bool vec_ok = n0 + 32 <= p.N && (p.ldy % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15) == 0);
+                for (int c = 0; c < PF_BT / 32; ++c) {
+                    if (m0 + c * 32 >= p.M) break;   // warp-uniform, and the same in all four warps
+                    unsigned r[32];
+                    pf_tmem_ld32(taddr + (unsigned)c * 32, r);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    for (int cc = c_lo; cc <= c_hi; ++cc) {
+                        if (cc == (int)blockIdx.x) continue;
+                        const long long t_begin = (long long)sg.tile * p.k_tiles, t_end = t_begin + p.k_tiles;
+                        const long long cb = pf_range_start(units, cc, (int)gridDim.x), ce = pf_range_start(units, cc + 1, (int)gridDim.x);
+                        if ((cb > t_begin ? cb : t_begin) >= (ce < t_end ? ce : t_end)) continue;   // an empty range
+                        const int *src = p.slots + ((size_t)2 * cc + (sg.tile != cb / p.k_tiles ? 1 : 0)) * (PF_BF * PF_BT) +
+                                         (c * 32) * PF_BF + frow;
+                        int t[32];   // all loads first: issued in order, a load next to its use would expose its latency
 #pragma unroll
-                for (int it2 = 0; it2 < 8; ++it2) {
-                    const int rr = it2 * 4 + (lane >> 3), ch = lane & 7;
-                    const float4 o = *reinterpret_cast<const float4 *>(epi + rr * 128 + ((ch ^ (rr & 7)) << 4));
-                    const int mm = m_base + rr;
-                    if (mm < p.M) {
-                        float *dst = p.y + (size_t)mm * p.ldy + n0 + ch * 4;
-                        if (vec_ok) {
-                            *reinterpret_cast<float4 *>(dst) = o;
-                        } else {
-                            if (n0 + ch * 4 + 0 < p.N) dst[0] = o.x;
-                            if (n0 + ch * 4 + 1 < p.N) dst[1] = o.y;
-                            if (n0 + ch * 4 + 2 < p.N) dst[2] = o.z;
-                            if (n0 + ch * 4 + 3 < p.N) dst[3] = o.w;
+                        for (int j = 0; j < 32; ++j) t[j] = __ldcg(src + j * PF_BF);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) r[j] += (unsigned)t[j];
+                    }
+                    const int m_left = p.M - (m0 + c * 32);   // tokens of this chunk that exist
+                    if (p.acc_out) {   // parity-test output of the integer sums; kept out of the loop below so that it stays branch-free
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (n_ok && j < m_left) p.acc_out[(size_t)(m0 + c * 32 + j) * p.ldy + n] = (int)r[j] - s_tab[c * 32 + j].x;
+                    }
+                    // loads first, arithmetic after: the warp issues in order, so a load placed next to
+                    // its use would expose its latency 32 times
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        int4 e[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) e[i] = reinterpret_cast<const int4 *>(s_tab)[c * 16 + h * 8 + i];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int j = h * 16 + 2 * i;
+                            r[j] = __float_as_uint(__fmul_rn((float)((int)r[j] - e[i].x), __int_as_float(e[i].y)));
+                            r[j + 1] = __float_as_uint(__fmul_rn((float)((int)r[j + 1] - e[i].z), __int_as_float(e[i].w)));
                         }
                     }
+                    if (p.tma_store) {
+                        send_chunk(r, true, n_tile * PF_BF, m0 + c * 32, nullptr);
+                    } else {
+                        float *ycol = p.y + (size_t)(m0 + c * 32) * p.ldy + n;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (n_ok && j < m_left) ycol[(size_t)j * p.ldy] = __uint_as_float(r[j]);
+                    }
                 }
-                __syncwarp();
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) pf_mbar_arrive(&s_acc_empty[buf]);
+            if (epi_leader) PF_TS(7, sc - 1);
         }
+        if (epi_leader) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // shared memory outlives the stores
     }
 
     // everyone meets here, also after a wait that gave up, so that tensor memory is always freed
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if (tid == 0) PF_TS(15, 1);
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
@@ -517,14 +765,24 @@ bool prefill_supports(size_t M, size_t K, size_t N)
 static size_t pf_q_bytes(size_t M, size_t K) { return align_up(M * K, 256); }
 static size_t pf_vec_bytes(size_t M) { return align_up(M * 4, 256); }
 
+static size_t pf_tiles(size_t M, size_t N) { return ((M + PF_BT - 1) / PF_BT) * ((N + PF_BF - 1) / PF_BF); }
+static size_t pf_counter_bytes(size_t M, size_t N) { return align_up(pf_tiles(M, N) * 8, 256); }   // claimed, published
+static size_t pf_grid(size_t M, size_t K, size_t N)
+{
+    const size_t units = pf_tiles(M, N) * (K / PF_BK);
+    const size_t sms = (size_t)device_sm_count();
+    return units < sms ? units : sms;
+}
+
 size_t prefill_workspace_bytes(size_t M, size_t K, size_t N)
 {
-    (void)N;
-    return pf_q_bytes(M, K) + 2 * pf_vec_bytes(M);   // int8 activations, fp32 scales, int32 row sums
+    // int8 activations, fp32 scales, int32 row sums, tile counters, two partial tiles per CTA
+    return pf_q_bytes(M, K) + 2 * pf_vec_bytes(M) + pf_counter_bytes(M, N) + 2 * pf_grid(M, K, N) * PF_SLOT_BYTES;
 }
 
 static bitnet_status_t encode_map(CUtensorMap *map, const void *base, uint64_t inner, uint64_t rows, uint64_t row_stride_bytes,
-                                  uint32_t box_inner, uint32_t box_rows, CUtensorMapSwizzle swizzle)
+                                  uint32_t box_inner, uint32_t box_rows, CUtensorMapSwizzle swizzle,
+                                  CUtensorMapDataType dtype = CU_TENSOR_MAP_DATA_TYPE_UINT8)
 {
     const cuuint64_t dims[2] = {inner, rows};
     const cuuint64_t strides[1] = {row_stride_bytes};
@@ -544,7 +802,7 @@ static bitnet_status_t encode_map(CUtensorMap *map, const void *base, uint64_t i
             return fail(BITNET_ERR_CUDA_DRIVER, "cuTensorMapEncodeTiled is not available from this driver");
         encode = reinterpret_cast<EncodeFn>(fn);
     }
-    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, elem,
+    const CUresult r = encode(map, dtype, 2, const_cast<void *>(base), dims, strides, box, elem,
                               CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(BITNET_ERR_CUDA_DRIVER, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
@@ -563,32 +821,47 @@ bitnet_status_t launch_prefill(const ForwardArgs &a, void *workspace, size_t wor
 
     char *ws = static_cast<char *>(workspace);
     int8_t *q_perm = reinterpret_cast<int8_t *>(ws);
-    float *a_scale = reinterpret_cast<float *>(ws + pf_q_bytes(a.M, a.K));
-    int *rowsum = reinterpret_cast<int *>(ws + pf_q_bytes(a.M, a.K) + pf_vec_bytes(a.M));
+    ws += pf_q_bytes(a.M, a.K);
+    float *a_scale = reinterpret_cast<float *>(ws);
+    ws += pf_vec_bytes(a.M);
+    int *rowsum = reinterpret_cast<int *>(ws);
+    ws += pf_vec_bytes(a.M);
+    unsigned *counters = reinterpret_cast<unsigned *>(ws);
+    ws += pf_counter_bytes(a.M, a.N);
+    int *slots = reinterpret_cast<int *>(ws);
 
-    quantize_rows_perm_kernel<<<(unsigned)a.M, 256, 0, stream>>>(a.x, a.K, q_perm, a_scale, rowsum, a.q_out, a.a_scale_out);
+    const int tiles = (int)pf_tiles(a.M, a.N);
+    quantize_rows_perm_kernel<<<(unsigned)a.M, 256, 0, stream>>>(a.x, a.K, q_perm, a_scale, rowsum, a.q_out, a.a_scale_out,
+                                                                  counters, 2 * tiles);
     BITNET_TRY(check_launch("quantize_rows_perm_kernel"));
 
-    CUtensorMap map_a, map_w;
-    BITNET_TRY(encode_map(&map_a, q_perm, a.K, a.M, a.K, PF_BK, PF_BM, CU_TENSOR_MAP_SWIZZLE_128B));
-    BITNET_TRY(encode_map(&map_w, a.wp, a.K / 4, a.N, a.K / 4, PF_BK / 4, PF_BN, CU_TENSOR_MAP_SWIZZLE_NONE));
+    CUtensorMap map_x, map_w, map_y;
+    BITNET_TRY(encode_map(&map_x, q_perm, a.K, a.M, a.K, PF_BK, PF_BT, CU_TENSOR_MAP_SWIZZLE_128B));
+    BITNET_TRY(encode_map(&map_w, a.wp, a.K / 4, a.N, a.K / 4, PF_BK / 4, PF_BF, CU_TENSOR_MAP_SWIZZLE_NONE));
 
     PrefillParams p = {};
     p.y = a.y; p.acc_out = a.acc_out; p.a_scale = a_scale; p.rowsum = rowsum; p.w_scale = a.w_scale;
+    p.slots = slots; p.counters = counters;
     p.M = (int)a.M; p.K = (int)a.K; p.N = (int)a.N; p.ldy = a.ldy ? a.ldy : a.N;
-    p.m_tiles = (int)((a.M + PF_BM - 1) / PF_BM);
-    p.n_tiles = (int)((a.N + PF_BN - 1) / PF_BN);
+    p.m_tiles = (int)((a.M + PF_BT - 1) / PF_BT);
+    p.n_tiles = (int)((a.N + PF_BF - 1) / PF_BF);
     p.k_tiles = (int)(a.K / PF_BK);
+    // y leaves through TMA when its rows are 16-byte aligned; any other output takes plain stores
+    p.tma_store = ((reinterpret_cast<uintptr_t>(a.y) & 15) == 0 && (p.ldy % 4) == 0) ? 1 : 0;
+    if (p.tma_store)
+        BITNET_TRY(encode_map(&map_y, a.y, a.N, a.M, p.ldy * 4, PF_BF, 32, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_DATA_TYPE_FLOAT32));
+    else
+        map_y = map_w;   // unused by the kernel
 
-    static bool attr_set = false;
-    if (!attr_set) {
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    BITNET_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
         BITNET_CUDA(cudaFuncSetAttribute(prefill_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM));
-        attr_set = true;
+        if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
-    const int tiles = p.m_tiles * p.n_tiles;
-    const int sms = device_sm_count();
-    const int grid = tiles < sms ? tiles : sms;
-    prefill_gemm_kernel<<<grid, PF_THREADS, PF_SMEM, stream>>>(map_a, map_w, p);
+    const int grid = (int)pf_grid(a.M, a.K, a.N);
+    prefill_gemm_kernel<<<grid, PF_THREADS, PF_SMEM, stream>>>(map_x, map_w, map_y, p);
     return check_launch("prefill_gemm_kernel");
 }
 
