@@ -362,21 +362,55 @@ constexpr unsigned PF_IDESC = (2u << 4) | (0u << 7) | (1u << 10) | ((unsigned)(P
 
 // The work of the whole GEMM is the sequence of (tile, k slice) units, tile-major; CTA c takes
 // the contiguous range [U*c/G, U*(c+1)/G), so every CTA has the same number of k slices whatever
-// the tile count.  A segment is the part of one tile inside a range.
+// the tile count.  A segment is the part of one tile inside a range.  A CTA works through its
+// segments in the order: first (often a partial tile), last (often a partial tile), then the whole
+// tiles in between -- the fix-up of a tile shared with a neighbour then happens early on both
+// sides and hides behind the MMAs of the whole tiles, and the kernel's tail is a plain tile.
 struct PfSegment {
     int tile, kb, ke;
 };
-__device__ __forceinline__ long long pf_range_start(long long units, int c, int ctas) { return units * c / ctas; }
-__device__ __forceinline__ bool pf_next_segment(long long &u, long long u_end, int k_tiles, PfSegment &sg)
+struct PfSchedule {
+    int t_first, kb_first;   // tile and k position of the range's first unit
+    int t_last, ke_last;     // tile of the range's last unit, end of its k range
+    int n_seg;
+};
+__device__ __forceinline__ long long pf_range_start(long long units, int c, int ctas)
 {
-    if (u >= u_end) return false;
-    sg.tile = (int)(u / k_tiles);
-    sg.kb = (int)(u - (long long)sg.tile * k_tiles);
-    const long long rest = u_end - u;
-    const int left = k_tiles - sg.kb;
-    sg.ke = sg.kb + (int)(rest < left ? rest : left);
-    u += sg.ke - sg.kb;
-    return true;
+    // 32-bit arithmetic when it fits (the usual case): 64-bit division is slow on the device
+    if (units < (1ll << 31) / (ctas > 0 ? ctas : 1)) return (long long)((unsigned)units * (unsigned)c / (unsigned)ctas);
+    return units * c / ctas;
+}
+__device__ __forceinline__ PfSchedule pf_schedule(long long u_begin, long long u_end, int k_tiles)
+{
+    PfSchedule sch;
+    sch.n_seg = 0;
+    sch.t_first = sch.kb_first = sch.t_last = sch.ke_last = 0;
+    if (u_end <= u_begin) return sch;
+    if (u_end < (1ll << 31)) {
+        sch.t_first = (int)((unsigned)u_begin / (unsigned)k_tiles);
+        sch.t_last = (int)((unsigned)(u_end - 1) / (unsigned)k_tiles);
+    } else {
+        sch.t_first = (int)(u_begin / k_tiles);
+        sch.t_last = (int)((u_end - 1) / k_tiles);
+    }
+    sch.kb_first = (int)(u_begin - (long long)sch.t_first * k_tiles);
+    sch.ke_last = (int)(u_end - (long long)sch.t_last * k_tiles);
+    sch.n_seg = sch.t_last - sch.t_first + 1;
+    return sch;
+}
+__device__ __forceinline__ PfSegment pf_segment(const PfSchedule &sch, int idx, int k_tiles)
+{
+    PfSegment sg;
+    if (sch.n_seg == 1) {
+        sg.tile = sch.t_first; sg.kb = sch.kb_first; sg.ke = sch.ke_last;
+    } else if (idx == 0) {
+        sg.tile = sch.t_first; sg.kb = sch.kb_first; sg.ke = k_tiles;
+    } else if (idx == 1) {
+        sg.tile = sch.t_last; sg.kb = 0; sg.ke = sch.ke_last;
+    } else {
+        sg.tile = sch.t_first + idx - 1; sg.kb = 0; sg.ke = k_tiles;
+    }
+    return sg;
 }
 
 __global__ void __launch_bounds__(PF_THREADS, 1)
@@ -424,6 +458,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     const long long u_begin = pf_range_start(units, (int)blockIdx.x, (int)gridDim.x);
     const long long u_end = pf_range_start(units, (int)blockIdx.x + 1, (int)gridDim.x);
     const int n_slices = (int)(u_end - u_begin);   // k slices of this CTA, numbered it = 0.. across its segments
+    const PfSchedule sch = pf_schedule(u_begin, u_end, p.k_tiles);
     // Slices are handed between the roles in pairs (pair pp = it / 2): one barrier round per pair
     // keeps the single MMA-issuing thread's waits and commits off the critical path.
 
@@ -431,29 +466,26 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         // ===================== TMA producer =====================
         if (lane == 0) {
             const int n_pairs = (n_slices + PF_PAIR - 1) / PF_PAIR;
-            // two cursors walk this CTA's slices (unit u_begin + it -> tile, k position) without
-            // divisions: one for the activations, one for the packed weights that run ahead
+            // two cursors walk this CTA's slices in segment order: one for the activations, one for
+            // the packed weights that run ahead
             struct Cursor {
-                int n_tile, m_tile, kt;
+                int idx, n_tile, m_tile, kt, ke;
             };
-            auto cursor_at = [&](long long uu) {
-                Cursor c;
-                const long long tile = uu / p.k_tiles;
-                c.kt = (int)(uu - tile * p.k_tiles);
-                c.n_tile = (int)(tile / p.m_tiles);
-                c.m_tile = (int)(tile - (long long)c.n_tile * p.m_tiles);
-                return c;
+            auto cursor_seg = [&](Cursor &c, int idx) {
+                c.idx = idx;
+                if (idx >= sch.n_seg) return;
+                const PfSegment sg = pf_segment(sch, idx, p.k_tiles);
+                c.n_tile = sg.tile / p.m_tiles;
+                c.m_tile = sg.tile - c.n_tile * p.m_tiles;
+                c.kt = sg.kb;
+                c.ke = sg.ke;
             };
             auto advance = [&](Cursor &c) {
-                if (++c.kt == p.k_tiles) {
-                    c.kt = 0;
-                    if (++c.m_tile == p.m_tiles) {
-                        c.m_tile = 0;
-                        ++c.n_tile;
-                    }
-                }
+                if (++c.kt == c.ke) cursor_seg(c, c.idx + 1);
             };
-            Cursor cx = cursor_at(u_begin), cw = cx;
+            Cursor cx, cw;
+            cursor_seg(cx, 0);
+            cw = cx;
             auto load_w = [&](int q) {   // packed weights of pair q (called for q = 0, 1, 2, ... in order)
                 const int cnt = n_slices - q * PF_PAIR < PF_PAIR ? n_slices - q * PF_PAIR : PF_PAIR;
                 if (cnt <= 0) return;
@@ -486,9 +518,8 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         if (lane == 0) {
             int it = 0, sc = 0;
             bool ok = true;
-            long long u = u_begin;
-            PfSegment sg;
-            while (ok && pf_next_segment(u, u_end, p.k_tiles, sg)) {
+            for (int si = 0; si < sch.n_seg && ok; ++si) {
+                const PfSegment sg = pf_segment(sch, si, p.k_tiles);
                 const int buf = sc & 1;
                 const unsigned acc_ph = (unsigned)(sc >> 1) & 1u;
                 ++sc;
@@ -499,10 +530,8 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     const int s = it % PF_XSTAGES;
                     const int pp = it / PF_PAIR, h = it % PF_PAIR;
                     if (h == 0) {   // the pair's expanded weights are in tensor memory and its activations have landed
-                        PF_TS(8, pp);
+                        // (the expanders wait for the pair's activations before they report, so one wait covers both)
                         if (!pf_mbar_wait(&s_full_a[pp % PF_ASLOTS], (unsigned)(pp / PF_ASLOTS) & 1u, false)) { ok = false; break; }
-                        PF_TS(9, pp);
-                        if (!pf_mbar_wait(&s_full_x[pp % PF_RING], (unsigned)(pp / PF_RING) & 1u, false)) { ok = false; break; }
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                         PF_TS(4, pp);
                     }
@@ -559,11 +588,14 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             }
             if (row == 0) PF_TS(2, pp);
             const unsigned ta = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(PF_TMEM_A0 + slot * PF_PAIR * PF_A_COLS);
+#ifndef PF_DBG_NOEXP
             pf_tmem_st32(ta, r[0]);
             if (pp * PF_PAIR + 1 < n_slices) pf_tmem_st32(ta + PF_A_COLS, r[1]);
+#endif
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
+            // report the pair only when its activations have landed too: the MMA thread then needs one wait
+            if (!pf_warp_wait(&s_full_x[pp % PF_RING], (unsigned)(pp / PF_RING) & 1u)) { ok = false; break; }
             if (lane == 0) pf_mbar_arrive(&s_full_a[slot]);
             if (row == 0) PF_TS(3, pp);
         }
@@ -579,8 +611,6 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         unsigned char *out_stage = smem + PF_RING_BYTES;
         int sc = 0, n_staged = 0;
         bool ok = true;
-        long long u = u_begin;
-        PfSegment sg;
 
         // stage one chunk (the thread's 32 values, raw bits) and send it: to y through the tensor map
         // (tile coordinates x, yrow) or to a contiguous 16 KB piece of a partial-sum slot
@@ -604,7 +634,8 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             }
         };
 
-        while (ok && pf_next_segment(u, u_end, p.k_tiles, sg)) {
+        for (int si = 0; si < sch.n_seg && ok; ++si) {
+            const PfSegment sg = pf_segment(sch, si, p.k_tiles);
             const int n_tile = sg.tile / p.m_tiles, m_tile = sg.tile % p.m_tiles;
             const int buf = sc & 1;
             const unsigned acc_ph = (unsigned)(sc >> 1) & 1u;
@@ -629,6 +660,12 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             if (epi_leader) PF_TS(6, sc - 1);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)buf * PF_BT;
+#ifdef PF_DBG_NOEPI
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) pf_mbar_arrive(&s_acc_empty[buf]);
+            continue;
+#endif
 
             // a tile that is split between CTAs: publish this part, and whoever completes the
             // tile's k range adds the published parts to its own (integer sums: order is irrelevant)
@@ -643,7 +680,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 finish = s_prev_count + len == (unsigned)p.k_tiles;
                 pf_epi_all(true);   // s_prev_count may be rewritten only after everyone has read it
                 if (!finish) {
-                    const long long my_first_tile = u_begin / p.k_tiles;
+                    const int my_first_tile = sch.t_first;
                     int *slot = p.slots + ((size_t)2 * blockIdx.x + (sg.tile != my_first_tile ? 1 : 0)) * (PF_BF * PF_BT);
 #pragma unroll 1
                     for (int c = 0; c < PF_BT / 32; ++c) {
@@ -769,8 +806,9 @@ static size_t pf_tiles(size_t M, size_t N) { return ((M + PF_BT - 1) / PF_BT) * 
 static size_t pf_counter_bytes(size_t M, size_t N) { return align_up(pf_tiles(M, N) * 8, 256); }   // claimed, published
 static size_t pf_grid(size_t M, size_t K, size_t N)
 {
-    const size_t units = pf_tiles(M, N) * (K / PF_BK);
+    const size_t tiles = pf_tiles(M, N), units = tiles * (K / PF_BK);
     const size_t sms = (size_t)device_sm_count();
+    if (tiles <= sms) return tiles;   // one whole tile per CTA: nothing to split, no fix-up
     return units < sms ? units : sms;
 }
 
