@@ -37,8 +37,9 @@ constexpr int PF_BT = 192;                         // tokens per tile (the MMA's
 constexpr int PF_BK = 128;                         // k per slice (bytes of int8)
 constexpr int PF_PAIR = 2;                         // k slices per hand-over between the roles (one barrier round per pair)
 constexpr int PF_RING = 3;                         // activation pairs in flight (the ring holds PF_RING * PF_PAIR slices)
-constexpr int PF_WRING = 6;                        // packed-weight pairs in flight: twice as far ahead, so that a pair's
-                                                   // weights are expanded before its activations land
+constexpr int PF_WLEAD = 2;                        // the packed weights run this many pairs ahead of the activations, so
+                                                   // that a pair's weights are expanded before its activations land
+constexpr int PF_WRING = PF_RING + PF_WLEAD;       // packed-weight pairs in flight
 constexpr int PF_XSTAGES = PF_RING * PF_PAIR, PF_WSTAGES = PF_WRING * PF_PAIR;
 constexpr int PF_ASLOTS = 2;                       // expanded-weight pairs in tensor memory
 constexpr int PF_X_BYTES = PF_BT * PF_BK;          // 24 KB
@@ -50,7 +51,8 @@ constexpr unsigned PF_WAIT_LIMIT = 1u << 20;
 constexpr int PF_TMEM_A0 = 2 * PF_BT;              // tensor-memory columns: two accumulators, then the weight ring
 constexpr int PF_A_COLS = PF_BK / 4;               // 32 columns hold 128 bytes of k per lane
 static_assert(PF_TMEM_A0 + PF_ASLOTS * PF_PAIR * PF_A_COLS <= 512, "tensor memory has 512 columns");
-constexpr int PF_OUT_BYTES = 32 * PF_BF * 4;        // epilogue staging: 32 tokens x 128 features fp32, two of them
+constexpr int PF_WARP_OUT_BYTES = 32 * 32 * 4;     // epilogue staging per warp: 32 tokens x 32 features fp32, two of them
+constexpr int PF_OUT_BYTES = 4 * PF_WARP_OUT_BYTES;
 constexpr size_t PF_RING_BYTES = (size_t)PF_XSTAGES * PF_X_BYTES + (size_t)PF_WSTAGES * PF_WP_BYTES;
 constexpr size_t PF_SMEM = PF_RING_BYTES + 2 * PF_OUT_BYTES + 1024;   // + alignment slack
 constexpr size_t PF_SLOT_BYTES = (size_t)PF_BF * PF_BT * 4;   // one partial accumulator tile
@@ -425,7 +427,8 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     __shared__ __align__(8) unsigned long long s_acc_full[2], s_acc_empty[2];
     __shared__ unsigned s_tmem_base;
     __shared__ unsigned s_prev_count;
-    __shared__ __align__(16) int2 s_tab[PF_BT];   // per token of the tile: row sum, scale bits
+    __shared__ __align__(16) int2 s_tab[4 * PF_BT];   // per epilogue warp, per token of the tile: row sum, scale bits
+    __shared__ __align__(8) unsigned long long s_in[4];   // per epilogue warp: a fetched part of a split tile has landed
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(pf_smem_raw) + 1023) & ~uintptr_t(1023));
@@ -438,6 +441,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         for (int r = 0; r < PF_WRING; ++r) pf_mbar_init(&s_full_w[r], 1);
         for (int sa = 0; sa < PF_ASLOTS; ++sa) pf_mbar_init(&s_full_a[sa], PF_EXP_WARPS / PF_GROUPS);
         for (int r = 0; r < PF_RING; ++r) pf_mbar_init(&s_done[r], 1);
+        for (int w = 0; w < 4; ++w) pf_mbar_init(&s_in[w], 1);
         for (int b = 0; b < 2; ++b) {
             pf_mbar_init(&s_acc_full[b], 1);
             pf_mbar_init(&s_acc_empty[b], 4);
@@ -496,11 +500,11 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     advance(cw);
                 }
             };
-            for (int q = 0; q < PF_RING; ++q) load_w(q);
+            for (int q = 0; q < PF_WLEAD; ++q) load_w(q);
             for (int pp = 0; pp < n_pairs; ++pp) {
                 const int cnt = n_slices - pp * PF_PAIR < PF_PAIR ? n_slices - pp * PF_PAIR : PF_PAIR;
                 // the pair that used these stages PF_RING pairs ago has been consumed; its packed
-                // weights (PF_WRING pairs behind the ones loaded now) as well
+                // weights (PF_WRING pairs behind the ones loaded below) as well
                 PF_TS(0, pp);
                 if (!pf_mbar_wait(&s_done[pp % PF_RING], ((unsigned)(pp / PF_RING) & 1u) ^ 1u, false)) break;
                 PF_TS(1, pp);
@@ -510,7 +514,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                                    &s_full_x[pp % PF_RING]);
                     advance(cx);
                 }
-                load_w(pp + PF_RING);
+                load_w(pp + PF_WLEAD);
             }
         }
     } else if (warp == 1) {
@@ -600,38 +604,77 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             if (row == 0) PF_TS(3, pp);
         }
     } else {
-        // ===================== epilogue (128 threads; a thread owns one feature row of the accumulator) =====================
+        // ===================== epilogue (4 warps; a thread owns one feature row of the accumulator) =====================
         // Accumulator lanes are features, columns are tokens, so a warp's 32 lanes hold 32 consecutive
-        // features of one token: chunks of 32 tokens x 128 features go through a shared-memory staging
-        // buffer ([token][feature], conflict-free) and leave as one TMA store each.
+        // features of one token.  Each warp works on its own: a chunk of 32 tokens x 32 features goes
+        // through the warp's private staging buffer ([token][feature], conflict-free) and leaves as one
+        // TMA store; no barrier between the warps inside a tile.
         const int quarter = warp & 3;   // the tensor-memory lanes a warp may touch: 32 * (warp % 4)
         const int frow = quarter * 32 + lane;
-        const int et = tid - (2 + PF_EXP_WARPS) * 32;
-        const bool epi_leader = et == 0;
-        unsigned char *out_stage = smem + PF_RING_BYTES;
-        int sc = 0, n_staged = 0;
+        const bool epi_leader = tid == (2 + PF_EXP_WARPS) * 32;
+        unsigned char *my_stage = smem + PF_RING_BYTES + (size_t)quarter * (2 * PF_WARP_OUT_BYTES);   // two 4 KB buffers
+        int sc = 0, n_staged = 0, n_in = 0;
         bool ok = true;
 
-        // stage one chunk (the thread's 32 values, raw bits) and send it: to y through the tensor map
-        // (tile coordinates x, yrow) or to a contiguous 16 KB piece of a partial-sum slot
-        auto send_chunk = [&](const unsigned (&v)[32], bool to_y, int x, int yrow, int *slot_piece) {
-            unsigned *st = reinterpret_cast<unsigned *>(out_stage + (size_t)(n_staged & 1) * PF_OUT_BYTES);
+        // the copy that read buffer (n_staged & 1) two sends ago has finished reading: lane 0 waited for it
+        // right after the previous send, and the __syncwarp orders that before everybody's stores
+        auto send_chunk = [&](const unsigned (&v)[32], int x, int yrow) {   // token-major, to y
+            unsigned *st = reinterpret_cast<unsigned *>(my_stage + (size_t)(n_staged & 1) * PF_WARP_OUT_BYTES);
             ++n_staged;
-            pf_epi_all(true);   // the leader has seen the copy that last read this buffer finish reading
+            __syncwarp();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) st[j * PF_BF + frow] = v[j];
+            for (int j = 0; j < 32; ++j) st[j * 32 + lane] = v[j];
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            pf_epi_all(true);
-            if (epi_leader) {
-                if (to_y)
-                    pf_tma_store_2d(&map_y, x, yrow, st);
-                else
-                    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(slot_piece),
-                                 "r"(pf_smem_u32(st)), "r"(PF_OUT_BYTES)
-                                 : "memory");
+            __syncwarp();
+            if (lane == 0) {
+                pf_tma_store_2d(&map_y, x, yrow, st);
                 asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");   // the other buffer is free again
             }
+        };
+        // a part of a split tile goes to its slot feature-major: the thread's 32 values are 128
+        // contiguous bytes (16-byte pieces XOR-swizzled so that the shared-memory accesses do not
+        // collide); a warp's 32 rows are 4 KB contiguous in the slot
+        auto send_partial = [&](const unsigned (&v)[32], int *slot_piece) {
+            unsigned char *st = my_stage + (size_t)(n_staged & 1) * PF_WARP_OUT_BYTES;
+            ++n_staged;
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                *reinterpret_cast<uint4 *>(st + lane * 128 + ((i ^ (lane & 7)) << 4)) = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+                asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(slot_piece + quarter * 32 * 32),
+                             "r"(pf_smem_u32(st)), "r"(PF_WARP_OUT_BYTES)
+                             : "memory");
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            }
+        };
+        // fetch this warp's 4 KB of another CTA's part into the staging buffer that is free, add it to v
+        auto add_partial = [&](unsigned (&v)[32], const int *slot_piece) -> bool {
+            unsigned char *st = my_stage + (size_t)(n_staged & 1) * PF_WARP_OUT_BYTES;
+            __syncwarp();   // lane 0 has seen the last copy out of this buffer finish reading
+            if (lane == 0) {
+                pf_mbar_expect_tx(&s_in[quarter], PF_WARP_OUT_BYTES);
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                 pf_smem_u32(st)),
+                             "l"(slot_piece + quarter * 32 * 32), "r"(PF_WARP_OUT_BYTES), "r"(pf_smem_u32(&s_in[quarter]))
+                             : "memory");
+            }
+            const bool got = pf_warp_wait(&s_in[quarter], (unsigned)n_in & 1u);
+            ++n_in;
+            if (!got) return false;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const uint4 t = *reinterpret_cast<const uint4 *>(st + lane * 128 + ((i ^ (lane & 7)) << 4));
+                v[4 * i + 0] += t.x;
+                v[4 * i + 1] += t.y;
+                v[4 * i + 2] += t.z;
+                v[4 * i + 3] += t.w;
+            }
+            return true;
         };
 
         for (int si = 0; si < sch.n_seg && ok; ++si) {
@@ -644,16 +687,18 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             const int m0 = m_tile * PF_BT;
             const int n = n_tile * PF_BF + frow;
             const bool n_ok = n < p.N;
-            // per token of the tile: row sum and scale, read back below as broadcast 16-byte loads
-            pf_epi_all(true);   // nobody reads the previous tile's table any more
-            for (int j = et; j < PF_BT; j += 128) {
+            // per token of the tile: row sum and scale (each warp keeps its own copy), read back below as
+            // broadcast 16-byte loads
+            int2 *tab = s_tab + quarter * PF_BT;
+            __syncwarp();
+            for (int j = lane; j < PF_BT; j += 32) {
                 const int m = m0 + j;
                 int2 e = make_int2(0, 0);
                 if (m < p.M) {
                     e.x = __ldg(p.rowsum + m);
                     e.y = __float_as_int(__fmul_rn(p.w_scale, __ldg(p.a_scale + m)));
                 }
-                s_tab[j] = e;
+                tab[j] = e;
             }
             ok = pf_epi_all(pf_warp_wait(&s_acc_full[buf], acc_ph));   // the four warps go on, or give up, together
             if (!ok) break;
@@ -680,18 +725,21 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 finish = s_prev_count + len == (unsigned)p.k_tiles;
                 pf_epi_all(true);   // s_prev_count may be rewritten only after everyone has read it
                 if (!finish) {
-                    const int my_first_tile = sch.t_first;
-                    int *slot = p.slots + ((size_t)2 * blockIdx.x + (sg.tile != my_first_tile ? 1 : 0)) * (PF_BF * PF_BT);
+                    int *slot = p.slots + ((size_t)2 * blockIdx.x + (sg.tile != sch.t_first ? 1 : 0)) * (PF_BF * PF_BT);
 #pragma unroll 1
                     for (int c = 0; c < PF_BT / 32; ++c) {
                         unsigned r[32];
                         pf_tmem_ld32(taddr + (unsigned)c * 32, r);
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                        send_chunk(r, false, 0, 0, slot + c * 32 * PF_BF);
+                        send_partial(r, slot + c * 32 * PF_BF);
                     }
-                    if (epi_leader) {
-                        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // the slot is written
+                    if (lane == 0) {
+                        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // this warp's pieces are written
                         asm volatile("fence.proxy.async;" ::: "memory");
+                        __threadfence();
+                    }
+                    pf_epi_all(true);
+                    if (epi_leader) {
                         __threadfence();
                         atomicAdd(p.counters + 2 * sg.tile + 1, len);
                     }
@@ -716,9 +764,9 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 }
             }
             if (finish) {
-#pragma unroll
+#pragma unroll 1
                 for (int c = 0; c < PF_BT / 32; ++c) {
-                    if (m0 + c * 32 >= p.M) break;   // warp-uniform, and the same in all four warps
+                    if (m0 + c * 32 >= p.M) break;   // warp-uniform
                     unsigned r[32];
                     pf_tmem_ld32(taddr + (unsigned)c * 32, r);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -727,19 +775,14 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                         const long long t_begin = (long long)sg.tile * p.k_tiles, t_end = t_begin + p.k_tiles;
                         const long long cb = pf_range_start(units, cc, (int)gridDim.x), ce = pf_range_start(units, cc + 1, (int)gridDim.x);
                         if ((cb > t_begin ? cb : t_begin) >= (ce < t_end ? ce : t_end)) continue;   // an empty range
-                        const int *src = p.slots + ((size_t)2 * cc + (sg.tile != cb / p.k_tiles ? 1 : 0)) * (PF_BF * PF_BT) +
-                                         (c * 32) * PF_BF + frow;
-                        int t[32];   // all loads first: issued in order, a load next to its use would expose its latency
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) t[j] = __ldcg(src + j * PF_BF);
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) r[j] += (unsigned)t[j];
+                        const int *piece = p.slots + ((size_t)2 * cc + (sg.tile != (int)(cb / p.k_tiles) ? 1 : 0)) * (PF_BF * PF_BT) + (c * 32) * PF_BF;
+                        if (!add_partial(r, piece)) break;
                     }
                     const int m_left = p.M - (m0 + c * 32);   // tokens of this chunk that exist
                     if (p.acc_out) {   // parity-test output of the integer sums; kept out of the loop below so that it stays branch-free
 #pragma unroll
                         for (int j = 0; j < 32; ++j)
-                            if (n_ok && j < m_left) p.acc_out[(size_t)(m0 + c * 32 + j) * p.ldy + n] = (int)r[j] - s_tab[c * 32 + j].x;
+                            if (n_ok && j < m_left) p.acc_out[(size_t)(m0 + c * 32 + j) * p.ldy + n] = (int)r[j] - tab[c * 32 + j].x;
                     }
                     // loads first, arithmetic after: the warp issues in order, so a load placed next to
                     // its use would expose its latency 32 times
@@ -747,7 +790,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     for (int h = 0; h < 2; ++h) {
                         int4 e[8];
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) e[i] = reinterpret_cast<const int4 *>(s_tab)[c * 16 + h * 8 + i];
+                        for (int i = 0; i < 8; ++i) e[i] = reinterpret_cast<const int4 *>(tab)[c * 16 + h * 8 + i];
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
                             const int j = h * 16 + 2 * i;
@@ -756,7 +799,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                         }
                     }
                     if (p.tma_store) {
-                        send_chunk(r, true, n_tile * PF_BF, m0 + c * 32, nullptr);
+                        send_chunk(r, n_tile * PF_BF + quarter * 32, m0 + c * 32);
                     } else {
                         float *ycol = p.y + (size_t)(m0 + c * 32) * p.ldy + n;
 #pragma unroll
@@ -770,7 +813,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             if (lane == 0) pf_mbar_arrive(&s_acc_empty[buf]);
             if (epi_leader) PF_TS(7, sc - 1);
         }
-        if (epi_leader) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // shared memory outlives the stores
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // shared memory outlives the stores
     }
 
     // everyone meets here, also after a wait that gave up, so that tensor memory is always freed
@@ -887,7 +930,7 @@ bitnet_status_t launch_prefill(const ForwardArgs &a, void *workspace, size_t wor
     // y leaves through TMA when its rows are 16-byte aligned; any other output takes plain stores
     p.tma_store = ((reinterpret_cast<uintptr_t>(a.y) & 15) == 0 && (p.ldy % 4) == 0) ? 1 : 0;
     if (p.tma_store)
-        BITNET_TRY(encode_map(&map_y, a.y, a.N, a.M, p.ldy * 4, PF_BF, 32, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_DATA_TYPE_FLOAT32));
+        BITNET_TRY(encode_map(&map_y, a.y, a.N, a.M, p.ldy * 4, 32, 32, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_DATA_TYPE_FLOAT32));
     else
         map_y = map_w;   // unused by the kernel
 
