@@ -24,6 +24,7 @@
 // The reference has no tensor-core kernel; this is what its BitLinearLayer::forward
 // (transformer_layers.rs:119-202) computes for a [B*S, K] input.
 #include <cuda.h>
+#include <cstdlib>
 
 #include "common.cuh"
 
@@ -80,7 +81,10 @@ __global__ void __launch_bounds__(256) quantize_rows_perm_kernel(const float *__
                                                                  float *__restrict__ a_scale_out, unsigned *__restrict__ counters,
                                                                  int n_counters)
 {
-    // the GEMM that follows counts the parts of split tiles in these; they start at zero
+    // the GEMM that follows may start (allocate tensor memory, fetch packed weights) while this runs;
+    // it waits for this grid before it touches anything written here
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // the GEMM counts the parts of split tiles in these; they start at zero
     if (blockIdx.x == 0)
         for (int i = threadIdx.x; i < n_counters; i += 256) counters[i] = 0u;
     __shared__ unsigned s_key[8];
@@ -357,10 +361,12 @@ struct PrefillParams {
     size_t ldy;
     int m_tiles, n_tiles, k_tiles;
     int tma_store;       // y can be written with TMA (16-byte aligned rows), else plain stores
+    int bt;              // tokens per tile (the MMA's N): a multiple of 32, at most PF_BT
+    int whole_tiles;     // ranges end on tile boundaries (no tile is split between CTAs)
 };
 
 // instruction descriptor: D = s32, A = u8 (codes, tensor memory), B = s8 (activations, K-major), N = tokens, M = 128
-constexpr unsigned PF_IDESC = (2u << 4) | (0u << 7) | (1u << 10) | ((unsigned)(PF_BT >> 3) << 17) | ((unsigned)(PF_BF >> 4) << 24);
+__host__ __device__ constexpr unsigned pf_idesc(int bt) { return (2u << 4) | (0u << 7) | (1u << 10) | ((unsigned)(bt >> 3) << 17) | ((unsigned)(PF_BF >> 4) << 24); }
 
 // The work of the whole GEMM is the sequence of (tile, k slice) units, tile-major; CTA c takes
 // the contiguous range [U*c/G, U*(c+1)/G), so every CTA has the same number of k slices whatever
@@ -376,8 +382,12 @@ struct PfSchedule {
     int t_last, ke_last;     // tile of the range's last unit, end of its k range
     int n_seg;
 };
-__device__ __forceinline__ long long pf_range_start(long long units, int c, int ctas)
+__device__ __forceinline__ long long pf_range_start(long long units, int c, int ctas, int k_tiles = 0)
 {
+    if (k_tiles > 0) {   // whole tiles only: split the tile count, not the slice count
+        const unsigned tiles = (unsigned)(units / k_tiles);
+        return (long long)(unsigned)((unsigned long long)tiles * (unsigned)c / (unsigned)ctas) * k_tiles;
+    }
     // 32-bit arithmetic when it fits (the usual case): 64-bit division is slow on the device
     if (units < (1ll << 31) / (ctas > 0 ? ctas : 1)) return (long long)((unsigned)units * (unsigned)c / (unsigned)ctas);
     return units * c / ctas;
@@ -459,8 +469,9 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     if (tid == 0) PF_TS(15, 0);
 
     const long long units = (long long)p.m_tiles * p.n_tiles * p.k_tiles;
-    const long long u_begin = pf_range_start(units, (int)blockIdx.x, (int)gridDim.x);
-    const long long u_end = pf_range_start(units, (int)blockIdx.x + 1, (int)gridDim.x);
+    const int whole_k = p.whole_tiles ? p.k_tiles : 0;
+    const long long u_begin = pf_range_start(units, (int)blockIdx.x, (int)gridDim.x, whole_k);
+    const long long u_end = pf_range_start(units, (int)blockIdx.x + 1, (int)gridDim.x, whole_k);
     const int n_slices = (int)(u_end - u_begin);   // k slices of this CTA, numbered it = 0.. across its segments
     const PfSchedule sch = pf_schedule(u_begin, u_end, p.k_tiles);
     // Slices are handed between the roles in pairs (pair pp = it / 2): one barrier round per pair
@@ -501,6 +512,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 }
             };
             for (int q = 0; q < PF_WLEAD; ++q) load_w(q);
+            asm volatile("griddepcontrol.wait;" ::: "memory");   // the int8 activations come from the quantiser grid
             for (int pp = 0; pp < n_pairs; ++pp) {
                 const int cnt = n_slices - pp * PF_PAIR < PF_PAIR ? n_slices - pp * PF_PAIR : PF_PAIR;
                 // the pair that used these stages PF_RING pairs ago has been consumed; its packed
@@ -508,9 +520,17 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 PF_TS(0, pp);
                 if (!pf_mbar_wait(&s_done[pp % PF_RING], ((unsigned)(pp / PF_RING) & 1u) ^ 1u, false)) break;
                 PF_TS(1, pp);
-                pf_mbar_expect_tx(&s_full_x[pp % PF_RING], (unsigned)cnt * PF_X_BYTES);
+#ifdef PF_DBG_NOTMA
+                if (pp >= PF_RING) {
+                    pf_mbar_arrive(&s_full_x[pp % PF_RING]);
+                    for (int h = 0; h < cnt; ++h) advance(cx);
+                    load_w(pp + PF_WLEAD);
+                    continue;
+                }
+#endif
+                pf_mbar_expect_tx(&s_full_x[pp % PF_RING], (unsigned)cnt * (unsigned)(p.bt * PF_BK));
                 for (int h = 0; h < cnt; ++h) {
-                    pf_tma_load_2d(stage_x((pp * PF_PAIR + h) % PF_XSTAGES), &map_x, cx.kt * PF_BK, cx.m_tile * PF_BT,
+                    pf_tma_load_2d(stage_x((pp * PF_PAIR + h) % PF_XSTAGES), &map_x, cx.kt * PF_BK, cx.m_tile * p.bt,
                                    &s_full_x[pp % PF_RING]);
                     advance(cx);
                 }
@@ -522,6 +542,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         if (lane == 0) {
             int it = 0, sc = 0;
             bool ok = true;
+            const unsigned idesc = pf_idesc(p.bt);
             for (int si = 0; si < sch.n_seg && ok; ++si) {
                 const PfSegment sg = pf_segment(sch, si, p.k_tiles);
                 const int buf = sc & 1;
@@ -543,7 +564,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     const unsigned long long b_desc = pf_smem_desc(pf_smem_u32(stage_x(s)));
 #pragma unroll
                     for (int ks = 0; ks < PF_BK / 32; ++ks)   // 32 bytes of k per instruction: 8 columns / +2 16-byte units
-                        pf_mma_i8_ts(tmem_d, tmem_a + 8u * ks, b_desc + 2ull * ks, PF_IDESC, (kt != sg.kb || ks != 0) ? 1u : 0u);
+                        pf_mma_i8_ts(tmem_d, tmem_a + 8u * ks, b_desc + 2ull * ks, idesc, (kt != sg.kb || ks != 0) ? 1u : 0u);
                     if (h == PF_PAIR - 1 || it == n_slices - 1) {
                         pf_commit(&s_done[pp % PF_RING]);   // TMA stages and the tensor-memory slot of the pair are free
                         PF_TS(5, pp);
@@ -615,6 +636,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         unsigned char *my_stage = smem + PF_RING_BYTES + (size_t)quarter * (2 * PF_WARP_OUT_BYTES);   // two 4 KB buffers
         int sc = 0, n_staged = 0, n_in = 0;
         bool ok = true;
+        asm volatile("griddepcontrol.wait;" ::: "memory");   // row sums, scales and the zeroed counters come from the quantiser grid
 
         // the copy that read buffer (n_staged & 1) two sends ago has finished reading: lane 0 waited for it
         // right after the previous send, and the __syncwarp orders that before everybody's stores
@@ -684,14 +706,14 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             const unsigned acc_ph = (unsigned)(sc >> 1) & 1u;
             ++sc;
             const bool whole = sg.kb == 0 && sg.ke == p.k_tiles;
-            const int m0 = m_tile * PF_BT;
+            const int m0 = m_tile * p.bt;
             const int n = n_tile * PF_BF + frow;
             const bool n_ok = n < p.N;
             // per token of the tile: row sum and scale (each warp keeps its own copy), read back below as
             // broadcast 16-byte loads
             int2 *tab = s_tab + quarter * PF_BT;
             __syncwarp();
-            for (int j = lane; j < PF_BT; j += 32) {
+            for (int j = lane; j < p.bt; j += 32) {
                 const int m = m0 + j;
                 int2 e = make_int2(0, 0);
                 if (m < p.M) {
@@ -727,7 +749,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 if (!finish) {
                     int *slot = p.slots + ((size_t)2 * blockIdx.x + (sg.tile != sch.t_first ? 1 : 0)) * (PF_BF * PF_BT);
 #pragma unroll 1
-                    for (int c = 0; c < PF_BT / 32; ++c) {
+                    for (int c = 0; c < p.bt / 32; ++c) {
                         unsigned r[32];
                         pf_tmem_ld32(taddr + (unsigned)c * 32, r);
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -765,7 +787,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             }
             if (finish) {
 #pragma unroll 1
-                for (int c = 0; c < PF_BT / 32; ++c) {
+                for (int c = 0; c < p.bt / 32; ++c) {
                     if (m0 + c * 32 >= p.M) break;   // warp-uniform
                     unsigned r[32];
                     pf_tmem_ld32(taddr + (unsigned)c * 32, r);
@@ -845,20 +867,59 @@ bool prefill_supports(size_t M, size_t K, size_t N)
 static size_t pf_q_bytes(size_t M, size_t K) { return align_up(M * K, 256); }
 static size_t pf_vec_bytes(size_t M) { return align_up(M * 4, 256); }
 
-static size_t pf_tiles(size_t M, size_t N) { return ((M + PF_BT - 1) / PF_BT) * ((N + PF_BF - 1) / PF_BF); }
-static size_t pf_counter_bytes(size_t M, size_t N) { return align_up(pf_tiles(M, N) * 8, 256); }   // claimed, published
-static size_t pf_grid(size_t M, size_t K, size_t N)
+// How a problem is cut: tokens per tile, whether tiles may be split between CTAs, and the grid.
+struct PfPlan {
+    int bt;
+    bool whole_tiles;
+    size_t tiles, grid;
+};
+static size_t pf_tiles(size_t M, size_t N, int bt) { return ((M + bt - 1) / bt) * ((N + PF_BF - 1) / PF_BF); }
+// Estimated device cycles of a plan, from timings of the 2560/6912-wide projections at 2048 tokens:
+// a k slice costs about 700 cycles at 192 tokens per tile and only 27 % of that scales with the
+// tile's tokens; finishing a split tile costs about as much as 35 slices, so splitting pays only
+// when whole tiles would leave most of a wave idle.
+static double pf_plan_cost(size_t M, size_t K, size_t N, int bt, bool whole, size_t sms)
 {
-    const size_t tiles = pf_tiles(M, N), units = tiles * (K / PF_BK);
-    const size_t sms = (size_t)device_sm_count();
-    if (tiles <= sms) return tiles;   // one whole tile per CTA: nothing to split, no fix-up
-    return units < sms ? units : sms;
+    const double k = (double)(K / PF_BK), tiles = (double)pf_tiles(M, N, bt);
+    const double per_slice = 700.0 * (0.73 + 0.27 * bt / (double)PF_BT);
+    const double epilogue = 900.0 * (bt / 32);
+    if (tiles <= (double)sms) return k * per_slice + epilogue;
+    if (whole) return (double)((size_t)((tiles + sms - 1) / sms)) * k * per_slice + epilogue;
+    return tiles * k / (double)sms * per_slice + epilogue + 25000.0;
 }
+static PfPlan pf_plan(size_t M, size_t K, size_t N)
+{
+    const size_t sms = (size_t)device_sm_count();
+    static const int env_bt = getenv("BITNET_PREFILL_BT") ? atoi(getenv("BITNET_PREFILL_BT")) : 0;
+    static const int env_mode = getenv("BITNET_PREFILL_WHOLE") ? atoi(getenv("BITNET_PREFILL_WHOLE")) : -1;
+    PfPlan best = {};
+    double best_cost = 0.0;
+    for (int bt = PF_BT; bt >= 64; bt -= 32) {
+        if (env_bt >= 32 && env_bt <= PF_BT && env_bt % 32 == 0 && bt != env_bt) continue;
+        for (int whole = 1; whole >= 0; --whole) {
+            if (env_mode >= 0 && whole != (env_mode != 0)) continue;
+            const double cost = pf_plan_cost(M, K, N, bt, whole != 0, sms);
+            if (best.bt == 0 || cost < best_cost) {
+                best.bt = bt;
+                best.whole_tiles = whole != 0;
+                best_cost = cost;
+            }
+        }
+    }
+    if (best.bt == 0) { best.bt = PF_BT; best.whole_tiles = false; }
+    best.tiles = pf_tiles(M, N, best.bt);
+    const size_t units = best.tiles * (K / PF_BK);
+    if (best.tiles <= sms) { best.grid = best.tiles; best.whole_tiles = true; }
+    else best.grid = best.whole_tiles ? sms : (units < sms ? units : sms);
+    return best;
+}
+static size_t pf_counter_bytes(size_t M, size_t N) { return align_up(pf_tiles(M, N, 64) * 8, 256); }   // claimed, published (largest tile count)
 
 size_t prefill_workspace_bytes(size_t M, size_t K, size_t N)
 {
     // int8 activations, fp32 scales, int32 row sums, tile counters, two partial tiles per CTA
-    return pf_q_bytes(M, K) + 2 * pf_vec_bytes(M) + pf_counter_bytes(M, N) + 2 * pf_grid(M, K, N) * PF_SLOT_BYTES;
+    (void)K;
+    return pf_q_bytes(M, K) + 2 * pf_vec_bytes(M) + pf_counter_bytes(M, N) + 2 * (size_t)device_sm_count() * PF_SLOT_BYTES;
 }
 
 static bitnet_status_t encode_map(CUtensorMap *map, const void *base, uint64_t inner, uint64_t rows, uint64_t row_stride_bytes,
@@ -911,20 +972,23 @@ bitnet_status_t launch_prefill(const ForwardArgs &a, void *workspace, size_t wor
     ws += pf_counter_bytes(a.M, a.N);
     int *slots = reinterpret_cast<int *>(ws);
 
-    const int tiles = (int)pf_tiles(a.M, a.N);
+    const PfPlan plan = pf_plan(a.M, a.K, a.N);
+    const int tiles = (int)plan.tiles;
     quantize_rows_perm_kernel<<<(unsigned)a.M, 256, 0, stream>>>(a.x, a.K, q_perm, a_scale, rowsum, a.q_out, a.a_scale_out,
                                                                   counters, 2 * tiles);
     BITNET_TRY(check_launch("quantize_rows_perm_kernel"));
 
     CUtensorMap map_x, map_w, map_y;
-    BITNET_TRY(encode_map(&map_x, q_perm, a.K, a.M, a.K, PF_BK, PF_BT, CU_TENSOR_MAP_SWIZZLE_128B));
+    BITNET_TRY(encode_map(&map_x, q_perm, a.K, a.M, a.K, PF_BK, (uint32_t)plan.bt, CU_TENSOR_MAP_SWIZZLE_128B));
     BITNET_TRY(encode_map(&map_w, a.wp, a.K / 4, a.N, a.K / 4, PF_BK / 4, PF_BF, CU_TENSOR_MAP_SWIZZLE_NONE));
 
     PrefillParams p = {};
     p.y = a.y; p.acc_out = a.acc_out; p.a_scale = a_scale; p.rowsum = rowsum; p.w_scale = a.w_scale;
     p.slots = slots; p.counters = counters;
     p.M = (int)a.M; p.K = (int)a.K; p.N = (int)a.N; p.ldy = a.ldy ? a.ldy : a.N;
-    p.m_tiles = (int)((a.M + PF_BT - 1) / PF_BT);
+    p.bt = plan.bt;
+    p.whole_tiles = plan.whole_tiles ? 1 : 0;
+    p.m_tiles = (int)((a.M + plan.bt - 1) / plan.bt);
     p.n_tiles = (int)((a.N + PF_BF - 1) / PF_BF);
     p.k_tiles = (int)(a.K / PF_BK);
     // y leaves through TMA when its rows are 16-byte aligned; any other output takes plain stores
@@ -941,8 +1005,19 @@ bitnet_status_t launch_prefill(const ForwardArgs &a, void *workspace, size_t wor
         BITNET_CUDA(cudaFuncSetAttribute(prefill_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM));
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
-    const int grid = (int)pf_grid(a.M, a.K, a.N);
-    prefill_gemm_kernel<<<grid, PF_THREADS, PF_SMEM, stream>>>(map_x, map_w, map_y, p);
+    const int grid = (int)plan.grid;
+    // programmatic dependent launch: the GEMM's prologue and weight fetch overlap the quantiser's tail
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(PF_THREADS);
+    cfg.dynamicSmemBytes = PF_SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    BITNET_CUDA(cudaLaunchKernelEx(&cfg, prefill_gemm_kernel, map_x, map_w, map_y, p));
     return check_launch("prefill_gemm_kernel");
 }
 
