@@ -213,9 +213,17 @@ decode_kernel(const DecodeParams p)
     const int NS = p.stages;
     PHASE(0);
 
+#ifdef DEC_CONTIGUOUS_BLOCKS
     const int b0 = (int)((long long)blockIdx.x * p.n_blocks / gridDim.x);
     const int b1 = (int)((long long)(blockIdx.x + 1) * p.n_blocks / gridDim.x);
     const int nb = b1 - b0;
+    const int bstride = 1;
+#else
+    // blocks are dealt round-robin: every CTA's stream of 16-row blocks is spread over the whole
+    // weight matrix in the same way, so no CTA sits on a slower set of memory channels
+    const int b0 = (int)blockIdx.x, bstride = (int)gridDim.x;
+    const int nb = (p.n_blocks - b0 + bstride - 1) / bstride;
+#endif
     const unsigned row_bytes = (unsigned)p.K / 4;
 
     unsigned char *s_w = smem;
@@ -253,7 +261,7 @@ decode_kernel(const DecodeParams p)
                 } else if (i >= p.stages_free) {   // first use of a stage that overlaps the staging area
                     if (!mbar_wait(&s_bst_free, 0)) return;
                 }
-                const int row0 = (b0 + i) * 16;
+                const int row0 = (b0 + i * bstride) * 16;
                 const unsigned bytes = (unsigned)min(16, p.N - row0) * row_bytes;
                 mbar_arrive_expect_tx(&s_full[s], NW * bytes);
                 unsigned char *stage = s_w + (size_t)s * p.stage_stride;
@@ -482,7 +490,7 @@ decode_kernel(const DecodeParams p)
         const int s = i % NS;
         const unsigned parity = (unsigned)(i / NS) & 1u;
         if (!mbar_wait(&s_full[s], parity)) return;
-        const int blk = b0 + i;
+        const int blk = b0 + i * bstride;
         const int row_a = blk * 16 + g, row_b = row_a + 8;
         const unsigned char *stage = s_w + (size_t)s * p.stage_stride;
 

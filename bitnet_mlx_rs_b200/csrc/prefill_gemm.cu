@@ -93,7 +93,11 @@ __global__ void __launch_bounds__(256) quantize_rows_perm_kernel(const float *__
     const float *row = x + m * K;
     const int tid = threadIdx.x;
     const size_t n_groups = K / 16;
+#ifdef PF_DBG_NONRES
+    const bool resident = false;
+#else
     const bool resident = n_groups <= 512;   // two 16-wide groups per thread stay in registers
+#endif
 
     float4 f[2][4];
     unsigned key = 0;
