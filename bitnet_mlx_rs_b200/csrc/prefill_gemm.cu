@@ -3,18 +3,25 @@
 //   1. quantize_rows_perm_kernel: per-token absmax int8 quantisation of x[M,K] into scratch,
 //      with the 16 values of every 16-wide k group stored transposed (byte 4j+i holds k = 4i+j),
 //      plus the row sums sum_k q[m,k].
-//   2. prefill_gemm_kernel: persistent CTAs, one 128-token x 256-feature tile at a time.
-//        warp 0      TMA producer: the int8 activation tile (128 x 128 bytes, 128-byte swizzle) and
-//                    the PACKED weight tile (256 rows x 32 bytes) per 128-wide k slice
-//        warps 2-9   expand packed weights to int8 codes {0,1,2} in shared memory, straight into
-//                    the swizzled K-major layout the tensor core reads: (w >> 2j) & 0x03030303
-//                    yields the four bytes k = j, j+4, j+8, j+12 of a group, i.e. word j of the
-//                    transposed group order the activations were stored in
-//                    (two groups of four warps take the k slices in turn)
-//        warp 1      issues tcgen05.mma kind::i8 (M=128, N=256, K=32; s8 x u8 -> s32) with the
-//                    accumulator in tensor memory; two accumulators alternate between tiles
+//   2. prefill_gemm_kernel: persistent CTAs; the accumulator tile is 128 output features (tensor-memory
+//      lanes) x up to 192 tokens (columns), i.e. the weights are the MMA's A operand.
+//        warp 0      TMA producer: per 128-wide k slice the int8 activation tile (tokens x 128 bytes,
+//                    128-byte swizzle) and the PACKED weight tile (128 rows x 32 bytes); the packed
+//                    weights run two slice pairs ahead of the activations
+//        warps 2-9   expand packed weights to u8 codes {0,1,2} in registers and write them straight
+//                    into TENSOR MEMORY (tcgen05.st), where the MMA reads its A operand: a thread
+//                    owns one feature row; (w >> 2j) & 0x03030303 yields the four bytes
+//                    k = j, j+4, j+8, j+12 of a group, i.e. word j of the transposed group order the
+//                    activations were stored in.  Expanded weights never touch shared memory.
+//                    (two groups of four warps take the slice pairs in turn)
+//        warp 1      one thread issues tcgen05.mma kind::i8 (M=128, N=tokens, K=32; u8 x s8 -> s32),
+//                    A from tensor memory, B (activations) from shared memory; two accumulators
+//                    alternate between tiles
 //        warps 10-13 epilogue: tcgen05.ld the accumulator, subtract the row sum
-//                    (sum_k (code-1) q = sum_k code q - sum_k q), scale, store y
+//                    (sum_k (code-1) q = sum_k code q - sum_k q), scale, stage 32 x 32 blocks in
+//                    shared memory and write y with TMA stores
+//      Work is dealt in whole tiles, or -- when whole tiles would leave most of a wave idle -- in
+//      equal runs of k slices with an exact integer fix-up of the tiles shared by two CTAs.
 //      Every barrier wait is bounded; a wait that runs out raises an error flag and the CTA
 //      drains and frees its tensor memory.
 //
@@ -93,11 +100,7 @@ __global__ void __launch_bounds__(256) quantize_rows_perm_kernel(const float *__
     const float *row = x + m * K;
     const int tid = threadIdx.x;
     const size_t n_groups = K / 16;
-#ifdef PF_DBG_NONRES
-    const bool resident = false;
-#else
     const bool resident = n_groups <= 512;   // two 16-wide groups per thread stay in registers
-#endif
 
     float4 f[2][4];
     unsigned key = 0;
@@ -524,14 +527,6 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 PF_TS(0, pp);
                 if (!pf_mbar_wait(&s_done[pp % PF_RING], ((unsigned)(pp / PF_RING) & 1u) ^ 1u, false)) break;
                 PF_TS(1, pp);
-#ifdef PF_DBG_NOTMA
-                if (pp >= PF_RING) {
-                    pf_mbar_arrive(&s_full_x[pp % PF_RING]);
-                    for (int h = 0; h < cnt; ++h) advance(cx);
-                    load_w(pp + PF_WLEAD);
-                    continue;
-                }
-#endif
                 pf_mbar_expect_tx(&s_full_x[pp % PF_RING], (unsigned)cnt * (unsigned)(p.bt * PF_BK));
                 for (int h = 0; h < cnt; ++h) {
                     pf_tma_load_2d(stage_x((pp * PF_PAIR + h) % PF_XSTAGES), &map_x, cx.kt * PF_BK, cx.m_tile * p.bt,
@@ -617,10 +612,8 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             }
             if (row == 0) PF_TS(2, pp);
             const unsigned ta = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(PF_TMEM_A0 + slot * PF_PAIR * PF_A_COLS);
-#ifndef PF_DBG_NOEXP
             pf_tmem_st32(ta, r[0]);
             if (pp * PF_PAIR + 1 < n_slices) pf_tmem_st32(ta + PF_A_COLS, r[1]);
-#endif
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             // report the pair only when its activations have landed too: the MMA thread then needs one wait
@@ -731,12 +724,6 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             if (epi_leader) PF_TS(6, sc - 1);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)buf * PF_BT;
-#ifdef PF_DBG_NOEPI
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) pf_mbar_arrive(&s_acc_empty[buf]);
-            continue;
-#endif
 
             // a tile that is split between CTAs: publish this part, and whoever completes the
             // tile's k range adds the published parts to its own (integer sums: order is irrelevant)

@@ -72,3 +72,34 @@ def test_prefill_layer_shapes_at_2048_tokens(K, N):
     w = ops.unpack_ternary(dwp, N * K).reshape(N, K)
     colsum = w.sum(dim=0, dtype=torch.float64)
     assert torch.equal(dbg["acc"].sum(dim=1, dtype=torch.float64), dbg["q"].to(torch.float64) @ colsum)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("env", [{"BITNET_PREFILL_WHOLE": "0"}, {"BITNET_PREFILL_WHOLE": "0", "BITNET_PREFILL_BT": "64"},
+                                 {"BITNET_PREFILL_WHOLE": "1", "BITNET_PREFILL_BT": "96"}])
+def test_prefill_every_work_split(env):
+    """The planner's other modes (tiles split between CTAs with the integer fix-up, smaller token
+    tiles) give the same bits as the generic kernel.  The mode is read once per process, so each
+    case runs in a child process."""
+    import os
+    import subprocess
+    import sys
+    code = r'''
+import sys, torch
+sys.path.insert(0, ".")
+from bitnet_mlx_rs_b200 import ops
+g = torch.Generator(device="cuda").manual_seed(5)
+for (M, K, N) in [(2048, 2560, 640), (300, 1024, 384), (1000, 6912, 2560), (17, 128, 1), (256, 8192, 1024)]:
+    w = torch.randint(0, 256, (N * K // 4,), dtype=torch.uint8, device="cuda", generator=g)
+    ops.sanitize_packed(w)
+    x = torch.randn(M, K, device="cuda", generator=g)
+    y = ops.bitlinear_forward(w, 0.02, x, N, path="prefill")
+    ref = ops.bitlinear_forward(w, 0.02, x, N, path="generic")
+    assert torch.equal(y, ref), (M, K, N)
+assert ops.device_error_flags() == 0
+print("ok")
+'''
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, "-c", code], cwd=root, env=dict(os.environ, **env), capture_output=True, text=True,
+                         timeout=300)
+    assert out.returncode == 0 and "ok" in out.stdout, out.stdout + out.stderr
