@@ -338,9 +338,15 @@ def run_cuda(args):
                        "l2": "inputs larger than L2 (398 MB of packed weights per step)", "launch_mode": mode,
                        "parallelism": f"row-sharded x{world}, weights replicated, no collective"},
             "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
-                         "peak_kind": peak_kind, "traffic": None,
+                         "peak_kind": peak_kind,
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one gate/up launch at M = 1 from an ncu
+                         # capture of the same kernel (profiles/bench_ffn_decode_launch_list.md); its algorithmic
+                         # bytes are 8.89 MB, so nothing is read twice
+                         "traffic": 8923392,
                          "kernel": "decode_kernel (gate/up pair and down launches; algorithmic bytes per launch "
-                                   f"{step_bytes() / launches_per_step:.0f} on average)"},
+                                   f"{step_bytes() / launches_per_step:.0f} on average); achieved = bytes of the whole "
+                                   "step / CUDA-event time of the whole graph-replayed step (every launch in it is "
+                                   "this kernel or its quantiser)"},
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": io_bytes, "d2h_bytes_per_step": io_bytes,
                     "steps": e2e_steps, "api": "bitnet_backend_ffn_forward_host"},
             "gpu_launches": launches_per_step * args.steps,
