@@ -79,10 +79,13 @@ __device__ __forceinline__ int pf_quantize_fast(float x, float scale)
     return (t == t) ? (mag ^ neg) - neg : 0;
 }
 
-// One CTA per token row, one read of the row when it fits the registers (K <= 8192).
+// One CTA per token row, one read of the row when it fits the registers (two 16-wide groups per
+// thread).  Short rows take 128-thread CTAs: more rows in flight per SM, which is what bounds this
+// kernel (a row is one dependent chain load -> absmax -> quantise -> store).
 // q_perm[m, 16G + 4j + i] = q[m, 16G + 4i + j]; rowsum[m] = sum_k q[m,k].
 // Semantics: TernaryProcessor::quantize_activations (ternary_operations.rs:130-163).
-__global__ void __launch_bounds__(256) quantize_rows_perm_kernel(const float *__restrict__ x, size_t K,
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS, THREADS == 128 ? 8 : 4) quantize_rows_perm_kernel(const float *__restrict__ x, size_t K,
                                                                  int8_t *__restrict__ q_perm, float *__restrict__ a_scale,
                                                                  int *__restrict__ rowsum, int8_t *__restrict__ q_out,
                                                                  float *__restrict__ a_scale_out, unsigned *__restrict__ counters,
@@ -93,21 +96,21 @@ __global__ void __launch_bounds__(256) quantize_rows_perm_kernel(const float *__
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // the GEMM counts the parts of split tiles in these; they start at zero
     if (blockIdx.x == 0)
-        for (int i = threadIdx.x; i < n_counters; i += 256) counters[i] = 0u;
-    __shared__ unsigned s_key[8];
-    __shared__ int s_sum[8];
+        for (int i = threadIdx.x; i < n_counters; i += THREADS) counters[i] = 0u;
+    __shared__ unsigned s_key[THREADS / 32];
+    __shared__ int s_sum[THREADS / 32];
     const size_t m = blockIdx.x;
     const float *row = x + m * K;
     const int tid = threadIdx.x;
     const size_t n_groups = K / 16;
-    const bool resident = n_groups <= 512;   // two 16-wide groups per thread stay in registers
+    const bool resident = n_groups <= 2 * THREADS;   // two 16-wide groups per thread stay in registers
 
     float4 f[2][4];
     unsigned key = 0;
     if (resident) {
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
-            const size_t G = tid + u * 256;
+            const size_t G = tid + u * THREADS;
             if (G < n_groups) {
                 const float4 *src = reinterpret_cast<const float4 *>(row + G * 16);
 #pragma unroll
@@ -116,13 +119,13 @@ __global__ void __launch_bounds__(256) quantize_rows_perm_kernel(const float *__
         }
 #pragma unroll
         for (int u = 0; u < 2; ++u)
-            if ((size_t)(tid + u * 256) < n_groups) {
+            if ((size_t)(tid + u * THREADS) < n_groups) {
 #pragma unroll
                 for (int v = 0; v < 4; ++v)
                     key = max(max(key, abs_key(f[u][v].x)), max(abs_key(f[u][v].y), max(abs_key(f[u][v].z), abs_key(f[u][v].w))));
             }
     } else {
-        for (size_t G = tid; G < n_groups; G += 256) {
+        for (size_t G = tid; G < n_groups; G += THREADS) {
             const float4 *src = reinterpret_cast<const float4 *>(row + G * 16);
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
@@ -136,16 +139,16 @@ __global__ void __launch_bounds__(256) quantize_rows_perm_kernel(const float *__
     __syncthreads();
     key = 0;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) key = max(key, s_key[w]);
+    for (int w = 0; w < THREADS / 32; ++w) key = max(key, s_key[w]);
     const float absmax = __uint_as_float(key);
     const float scale = quant_scale(absmax);
     // a huge or tiny absmax makes the scale leave the normal range; the fast rounding assumes it has not
     const bool fast = scale >= 1e-30f && scale <= 1e30f;
 
     int sum = 0;
-    const size_t rounds = resident ? 2 : (n_groups + 255) / 256;
+    const size_t rounds = resident ? 2 : (n_groups + THREADS - 1) / THREADS;
     for (size_t u = 0; u < rounds; ++u) {
-        const size_t G = tid + u * 256;
+        const size_t G = tid + u * THREADS;
         if (G >= n_groups) break;
         float4 g4[4];
         if (resident) {
@@ -194,7 +197,7 @@ __global__ void __launch_bounds__(256) quantize_rows_perm_kernel(const float *__
     if (tid == 0) {
         int total = 0;
 #pragma unroll
-        for (int w = 0; w < 8; ++w) total += s_sum[w];
+        for (int w = 0; w < THREADS / 32; ++w) total += s_sum[w];
         rowsum[m] = total;
         a_scale[m] = dequant_scale(absmax);
         if (a_scale_out) a_scale_out[m] = dequant_scale(absmax);
@@ -965,8 +968,12 @@ bitnet_status_t launch_prefill(const ForwardArgs &a, void *workspace, size_t wor
 
     const PfPlan plan = pf_plan(a.M, a.K, a.N);
     const int tiles = (int)plan.tiles;
-    quantize_rows_perm_kernel<<<(unsigned)a.M, 256, 0, stream>>>(a.x, a.K, q_perm, a_scale, rowsum, a.q_out, a.a_scale_out,
-                                                                  counters, 2 * tiles);
+    if (a.K / 16 <= 256)
+        quantize_rows_perm_kernel<128><<<(unsigned)a.M, 128, 0, stream>>>(a.x, a.K, q_perm, a_scale, rowsum, a.q_out, a.a_scale_out,
+                                                                           counters, 2 * tiles);
+    else
+        quantize_rows_perm_kernel<256><<<(unsigned)a.M, 256, 0, stream>>>(a.x, a.K, q_perm, a_scale, rowsum, a.q_out, a.a_scale_out,
+                                                                           counters, 2 * tiles);
     BITNET_TRY(check_launch("quantize_rows_perm_kernel"));
 
     CUtensorMap map_x, map_w, map_y;
