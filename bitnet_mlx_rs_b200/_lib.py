@@ -25,7 +25,7 @@ FLAG_PDL = 1
 
 class ForwardOpts(C.Structure):
     _fields_ = [("path", i32), ("flags", u32), ("q_out_dev", vp), ("a_scale_out_dev", vp),
-                ("acc_out_dev", vp), ("ldy", sz), ("stages", i32), ("reserved", i32)]
+                ("acc_out_dev", vp), ("ldy", sz), ("stages", i32), ("n_peers", i32), ("y_peers_dev", vp * 8)]
 
 
 class DeviceInfo(C.Structure):

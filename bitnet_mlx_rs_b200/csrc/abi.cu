@@ -207,6 +207,17 @@ extern "C" bitnet_status_t bitnet_bitlinear_forward(const uint8_t *weights_dev, 
     a.acc_out = o.acc_out_dev; a.q_out = o.q_out_dev; a.a_scale_out = o.a_scale_out_dev;
     a.M = M; a.K = K; a.N = N; a.ldy = ldy; a.flags = o.flags; a.stages = o.stages;
     cudaStream_t s = as_stream(stream);
+    if (o.n_peers < 0 || o.n_peers > BITNET_MAX_PEERS)
+        return fail(BITNET_ERR_INVALID_CONFIG, "n_peers must be in 0..%d (got %d)", BITNET_MAX_PEERS, o.n_peers);
+    if (o.n_peers > 0) {
+        if (path != BITNET_PATH_DECODE)
+            return fail(BITNET_ERR_UNSUPPORTED_OPERATION, "peer outputs are written by the decode kernel only (M <= 16)");
+        for (int r = 0; r < o.n_peers; ++r) {
+            if (!o.y_peers_dev[r]) return fail(BITNET_ERR_NULL_POINTER, "y_peers_dev[%d] is null", r);
+            a.y_peers[r] = o.y_peers_dev[r];
+        }
+        a.n_peers = o.n_peers;
+    }
 
     switch (path) {
         case BITNET_PATH_DECODE: {

@@ -54,6 +54,9 @@ struct ForwardArgs {
     void *image_ws;
     size_t image_ws_bytes;
     bool force_split;    // quantise through the image even for a single token
+    // output-feature split over several GPUs: the epilogue stores to every one of these (decode kernel)
+    float *y_peers[8];
+    int n_peers;
 };
 
 bitnet_status_t launch_decode(const ForwardArgs &a, cudaStream_t stream);

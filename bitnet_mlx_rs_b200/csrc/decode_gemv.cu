@@ -84,6 +84,8 @@ struct DecodeParams {
     unsigned image_bytes;
     unsigned bst_offset; // where the activation staging area starts in dynamic shared memory
     unsigned red_offset; // where the K-split sums start
+    float *y_peers[8];   // output-feature split over several GPUs: every output goes to each of these
+    int n_peers;         // (own and peer memory, plain stores over NVLink); 0 = write y only
 };
 
 // ---- mbarrier / bulk-copy primitives ---------------------------------------------------------
@@ -592,7 +594,11 @@ decode_kernel(const DecodeParams p)
                         } else {
                             if (p.acc_out) p.acc_out[o] = tot[t][r];
                             out = __fmul_rn((float)tot[t][r], __fmul_rn(p.w_scale, s_ascale[m]));
-                            if (p.y) p.y[o] = out;
+                            if (p.n_peers) {   // this GPU's column slice, stored into every GPU's full-width output
+                                for (int pr = 0; pr < p.n_peers; ++pr) p.y_peers[pr][o] = out;
+                            } else if (p.y) {
+                                p.y[o] = out;
+                            }
                         }
                         if (p.amax_out) {
                             const unsigned key = abs_key(out);
@@ -916,6 +922,9 @@ bitnet_status_t launch_decode(const ForwardArgs &a, cudaStream_t stream)
     p.stages = a.stages;
     p.amax_in = a.amax_in; p.n_amax_in = a.n_amax_in; p.amax_out = a.amax_out;
     p.weights_first = (a.flags & BITNET_FLAG_PDL) ? 1 : 0;
+    p.n_peers = a.n_peers;
+    for (int r = 0; r < a.n_peers && r < 8; ++r) p.y_peers[r] = a.y_peers[r];
+    if (a.n_peers && dual) return fail(BITNET_ERR_UNSUPPORTED_OPERATION, "peer outputs are not available for the gate/up pair launch");
     const DecodePlan pl = decode_plan(a.M, a.K, a.N, dual);
 
     if (!in_i8 && a.image_ws && (a.force_split || use_split(a.M, a.K))) {

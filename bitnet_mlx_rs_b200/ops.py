@@ -10,7 +10,7 @@ import ctypes as C
 import torch
 
 from . import _lib as L
-from .cuda import IncompatibleShapes, UnsupportedDataType, check
+from .cuda import IncompatibleShapes, InvalidConfig, UnsupportedDataType, check
 
 PATHS = {"auto": L.PATH_AUTO, "decode": L.PATH_DECODE, "prefill": L.PATH_PREFILL, "generic": L.PATH_GENERIC}
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
@@ -48,15 +48,19 @@ def packed_len(n_values: int) -> int:
     return (n_values + 3) // 4
 
 
-def make_opts(path="auto", pdl=False, q_out=None, a_scale_out=None, acc_out=None, ldy=0, stages=0) -> L.ForwardOpts:
+def make_opts(path="auto", pdl=False, q_out=None, a_scale_out=None, acc_out=None, ldy=0, stages=0, y_peers=()) -> L.ForwardOpts:
+    """``y_peers``: device addresses (ints) of the output slice in every GPU's full-width output."""
+    if len(y_peers) > 8:
+        raise InvalidConfig(f"at most 8 peer outputs (got {len(y_peers)})")
+    peers = (C.c_void_p * 8)(*[C.c_void_p(int(p)) for p in y_peers])
     return L.ForwardOpts(PATHS[path] if isinstance(path, str) else path, L.FLAG_PDL if pdl else 0,
                          q_out.data_ptr() if q_out is not None else None,
                          a_scale_out.data_ptr() if a_scale_out is not None else None,
-                         acc_out.data_ptr() if acc_out is not None else None, ldy, stages, 0)
+                         acc_out.data_ptr() if acc_out is not None else None, ldy, stages, len(y_peers), peers)
 
 
 def bitlinear_forward(wp: torch.Tensor, w_scale: float, x: torch.Tensor, out_features: int, *, path="auto",
-                      pdl=False, debug=False, out: torch.Tensor | None = None, stages=0, stream=None):
+                      pdl=False, debug=False, out: torch.Tensor | None = None, stages=0, stream=None, ldy=0, y_peers=()):
     """y[M,N] = BitLinear(x[M,K]) with packed ternary weights ``wp`` (uint8, ceil(N*K/4) bytes).
 
     With ``debug=True`` also returns the int8 activations, per-token scales and int32
@@ -77,7 +81,7 @@ def bitlinear_forward(wp: torch.Tensor, w_scale: float, x: torch.Tensor, out_fea
         dbg = {"q": torch.empty((M, K), dtype=torch.int8, device=x.device),
                "a_scale": torch.empty((M,), dtype=torch.float32, device=x.device),
                "acc": torch.empty((M, N), dtype=torch.int32, device=x.device)}
-    opts = make_opts(path, pdl, dbg.get("q"), dbg.get("a_scale"), dbg.get("acc"), 0, stages)
+    opts = make_opts(path, pdl, dbg.get("q"), dbg.get("a_scale"), dbg.get("acc"), ldy, stages, y_peers)
     need = C.c_size_t()
     check(L.load().bitnet_bitlinear_workspace_size(M, K, N, opts.path, C.byref(need)))
     ws = _workspace(need.value, x.device)

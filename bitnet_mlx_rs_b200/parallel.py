@@ -68,9 +68,152 @@ class NSplitBitLinear:
         return gathered.view(self.world, M, n_local).permute(1, 0, 2).reshape(M, self.out_features)
 
 
+class FusedNSplitBitLinear:
+    """Output-feature-split BitLinear for decode shapes (M <= 16) without a collective: every rank's
+    kernel stores its column slice straight into ALL ranks' full-width outputs (plain peer stores
+    over NVLink from the kernel's epilogue), and a symmetric-memory barrier tells the ranks that the
+    slices have arrived.  The outputs live in torch symmetric memory, which maps every rank's
+    buffer into every process.  The barrier before the launch keeps a fast rank from overwriting an
+    output that a slow rank is still reading."""
+
+    def __init__(self, packed_full: torch.Tensor, scale: float, out_features: int, in_features: int, max_tokens: int = 16,
+                 group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import ops
+        self._ops = ops
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.world > 8:
+            raise ValueError("at most 8 ranks (one node)")
+        if max_tokens > 16:
+            raise ValueError("the fused output path covers decode shapes only (at most 16 tokens)")
+        self.out_features, self.in_features, self.scale, self.max_tokens = out_features, in_features, scale, max_tokens
+        self.packed, (self.r0, self.r1) = packed_row_slice(packed_full, out_features, in_features, self.world, self.rank)
+        self.packed = self.packed.contiguous()
+        if (self.r0 * 4) % 16:
+            raise ValueError("a rank's first column must be 16-byte aligned in the output row")
+        self.y = symm_mem.empty((max_tokens, out_features), dtype=torch.float32, device=packed_full.device)
+        self.handle = symm_mem.rendezvous(self.y, self.group)
+        # this rank's slice inside every rank's output
+        self.peer_ptrs = [int(ptr) + 4 * self.r0 for ptr in self.handle.buffer_ptrs]
+        self._unused = torch.empty((max_tokens, self.r1 - self.r0), dtype=torch.float32, device=packed_full.device)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """x [M,K] (replicated on every rank) -> y [M,N] (complete on every rank, a view of the shared output)."""
+        M = x.shape[0]
+        if M > self.max_tokens:
+            raise ValueError(f"{M} tokens > max_tokens {self.max_tokens}")
+        self.handle.barrier(channel=0)   # nobody still reads the previous result
+        self._ops.bitlinear_forward(self.packed, self.scale, x, self.r1 - self.r0, path="decode", out=self._unused[:M],
+                                    ldy=self.out_features, y_peers=self.peer_ptrs)
+        self.handle.barrier(channel=1)   # every rank's slice has landed everywhere
+        return self.y[:M]
+
+
 def row_sharded_forward(forward: Callable[[torch.Tensor], torch.Tensor], x_all: torch.Tensor, group=None) -> torch.Tensor:
     """Independent token rows: this rank's share of `x_all` through `forward`; no communication.
     Returns the local outputs (callers that need all rows on one rank gather them themselves)."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     b, e = shard_range(x_all.shape[0], world, rank)
     return forward(x_all[b:e].contiguous())
+
+
+def _bench_nsplit() -> None:
+    """Times the output-feature-split oversized layer (K = 8192, N = 28672, M in {1, 16, 256}) on the
+    ranks of this job: local column slice + all-gather, CUDA events, maximum over ranks.  Run as
+
+        python -m torch.distributed.run --nnodes=1 --nproc-per-node G --master-addr 127.0.0.1 \\
+            -m bitnet_mlx_rs_b200.parallel
+
+    Rank 0 prints one JSON line per token count."""
+    import json
+    import os
+
+    from . import ops
+
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    world, rank = dist.get_world_size(), dist.get_rank()
+    K, N = 8192, 28672
+    n_local = N // world
+    gen = torch.Generator(device="cuda").manual_seed(7)   # same weights on every rank; each keeps its slice
+    copies = max(2, -(-(160 << 20) // (n_local * K // 4)))   # rotate enough slices to exceed L2
+    layers, fulls = [], []
+    for _ in range(copies):
+        full = torch.randint(0, 256, (N * K // 4,), dtype=torch.uint8, device="cuda", generator=gen)
+        ops.sanitize_packed(full)
+        layers.append(NSplitBitLinear(full, 0.01, N, K))
+        fulls.append(full)
+    fused = [FusedNSplitBitLinear(l_full, 0.01, N, K) for l_full in fulls]
+    del fulls
+    for M in (1, 16, 256):
+        x = torch.randn((M, K), device="cuda", generator=gen)
+        if M <= 16:   # the same layer with the slices stored straight into every GPU's output
+            for i in range(3):
+                yf = fused[i % copies].forward(x)
+            same = bool(torch.equal(yf, layers[(3 - 1) % copies].forward(x)))
+            dist.barrier()
+            torch.cuda.synchronize()
+            f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            f0.record()
+            for i in range(4 * copies):
+                yf = fused[i % copies].forward(x)
+            f1.record()
+            torch.cuda.synchronize()
+            tf = torch.tensor([f0.elapsed_time(f1) / (4 * copies)], device="cuda")
+            dist.all_reduce(tf, op=dist.ReduceOp.MAX)
+            line = {"workload": "N-split BitLinear 8192->28672, slices stored into peer outputs (no collective)",
+                    "n_gpus": world, "M": M, "us_per_call": round(float(tf.item()) * 1e3, 2),
+                    "equals_allgather_result": same, "launch": "eager"}
+            try:   # the same calls replayed as one CUDA graph (launch overhead off the critical path)
+                side = torch.cuda.Stream()
+                with torch.cuda.stream(side):
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph, stream=side):
+                        for i in range(copies):
+                            yf = fused[i].forward(x)
+                for _ in range(2):
+                    graph.replay()
+                dist.barrier()
+                torch.cuda.synchronize()
+                f0.record()
+                for _ in range(4):
+                    graph.replay()
+                f1.record()
+                torch.cuda.synchronize()
+                tg = torch.tensor([f0.elapsed_time(f1) / (4 * copies)], device="cuda")
+                dist.all_reduce(tg, op=dist.ReduceOp.MAX)
+                line["us_per_call_graph"] = round(float(tg.item()) * 1e3, 2)
+                line["algorithmic_gbs_whole_job_graph"] = round((N * K // 4 + 4 * M * K + 4 * M * N) / (float(tg.item()) * 1e3) / 1e3, 1)
+            except Exception as ex:   # capture is an optimisation of the measurement, not of the result
+                line["graph"] = f"not captured: {type(ex).__name__}"
+                torch.cuda.synchronize()
+            if rank == 0:
+                print(json.dumps(line))
+        for i in range(3):
+            y = layers[i % copies].forward(x)
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        iters = 4 * copies
+        e0.record()
+        for i in range(iters):
+            y = layers[i % copies].forward(x)
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / iters], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        us = float(t.item()) * 1e3
+        nbytes = N * K // 4 + 4 * M * K + 4 * M * N
+        if rank == 0:
+            print(json.dumps({"workload": "N-split BitLinear 8192->28672 + all-gather", "n_gpus": world, "M": M,
+                              "us_per_call": round(us, 2), "algorithmic_gbs_whole_job": round(nbytes / us / 1e3, 1),
+                              "int_tops": round(2.0 * M * K * N / us / 1e6, 1), "allgather_bytes_per_gpu": 4 * M * N * (world - 1) // world,
+                              "launch": "eager", "checksum": float(y.double().sum().item())}))
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    _bench_nsplit()

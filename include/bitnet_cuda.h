@@ -82,8 +82,17 @@ typedef struct bitnet_forward_opts {
     int32_t *acc_out_dev;   /* optional [M,N]: the int32 accumulators */
     size_t ldy;             /* row stride of y (and acc_out) in elements; 0 means N */
     int32_t stages;         /* decode kernel: depth of the shared-memory weight ring (0 = choose) */
-    int32_t reserved;
+    int32_t n_peers;        /* 0, or the number of entries of y_peers_dev (at most BITNET_MAX_PEERS) */
+    /* Output-feature-split layer on several GPUs: when n_peers > 0 the kernel's epilogue stores every
+       output element into each of these buffers (this GPU's and its peers', mapped into this process:
+       CUDA IPC, symmetric memory or cudaDeviceEnablePeerAccess) instead of y_dev alone, which replaces
+       the all-gather of the column slices by plain peer stores over NVLink.  Each pointer addresses
+       the slice's first column in that GPU's full-width output (row stride ldy).  Decode shapes
+       (M <= 16) only; the caller synchronises the GPUs afterwards.  No counterpart in the
+       reference, which has no multi-GPU code. */
+    float *y_peers_dev[8];
 } bitnet_forward_opts;
+#define BITNET_MAX_PEERS 8
 
 /* Device facts (CudaBackend::validate_device_capabilities, bitnet-cuda/src/backend.rs:192-213). */
 typedef struct bitnet_device_info {

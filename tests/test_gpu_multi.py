@@ -29,6 +29,11 @@ def _worker(rank, world, port, M, K, N, out):
         y = layer.forward(x)
         full = oracle.bitlinear_forward(wp_h, scale, x_h, N)["y"]
         ok_split = np.array_equal(y.cpu().numpy(), full)
+        if M <= 16:   # the same split with the slices stored straight into every rank's output
+            fused = parallel.FusedNSplitBitLinear(wp, scale, N, K)
+            for _ in range(2):
+                yf = fused.forward(x)
+            ok_split = ok_split and np.array_equal(yf.cpu().numpy(), full)
         rows = parallel.row_sharded_forward(lambda xs: ops.bitlinear_forward(wp, scale, xs, N), x)
         b, e = parallel.shard_range(M, world, rank)
         ok_rows = np.array_equal(rows.cpu().numpy(), full[b:e])
