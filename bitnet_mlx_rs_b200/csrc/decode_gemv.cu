@@ -798,10 +798,13 @@ static bitnet_status_t launch_one(DecodeParams p, uint32_t flags, cudaStream_t s
     p.bst_offset = (unsigned)bst_offset;
     p.red_offset = (unsigned)(smem - (size_t)stages * red_per_stage);
 
-    static size_t smem_set = 0;   // per instantiation; one launching thread per process
-    if (smem > 40 * 1024 && smem > smem_set) {   // static shared memory counts against the default 48 KB too
+    static size_t smem_set[64] = {0};   // per instantiation and device; one launching thread per process
+    int dev = 0;
+    BITNET_CUDA(cudaGetDevice(&dev));
+    const bool tracked = dev >= 0 && dev < 64;
+    if (smem > 40 * 1024 && (!tracked || smem > smem_set[dev])) {   // static shared memory counts against the default 48 KB too
         BITNET_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        smem_set = smem;
+        if (tracked) smem_set[dev] = smem;
     }
 
     cudaLaunchConfig_t cfg = {};
