@@ -340,7 +340,7 @@ def run_cuda(args):
             "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
                          "peak_kind": peak_kind,
                          # dram__bytes_read.sum + dram__bytes_write.sum of one gate/up launch at M = 1 from an ncu
-                         # capture of the same kernel (profiles/bench_ffn_decode_launch_list.md); its algorithmic
+                         # capture of the same kernel (summary under profiles/); its algorithmic
                          # bytes are 8.89 MB, so nothing is read twice
                          "traffic": 8923392,
                          "kernel": "decode_kernel (gate/up pair and down launches; algorithmic bytes per launch "
