@@ -103,3 +103,28 @@ print("ok")
     out = subprocess.run([sys.executable, "-c", code], cwd=root, env=dict(os.environ, **env), capture_output=True, text=True,
                          timeout=300)
     assert out.returncode == 0 and "ok" in out.stdout, out.stdout + out.stderr
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("ldy_extra,col0", [(64, 0), (64, 32), (3, 0), (5, 1)])
+def test_prefill_strided_and_unaligned_output(ldy_extra, col0):
+    """y with a row stride larger than N (a column slice of a wider output): rows that are
+    16-byte aligned leave through TMA stores, anything else through plain stores; bytes outside
+    the slice stay untouched."""
+    M, K, N = 200, 512, 320
+    g = torch.Generator(device="cuda").manual_seed(11)
+    w = torch.randint(0, 256, (N * K // 4,), dtype=torch.uint8, device="cuda", generator=g)
+    ops.sanitize_packed(w)
+    x = torch.randn(M, K, device="cuda", generator=g)
+    ref = ops.bitlinear_forward(w, 0.03, x, N, path="generic")
+    ldy = N + ldy_extra
+    wide = torch.full((M, ldy), -7.0, device="cuda")
+    view = wide.view(-1)[col0:]           # the slice's first element
+    ops.bitlinear_forward(w, 0.03, x, N, path="prefill", out=view, ldy=ldy)
+    torch.cuda.synchronize()
+    got = wide[:, col0:col0 + N]
+    assert torch.equal(got, ref)
+    mask = torch.ones_like(wide, dtype=torch.bool)
+    mask[:, col0:col0 + N] = False
+    assert bool((wide[mask] == -7.0).all())
+    assert ops.device_error_flags() == 0
