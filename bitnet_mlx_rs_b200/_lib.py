@@ -68,6 +68,7 @@ SIGNATURES = {
     "bitnet_pack_ternary": (i32, [vp, sz, vp, vp]),
     "bitnet_unpack_ternary": (i32, [vp, sz, vp, vp]),
     "bitnet_sanitize_packed": (i32, [vp, sz, vp, vp]),
+    "bitnet_prepare_weights": (i32, [vp, sz, sz, i32, vp, vp, vp]),
     "bitnet_backend_config_default": (None, [_P(BackendConfig)]),
     "bitnet_backend_create": (i32, [_P(BackendConfig), _P(vp)]),
     "bitnet_backend_destroy": (None, [vp]),

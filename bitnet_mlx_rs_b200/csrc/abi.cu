@@ -330,3 +330,16 @@ extern "C" bitnet_status_t bitnet_ffn_forward(const uint8_t *w_gate_dev, float s
     po.path = p2; po.flags = o.flags; po.stages = o.stages;
     return bitnet_bitlinear_forward(w_down_dev, s_down, h_dev, y_dev, M, ffn, hidden, &po, ws + off, workspace_bytes - off, stream);
 }
+
+// The reference's weight-preparation hook (w2a8_gemv.rs:21, :259): nothing to permute here.
+extern "C" bitnet_status_t bitnet_prepare_weights(uint8_t *packed_dev, size_t N, size_t K, int32_t layout_id,
+                                                  unsigned long long *count_dev, uint32_t *fast_paths,
+                                                  bitnet_stream_t stream)
+{
+    if (fast_paths) *fast_paths = 0;
+    if (layout_id != 0) return fail(BITNET_ERR_INVALID_CONFIG, "unknown weight layout %d (0 = canonical packed stream)", layout_id);
+    if (N == 0 || K == 0) return BITNET_OK;
+    if (!packed_dev) return fail(BITNET_ERR_NULL_POINTER, "bitnet_prepare_weights: null buffer");
+    if (fast_paths) *fast_paths = (decode_supports(1, K, N) ? 1u : 0u) | (prefill_supports(17, K, N) ? 2u : 0u);
+    return bitnet_sanitize_packed(packed_dev, (N * K + 3) / 4, count_dev, stream);
+}

@@ -164,3 +164,18 @@ def sanitize_packed(packed: torch.Tensor, stream=None) -> int:
     count = torch.zeros((1,), dtype=torch.int64, device=packed.device)
     check(L.load().bitnet_sanitize_packed(packed.data_ptr(), packed.numel(), count.data_ptr(), _stream(stream)))
     return int(count.item())
+
+
+def prepare_weights(packed: torch.Tensor, out_features: int, in_features: int, layout_id: int = 0, stream=None):
+    """One-time preparation of a packed weight buffer (the reference's weight-permutation hook,
+    bitnet-cuda/src/kernels/w2a8_gemv.rs:21, :259): removes code 3 in place and reports which fast
+    kernels take the shape.  Returns (invalid codes found, {"decode": bool, "prefill": bool})."""
+    packed = _require(packed, torch.uint8, "packed")
+    if packed.numel() != packed_len(out_features * in_features):
+        raise IncompatibleShapes(f"Weight tensor size mismatch: expected {packed_len(out_features * in_features)} bytes, "
+                                 f"got {packed.numel()}")
+    count = torch.zeros((1,), dtype=torch.int64, device=packed.device)
+    mask = C.c_uint32(0)
+    check(L.load().bitnet_prepare_weights(packed.data_ptr(), out_features, in_features, layout_id, count.data_ptr(),
+                                          C.byref(mask), _stream(stream)))
+    return int(count.item()), {"decode": bool(mask.value & 1), "prefill": bool(mask.value & 2)}

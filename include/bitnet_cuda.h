@@ -197,6 +197,17 @@ bitnet_status_t bitnet_unpack_ternary(const uint8_t *packed_dev, size_t n_values
 bitnet_status_t bitnet_sanitize_packed(uint8_t *packed_dev, size_t n_bytes,
                                        unsigned long long *count_dev, bitnet_stream_t stream);
 
+/* One-time preparation of a packed weight buffer for the kernels of this library: the hook that
+ * the reference names enable_weight_permutation / permute_weights_16x32
+ * (bitnet-cuda/src/kernels/w2a8_gemv.rs:21, :259).  No permutation is needed here -- every kernel
+ * consumes the canonical layout (layout_id 0, the only one accepted) -- so preparation is the
+ * in-place removal of code 3 plus the shape checks of the fast paths: *fast_paths receives a mask
+ * (bit 0: decode kernel usable for M <= 16, bit 1: tensor-core GEMM usable); shapes that fit
+ * neither still run on the generic kernel.  count_dev as in bitnet_sanitize_packed. */
+bitnet_status_t bitnet_prepare_weights(uint8_t *packed_dev, size_t N, size_t K, int32_t layout_id,
+                                       unsigned long long *count_dev, uint32_t *fast_paths,
+                                       bitnet_stream_t stream);
+
 /* ---- host-side backend (handle based) ------------------------------------------------- */
 /* Mirrors CudaBackend / CudaBackendConfig / W2A8GemvConfig / CudaMemoryManager /
  * CudaStream / PerformanceStats of the reference's bitnet-cuda crate

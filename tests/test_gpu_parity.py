@@ -346,3 +346,16 @@ def test_linearity_of_the_integer_path():
     _, dbg = ops.bitlinear_forward(dev(p2), ws, dev(x), 2 * N, debug=True)
     acc = dbg["acc"].cpu().numpy()
     assert np.array_equal(acc[:, :N], -acc[:, N:])
+
+
+def test_prepare_weights_hook():
+    # canonical layout is the prepared layout: code 3 removed in place, fast-path mask reported
+    wp = np.full(64 * 256 // 4, 0xFF, dtype=np.uint8)          # every code is 3
+    t = dev(wp)
+    n, paths = ops.prepare_weights(t, 64, 256)
+    assert n == 64 * 256 and paths == {"decode": True, "prefill": True}
+    assert np.array_equal(t.cpu().numpy(), np.full_like(wp, 0x55))
+    n2, paths2 = ops.prepare_weights(dev(np.zeros(3 * 100 // 4, dtype=np.uint8)), 3, 100)
+    assert n2 == 0 and paths2 == {"decode": False, "prefill": False}       # K % 64 != 0: generic kernel only
+    with pytest.raises(Exception):
+        ops.prepare_weights(t, 64, 256, layout_id=1)
