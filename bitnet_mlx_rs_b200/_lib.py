@@ -88,6 +88,7 @@ SIGNATURES = {
     "bitnet_backend_bitlinear_forward": (i32, [vp, vp, vp, vp, sz, _P(ForwardOpts), sz]),
     "bitnet_backend_bitlinear_forward_host": (i32, [vp, vp, vp, vp, sz, _P(ForwardOpts), sz]),
     "bitnet_backend_ffn_forward_host": (i32, [vp, vp, vp, vp, vp, vp, sz, _P(ForwardOpts), sz]),
+    "bitnet_backend_ffn_forward_host_async": (i32, [vp, vp, vp, vp, vp, vp, sz, _P(ForwardOpts), sz]),
 }
 
 _lib = None

@@ -88,7 +88,24 @@ struct CudaStream {
     void *dev = nullptr;      // device staging (x, h, y) + workspace, grown on demand
     size_t dev_bytes = 0;
     std::mutex mu;            // one host-facing call at a time per stream
+    // result of an asynchronous host-buffer call that is still in flight on this stream:
+    // `pending_bytes` bytes at `pending_src` (pinned staging) go to `pending_dst` once the stream is idle
+    void *pending_dst = nullptr;
+    const void *pending_src = nullptr;
+    size_t pending_bytes = 0;
 };
+
+// Waits for the stream and hands a pending asynchronous result to its host buffer (caller holds s.mu).
+static bitnet_status_t deliver_pending(CudaStream &s)
+{
+    if (!s.pending_dst) return BITNET_OK;
+    const cudaError_t err = cudaStreamSynchronize(s.stream);
+    void *dst = s.pending_dst;
+    s.pending_dst = nullptr;
+    if (err != cudaSuccess) return fail(BITNET_ERR_STREAM_SYNC, "stream synchronize: %s", cudaGetErrorString(err));
+    memcpy(dst, s.pending_src, s.pending_bytes);
+    return BITNET_OK;
+}
 
 struct Weights {
     uint8_t *packed_dev = nullptr;
@@ -254,7 +271,10 @@ extern "C" bitnet_status_t bitnet_backend_stream(bitnet_backend *b, size_t index
 extern "C" bitnet_status_t bitnet_backend_synchronize(bitnet_backend *b)
 {
     if (!b) return fail(BITNET_ERR_NULL_POINTER, "bitnet_backend_synchronize: null backend");
+    BITNET_CUDA(cudaSetDevice(b->impl.device));
     for (auto &s : b->impl.streams) {
+        std::lock_guard<std::mutex> lock(s->mu);
+        BITNET_TRY(deliver_pending(*s));
         const cudaError_t err = cudaStreamSynchronize(s->stream);
         if (err != cudaSuccess) return fail(BITNET_ERR_STREAM_SYNC, "stream synchronize: %s", cudaGetErrorString(err));
     }
@@ -460,6 +480,7 @@ extern "C" bitnet_status_t bitnet_backend_bitlinear_forward_host(bitnet_backend 
     BITNET_TRY(b->impl.stream_at(stream_idx, &s));
     std::lock_guard<std::mutex> lock(s->mu);
     BITNET_CUDA(cudaSetDevice(b->impl.device));
+    BITNET_TRY(deliver_pending(*s));   // an earlier asynchronous call on this stream still owns the staging buffers
     const size_t K = w->impl.K, N = w->impl.N;
     const size_t xb = align_up(M * K * sizeof(float), 256), yb = align_up(M * N * sizeof(float), 256);
     size_t ws = 0;
@@ -497,6 +518,7 @@ extern "C" bitnet_status_t bitnet_backend_ffn_forward_host(bitnet_backend *b, co
     BITNET_TRY(b->impl.stream_at(stream_idx, &s));
     std::lock_guard<std::mutex> lock(s->mu);
     BITNET_CUDA(cudaSetDevice(b->impl.device));
+    BITNET_TRY(deliver_pending(*s));   // an earlier asynchronous call on this stream still owns the staging buffers
     const size_t xb = align_up(M * hidden * sizeof(float), 256), hb = align_up(M * ffn * sizeof(float), 256);
     size_t ws = 0;
     BITNET_TRY(bitnet_ffn_workspace_size(M, hidden, ffn, opts ? opts->path : BITNET_PATH_AUTO, &ws));
@@ -514,6 +536,50 @@ extern "C" bitnet_status_t bitnet_backend_ffn_forward_host(bitnet_backend *b, co
     const cudaError_t err = cudaStreamSynchronize(s->stream);
     if (err != cudaSuccess) return fail(BITNET_ERR_STREAM_SYNC, "stream synchronize: %s", cudaGetErrorString(err));
     memcpy(y_host, pin + xb, M * hidden * sizeof(float));
+    b->impl.record(now_ns() - t0, 3 * (ffn * hidden / 4) + 4 * M * (2 * hidden + 2 * ffn) + 4 * M * (2 * ffn + hidden));
+    s->operation_count.fetch_add(1, std::memory_order_relaxed);
+    return BITNET_OK;
+}
+
+// Asynchronous form of the call above, the reference's usage model for its stream pool (launches are
+// asynchronous per stream, CudaBackend::synchronize joins them: bitnet-cuda/src/backend.rs:129-178):
+// the copies and launches are queued on the chosen stream and the call returns; y_host is complete after
+// bitnet_backend_synchronize, or after the next host-buffer call on the same stream.  x_host may be
+// reused at once (it is staged before the call returns).
+extern "C" bitnet_status_t bitnet_backend_ffn_forward_host_async(bitnet_backend *b, const bitnet_weights *gate,
+                                                                 const bitnet_weights *up, const bitnet_weights *down,
+                                                                 const float *x_host, float *y_host, size_t M,
+                                                                 const bitnet_forward_opts *opts, size_t stream_idx)
+{
+    if (!b || !gate || !up || !down) return fail(BITNET_ERR_NULL_POINTER, "bitnet_backend_ffn_forward_host_async: null argument");
+    if (M == 0) return BITNET_OK;
+    if (!x_host || !y_host) return fail(BITNET_ERR_NULL_POINTER, "bitnet_backend_ffn_forward_host_async: null buffer");
+    const size_t hidden = gate->impl.K, ffn = gate->impl.N;
+    if (up->impl.K != hidden || up->impl.N != ffn || down->impl.K != ffn || down->impl.N != hidden)
+        return fail(BITNET_ERR_INCOMPATIBLE_SHAPES, "FFN shapes disagree: gate %zux%zu, up %zux%zu, down %zux%zu", ffn, hidden,
+                    up->impl.N, up->impl.K, down->impl.N, down->impl.K);
+    CudaStream *s = nullptr;
+    BITNET_TRY(b->impl.stream_at(stream_idx, &s));
+    std::lock_guard<std::mutex> lock(s->mu);
+    BITNET_CUDA(cudaSetDevice(b->impl.device));
+    BITNET_TRY(deliver_pending(*s));
+    const size_t xb = align_up(M * hidden * sizeof(float), 256), hb = align_up(M * ffn * sizeof(float), 256);
+    size_t ws = 0;
+    BITNET_TRY(bitnet_ffn_workspace_size(M, hidden, ffn, opts ? opts->path : BITNET_PATH_AUTO, &ws));
+    BITNET_TRY(b->impl.ensure_staging(*s, 2 * xb, 2 * xb + hb + ws));
+    char *pin = static_cast<char *>(s->pinned), *dev = static_cast<char *>(s->dev);
+    float *x_dev = reinterpret_cast<float *>(dev), *y_dev = reinterpret_cast<float *>(dev + xb);
+    float *h_dev = reinterpret_cast<float *>(dev + 2 * xb);
+    const uint64_t t0 = now_ns();
+    memcpy(pin, x_host, M * hidden * sizeof(float));
+    BITNET_CUDA(cudaMemcpyAsync(x_dev, pin, M * hidden * sizeof(float), cudaMemcpyHostToDevice, s->stream));
+    BITNET_TRY(bitnet_ffn_forward(gate->impl.packed_dev, gate->impl.w_scale, up->impl.packed_dev, up->impl.w_scale,
+                                  down->impl.packed_dev, down->impl.w_scale, x_dev, h_dev, y_dev, M, hidden, ffn, opts,
+                                  ws ? dev + 2 * xb + hb : nullptr, ws, s->stream));
+    BITNET_CUDA(cudaMemcpyAsync(pin + xb, y_dev, M * hidden * sizeof(float), cudaMemcpyDeviceToHost, s->stream));
+    s->pending_dst = y_host;
+    s->pending_src = pin + xb;
+    s->pending_bytes = M * hidden * sizeof(float);
     b->impl.record(now_ns() - t0, 3 * (ffn * hidden / 4) + 4 * M * (2 * hidden + 2 * ffn) + 4 * M * (2 * ffn + hidden));
     s->operation_count.fetch_add(1, std::memory_order_relaxed);
     return BITNET_OK;

@@ -283,6 +283,20 @@ class CudaBackend:
                                                        x.shape[0], C.byref(opts) if opts else None, stream_idx))
         return y
 
+    def ffn_forward_host_async(self, gate: DeviceWeights, up: DeviceWeights, down: DeviceWeights, x_host, out,
+                               opts: L.ForwardOpts | None = None, stream_idx: int = 0) -> None:
+        """Queues the FFN block on stream `stream_idx` and returns; `out` (a C-contiguous float32 numpy
+        array [M, hidden] that the caller keeps alive) is complete after `synchronize()` or after the next
+        host-buffer call on the same stream (backend.rs:129-178: asynchronous launches, synchronize joins)."""
+        import numpy as np
+        x = np.ascontiguousarray(x_host, dtype=np.float32)
+        if x.ndim != 2 or x.shape[1] != gate.in_features:
+            raise IncompatibleShapes(f"expected [M,{gate.in_features}], got {list(x.shape)}")
+        if out.dtype != np.float32 or not out.flags["C_CONTIGUOUS"] or out.shape != (x.shape[0], down.out_features):
+            raise IncompatibleShapes(f"out must be a C-contiguous float32 array [{x.shape[0]},{down.out_features}]")
+        check(L.load().bitnet_backend_ffn_forward_host_async(self._h, gate._h, up._h, down._h, x.ctypes.data, out.ctypes.data,
+                                                             x.shape[0], C.byref(opts) if opts else None, stream_idx))
+
 
 def device_count() -> int:          # lib.rs:56-64
     n = C.c_int32()

@@ -293,6 +293,15 @@ bitnet_status_t bitnet_backend_ffn_forward_host(bitnet_backend *b, const bitnet_
                                                 const bitnet_weights *up, const bitnet_weights *down,
                                                 const float *x_host, float *y_host, size_t M,
                                                 const bitnet_forward_opts *opts, size_t stream_idx);
+/* Asynchronous form: the copies and launches are queued on the chosen stream and the call returns
+ * (the reference's model for its stream pool: launches are asynchronous per stream and
+ * CudaBackend::synchronize joins them, bitnet-cuda/src/backend.rs:129-178).  x_host may be reused at
+ * once; y_host is complete after bitnet_backend_synchronize or after the next host-buffer call on
+ * the same stream.  One call may be in flight per stream: spread calls over the backend's streams. */
+bitnet_status_t bitnet_backend_ffn_forward_host_async(bitnet_backend *b, const bitnet_weights *gate,
+                                                      const bitnet_weights *up, const bitnet_weights *down,
+                                                      const float *x_host, float *y_host, size_t M,
+                                                      const bitnet_forward_opts *opts, size_t stream_idx);
 
 #ifdef __cplusplus
 }

@@ -359,3 +359,35 @@ def test_prepare_weights_hook():
     assert n2 == 0 and paths2 == {"decode": False, "prefill": False}       # K % 64 != 0: generic kernel only
     with pytest.raises(Exception):
         ops.prepare_weights(t, 64, 256, layout_id=1)
+
+
+def test_backend_host_ffn_async_streams():
+    # asynchronous host-buffer calls spread over the backend's streams, joined by synchronize()
+    hidden, ffn = 256, 640
+    b = cuda.CudaBackend(cuda.CudaBackendConfig(num_streams=3))
+    try:
+        layers = []
+        for l in range(5):
+            packs = [oracle.gen_ternary_packed(7, 10 * l + i, ffn * hidden) for i in range(3)]
+            scales = [oracle.gen_weight_scale(7, 10 * l + i, k) for i, k in ((0, hidden), (1, hidden), (2, ffn))]
+            layers.append((packs, scales, (b.upload_packed(packs[0], ffn, hidden, scales[0]), b.upload_packed(packs[1], ffn, hidden, scales[1]),
+                                           b.upload_packed(packs[2], hidden, ffn, scales[2]))))
+        xs = [oracle.gen_activations(7, 100 + i, (1 + i % 4, hidden)) for i in range(12)]
+        outs = [np.full((x.shape[0], hidden), np.nan, dtype=np.float32) for x in xs]
+        for i, x in enumerate(xs):           # more calls than streams: a stream delivers its pending result before it is reused
+            g, u, d = layers[i % 5][2]
+            b.ffn_forward_host_async(g, u, d, x, outs[i], stream_idx=i % 3)
+        b.synchronize()
+        for i, x in enumerate(xs):
+            packs, scales, _ = layers[i % 5]
+            ref, _ = oracle.ffn_forward(packs[0], scales[0], packs[1], scales[1], packs[2], scales[2], x, ffn)
+            assert np.array_equal(outs[i], ref), i
+        # a synchronous call after asynchronous ones on the same stream
+        g, u, d = layers[0][2]
+        b.ffn_forward_host_async(g, u, d, xs[0], outs[0], stream_idx=0)
+        y = b.ffn_forward_host(g, u, d, xs[1], stream_idx=0)
+        packs, scales, _ = layers[0]
+        assert np.array_equal(y, oracle.ffn_forward(packs[0], scales[0], packs[1], scales[1], packs[2], scales[2], xs[1], ffn)[0])
+        assert np.array_equal(outs[0], oracle.ffn_forward(packs[0], scales[0], packs[1], scales[1], packs[2], scales[2], xs[0], ffn)[0])
+    finally:
+        b.close()
