@@ -7,6 +7,11 @@ tokens over 30 distinct layers' weights (398 MB packed, larger than L2), seeded 
 ternary weights (P(0)=0.4, P(+-1)=0.3) and N(0,1) activations with 0.1 % x20 outliers.
 One step = 3 token counts x 30 layers x one FFN block = 300 kernel launches
 (2 per block at M = 1, 4 at M > 1 where a small quantiser launch precedes each decode launch).
+The 90 blocks of a step are independent (own weights, own input), so the step is replayed as one
+CUDA graph in which they are dealt round-robin to eight streams: each block's launches stay
+ordered (with programmatic dependent launch), blocks of different streams overlap on the device.
+`single_chain` in the output is the same step as ONE dependent chain of launches on one stream
+(the latency a single sequence sees).
 
 metric  = algorithmic HBM GB/s: bytes N*K/4 + 4*M*K + 4*M*N per BitLinear call, summed
           over the step, divided by device time (CUDA events, max over ranks).
@@ -212,13 +217,26 @@ def run_cuda(args):
     x0 = oracle.gen_activations(0, 2008, (8, HIDDEN))
     X[8][0] = torch.from_numpy(x0).cuda()
     Y = {M: torch.empty((LAYERS, M, HIDDEN), device="cuda") for M in TOKEN_COUNTS}
-    Hb = {M: torch.empty((M, FFN), device="cuda") for M in TOKEN_COUNTS}
+    n_streams = max(1, args.streams)
+    Hb = {M: [torch.empty((M, FFN), device="cuda") for _ in range(n_streams)] for M in TOKEN_COUNTS}
+    calls = [(M, l) for M in TOKEN_COUNTS for l in range(LAYERS)]
+    branch = [torch.cuda.Stream() for _ in range(n_streams)] if n_streams > 1 else []
 
-    def step(pdl):
-        for M in TOKEN_COUNTS:
-            for l in range(LAYERS):
-                ops.ffn_forward(Wg[l], S[l][0], Wu[l], S[l][1], Wd[l], S[l][2], X[M][l], FFN, out=Y[M][l], h_out=Hb[M],
+    def step(pdl, concurrent=True):
+        """The step's 90 independent FFN blocks: one chain on the current stream, or dealt round-robin
+        to `n_streams` streams forked from it (each block's two to four launches stay in order on
+        their stream; blocks on different streams may overlap on the device)."""
+        cur = torch.cuda.current_stream()
+        use = branch if (concurrent and branch) else []
+        for st in use:
+            st.wait_stream(cur)
+        for i, (M, l) in enumerate(calls):
+            k = i % n_streams if use else 0
+            with torch.cuda.stream(use[k] if use else cur):
+                ops.ffn_forward(Wg[l], S[l][0], Wu[l], S[l][1], Wd[l], S[l][2], X[M][l], FFN, out=Y[M][l], h_out=Hb[M][k],
                                 pdl=pdl)
+        for st in use:
+            cur.wait_stream(st)
 
     # per FFN block: M = 1 runs two launches (gate/up pair, down), each quantising its own input;
     # M >= 2 adds one small quantiser launch in front of each (activations are quantised once, not per CTA)
@@ -232,31 +250,36 @@ def run_cuda(args):
         np.testing.assert_allclose(Y[8][0].cpu().numpy(), ry, rtol=1e-5, atol=0)
 
     # capture the step in a CUDA graph: try programmatic dependent launch first
-    mode, graph = "eager", None
     side = torch.cuda.Stream()
-    for pdl in ((True, False) if not args.no_pdl else (False,)):
-        try:
-            with torch.cuda.stream(side):
-                step(pdl)
+
+    def capture(concurrent):
+        for pdl in ((True, False) if not args.no_pdl else (False,)):
+            try:
+                with torch.cuda.stream(side):
+                    step(pdl, concurrent)
+                    torch.cuda.synchronize()
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=side):
+                        step(pdl, concurrent)
+                g.replay()
                 torch.cuda.synchronize()
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g, stream=side):
-                    step(pdl)
-            g.replay()
-            torch.cuda.synchronize()
-            graph, mode = g, ("cuda_graph+pdl" if pdl else "cuda_graph")
-            break
-        except Exception as ex:   # capture not possible in this mode: try the next one
-            print(f"graph capture (pdl={pdl}) failed: {ex}", file=sys.stderr)
-            torch.cuda.synchronize()
+                return g, ("cuda_graph+pdl" if pdl else "cuda_graph")
+            except Exception as ex:   # capture not possible in this mode: try the next one
+                print(f"graph capture (pdl={pdl}, concurrent={concurrent}) failed: {ex}", file=sys.stderr)
+                torch.cuda.synchronize()
+        return None, "eager"
+
+    graph, mode = capture(True)
     if args.eager or graph is None:
         graph, mode = None, "eager"
+    if graph is not None and n_streams > 1:
+        mode += f", {n_streams} concurrent streams"
 
     def run_step():
         if graph is not None:
             graph.replay()
         else:
-            step(False)
+            step(False, False)
 
     def barrier():
         if world > 1:
@@ -284,6 +307,25 @@ def run_cuda(args):
     clocks = sampler.stop() if rank == 0 else None
 
     nbytes = step_bytes()
+    # the same step as ONE dependent chain of launches on one stream (what a single sequence sees)
+    chain = None
+    if graph is not None and n_streams > 1:
+        g1, mode1 = capture(False)
+        if g1 is not None:
+            for _ in range(3):
+                g1.replay()
+            c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            barrier()
+            c0.record()
+            n1 = max(5, min(args.steps, 20))
+            for _ in range(n1):
+                g1.replay()
+            c1.record()
+            barrier()
+            ms1 = c0.elapsed_time(c1) / n1
+            chain = {"ms_per_step": ms1, "value": nbytes / (ms1 * 1e-3) / 1e9, "unit": "GB/s", "launch_mode": mode1,
+                     "us_per_ffn_block": ms1 * 1e3 / len(calls)}
+            del g1
     value = world * nbytes * args.steps / (ms_total * 1e-3) / 1e9
     per_gpu = value / world
     peak, peak_kind = measured_peaks()
@@ -298,15 +340,20 @@ def run_cuda(args):
     xh = {M: [X[M][l].cpu().numpy() for l in range(e2e_layers)] for M in TOKEN_COUNTS}
     yh = {M: [np.empty((M, HIDDEN), dtype=np.float32) for _ in range(e2e_layers)] for M in TOKEN_COUNTS}
 
+    from concurrent.futures import ThreadPoolExecutor
+    calls = [(M, l) for M in TOKEN_COUNTS for l in range(e2e_layers)]
+    pool = ThreadPoolExecutor(max_workers=E2E_STREAMS)
+
+    def feed(sidx):
+        # one host thread per stream (the C calls release the interpreter lock)
+        for M, l in calls[sidx::E2E_STREAMS]:
+            backend.ffn_forward_host_async(dw[l][0], dw[l][1], dw[l][2], xh[M][l], yh[M][l], stream_idx=sidx)
+
     def e2e_step():
         # host buffers in, host buffers out; the calls are queued round-robin on the backend's streams
         # (asynchronous launches, joined by synchronize -- the reference's stream-pool model) and every
         # result is in its host buffer when the step ends
-        i = 0
-        for M in TOKEN_COUNTS:
-            for l in range(e2e_layers):
-                backend.ffn_forward_host_async(dw[l][0], dw[l][1], dw[l][2], xh[M][l], yh[M][l], stream_idx=i % E2E_STREAMS)
-                i += 1
+        list(pool.map(feed, range(E2E_STREAMS)))
         backend.synchronize()
 
     for _ in range(3):
@@ -325,6 +372,7 @@ def run_cuda(args):
         np.testing.assert_allclose(yh[8][LAYERS - 1], Y[8][LAYERS - 1].cpu().numpy(), rtol=1e-5, atol=0)
         np.testing.assert_allclose(yh[1][0], Y[1][0].cpu().numpy(), rtol=1e-5, atol=0)
     io_bytes = sum(M * HIDDEN * 4 for M in TOKEN_COUNTS) * LAYERS
+    pool.shutdown()
     backend.close()
 
     # ---- supporting single-kernel figures (same kernel, other configs of the spec) ---------------
@@ -359,10 +407,13 @@ def run_cuda(args):
                                    "this kernel or its quantiser)"},
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": io_bytes, "d2h_bytes_per_step": io_bytes,
                     "steps": e2e_steps,
-                    "api": f"bitnet_backend_ffn_forward_host_async on {E2E_STREAMS} streams + bitnet_backend_synchronize per step"},
+                    "api": f"bitnet_backend_ffn_forward_host_async on {E2E_STREAMS} streams, one host thread each, + "
+                           "bitnet_backend_synchronize per step"},
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
         }
+        if chain:
+            line["single_chain"] = chain
         if cpu:
             line["cpu_baseline"] = cpu
         if extra:
@@ -448,6 +499,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--eager", action="store_true", help="launch kernels one by one instead of replaying a CUDA graph")
     ap.add_argument("--no-pdl", action="store_true")
+    ap.add_argument("--streams", type=int, default=8, help="streams the step's independent FFN blocks are dealt to (1 = one chain)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-extra", action="store_true", help="skip the single-kernel figures")
     args = ap.parse_args()

@@ -84,6 +84,7 @@ struct DecodeParams {
     unsigned image_bytes;
     unsigned bst_offset; // where the activation staging area starts in dynamic shared memory
     unsigned red_offset; // where the K-split sums start
+    int mrows;           // token rows kept per 8-token tile of the activation staging area (1, 2, 4 or 8)
     float *y_peers[8];   // output-feature split over several GPUs: every output goes to each of these
     int n_peers;         // (own and peer memory, plain stores over NVLink); 0 = write y only
 };
@@ -182,7 +183,7 @@ __device__ __forceinline__ int quantize_any(float x, float scale, bool fast)
 }
 
 // Dynamic shared memory: the weight ring [stages x stage_bytes], the activation staging
-// area (eight warp-private regions of SW*4*NT*512 bytes; with BREG and little shared memory
+// area (warp-private regions of SW*4*NT fragment blocks of 64 bytes per kept token row; with BREG and little shared memory
 // it overlaps the last ring stages, which the producer then fills only after every warp has
 // moved its activations to registers), and the K-split sums [stages x CW x NW*NT*512].
 // NT: token tiles of 8; SW: loop steps per warp (a step is 4 chunks = 256 k per warp);
@@ -281,7 +282,11 @@ decode_kernel(const DecodeParams p)
     const int cw0 = (int)((long long)warp * p.chunks / DEC_CWARPS);
     const int cw1 = (int)((long long)(warp + 1) * p.chunks / DEC_CWARPS);
     const int Cw = cw1 - cw0;                              // chunks of this warp's K slice (<= 4*SW)
-    unsigned char *bst = s_bst + DEC_IMG_HDR + (size_t)warp * (SW * 4 * NT * 512);
+    // a fragment block holds 16 bytes for each (token row, k quad); only the token rows that exist are kept
+    const unsigned frag_blk = (unsigned)p.mrows * 64u;
+    // lanes of token rows that do not exist feed accumulator columns nobody reads: they re-read lane 0's bytes
+    const unsigned frag_lane_off = ((unsigned)lane < (unsigned)p.mrows * 4u ? (unsigned)lane : 0u) * 16u;
+    unsigned char *bst = s_bst + DEC_IMG_HDR + (size_t)warp * (SW * 4 * NT) * frag_blk;
     const unsigned groups_per_token = (unsigned)Cw * 4;   // 16-wide k groups
     const unsigned n_groups = (unsigned)p.M * groups_per_token;
     const size_t k_base = (size_t)cw0 * 64;
@@ -440,7 +445,7 @@ decode_kernel(const DecodeParams p)
                         // the 16-wide group inside the chunk; token m sits in tile m/8, fragment row m%8
                         const unsigned c = l >> 2, i = l & 3;
                         const unsigned step = c >> 2, ctig = c & 3;
-                        const unsigned off = (((step * 4 + i) * NT + (m >> 3)) * 32 + (m & 7) * 4 + ctig) * 16;
+                        const unsigned off = ((step * 4 + i) * NT + (m >> 3)) * frag_blk + ((m & 7) * 4 + ctig) * 16;
                         *reinterpret_cast<uint4 *>(bst + off) = frag;
                     }
                 }
@@ -460,7 +465,7 @@ decode_kernel(const DecodeParams p)
             for (int i = 0; i < 4; ++i)
 #pragma unroll
                 for (int t = 0; t < NT; ++t)
-                    breg[s2][i][t] = *reinterpret_cast<const uint4 *>(bst + ((size_t)((s2 * 4 + i) * NT + t) * 32 + lane) * 16);
+                    breg[s2][i][t] = *reinterpret_cast<const uint4 *>(bst + (size_t)((s2 * 4 + i) * NT + t) * frag_blk + frag_lane_off);
         __syncwarp();
         if (lane == 0) mbar_arrive(&s_bst_free);   // the staging area may be overwritten by weights
     }
@@ -517,7 +522,7 @@ decode_kernel(const DecodeParams p)
 #pragma unroll
                     for (int t = 0; t < NT; ++t) {
                         if constexpr (BREG) bw[i2][t] = breg[s2][i2][t];
-                        else bw[i2][t] = *reinterpret_cast<const uint4 *>(bst + ((size_t)((s2 * 4 + i2) * NT + t) * 32 + lane) * 16);
+                        else bw[i2][t] = *reinterpret_cast<const uint4 *>(bst + (size_t)((s2 * 4 + i2) * NT + t) * frag_blk + frag_lane_off);
                     }
 #pragma unroll
                 for (int w = 0; w < NW; ++w) {
@@ -628,7 +633,7 @@ extern "C" int bitnet_debug_read_phases(unsigned long long *host)
 // warps want (header: per-warp-slice sums and absmax/127; then fragment-ordered bytes), so that
 // kernel fetches it with a single bulk copy.  cw/sw/nt describe the consuming instantiation.
 // Semantics: TernaryProcessor::quantize_activations (ternary_operations.rs:130-163).
-__global__ void __launch_bounds__(512) decode_quantize_kernel(const float *__restrict__ x, int M, int K, int cw, int sw, int nt,
+__global__ void __launch_bounds__(512) decode_quantize_kernel(const float *__restrict__ x, int M, int K, int cw, int sw, int nt, int mrows,
                                                               unsigned char *__restrict__ image,
                                                               const unsigned *__restrict__ amax_in, int n_amax_in,
                                                               int8_t *__restrict__ q_out, float *__restrict__ a_scale_out)
@@ -674,7 +679,8 @@ __global__ void __launch_bounds__(512) decode_quantize_kernel(const float *__res
     const float scale = quant_scale(absmax);
     const bool fast = scale >= 1e-30f && scale <= 1e30f;
     const int C = K / 64;
-    const unsigned region = (unsigned)sw * 4 * nt * 512;
+    const unsigned frag_blk = (unsigned)mrows * 64u;
+    const unsigned region = (unsigned)sw * 4 * nt * frag_blk;
 
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
@@ -709,7 +715,7 @@ __global__ void __launch_bounds__(512) decode_quantize_kernel(const float *__res
             const int w = (int)((((long long)chunk + 1) * cw - 1) / C);
             const int c_rel = chunk - (int)((long long)w * C / cw);
             const unsigned step = (unsigned)c_rel >> 2, ctig = (unsigned)c_rel & 3;
-            const unsigned off = DEC_IMG_HDR + (unsigned)w * region + (((step * 4 + i) * nt + (m >> 3)) * 32 + (m & 7) * 4 + ctig) * 16;
+            const unsigned off = DEC_IMG_HDR + (unsigned)w * region + ((step * 4 + i) * nt + (m >> 3)) * frag_blk + ((m & 7) * 4 + ctig) * 16;
             *reinterpret_cast<uint4 *>(image + off) = frag;
             if (sum) atomicAdd(&s_sum[w], sum);
         }
@@ -758,7 +764,7 @@ static bitnet_status_t launch_one(DecodeParams p, uint32_t flags, cudaStream_t s
     const unsigned real_stage = NW * 16 * row_bytes;
     p.stage_bytes = real_stage;
     p.stage_stride = real_stage + 128;
-    const size_t bst_bytes = DEC_IMG_HDR + (size_t)CW * SW * 4 * NT * 512;   // image header + fragment data
+    const size_t bst_bytes = DEC_IMG_HDR + (size_t)CW * SW * 4 * NT * (size_t)p.mrows * 64;   // image header + fragment data
     if (p.image) p.image_bytes = (unsigned)bst_bytes;
     const size_t red_per_stage = (size_t)CW * NW * NT * 512;   // one slot of partial sums per consumer warp
     const size_t budget = 208 * 1024;
@@ -887,17 +893,19 @@ static bool use_split(size_t M, size_t K)
     return M * K > (size_t)v;
 }
 
+// Token rows kept per 8-token tile of the staging area: the power of two that covers M (8 from 5 tokens on).
+static int decode_mrows(size_t M) { return M > 4 ? 8 : (M > 2 ? 4 : (M > 1 ? 2 : 1)); }
+
 size_t decode_image_bytes_always(size_t M, size_t K, size_t N, bool dual)
 {
     const DecodePlan pl = decode_plan(M, K, N, dual);
-    return align_up(DEC_IMG_HDR + (size_t)pl.cw * pl.sw * 4 * pl.nt * 512, 256);
+    return align_up(DEC_IMG_HDR + (size_t)pl.cw * pl.sw * 4 * pl.nt * (size_t)decode_mrows(M) * 64, 256);
 }
 
 size_t decode_image_bytes(size_t M, size_t K, size_t N, bool dual)
 {
     if (!use_split(M, K)) return 0;
-    const DecodePlan pl = decode_plan(M, K, N, dual);
-    return align_up(DEC_IMG_HDR + (size_t)pl.cw * pl.sw * 4 * pl.nt * 512, 256);
+    return decode_image_bytes_always(M, K, N, dual);
 }
 
 bitnet_status_t launch_decode(const ForwardArgs &a, cudaStream_t stream)
@@ -925,6 +933,7 @@ bitnet_status_t launch_decode(const ForwardArgs &a, cudaStream_t stream)
     p.stages = a.stages;
     p.amax_in = a.amax_in; p.n_amax_in = a.n_amax_in; p.amax_out = a.amax_out;
     p.weights_first = (a.flags & BITNET_FLAG_PDL) ? 1 : 0;
+    p.mrows = decode_mrows(a.M);
     p.n_peers = a.n_peers;
     for (int r = 0; r < a.n_peers && r < 8; ++r) p.y_peers[r] = a.y_peers[r];
     if (a.n_peers && dual) return fail(BITNET_ERR_UNSUPPORTED_OPERATION, "peer outputs are not available for the gate/up pair launch");
@@ -946,7 +955,7 @@ bitnet_status_t launch_decode(const ForwardArgs &a, cudaStream_t stream)
             attrs[0].val.programmaticStreamSerializationAllowed = 1;
             cfg.numAttrs = 1;
         }
-        BITNET_CUDA(cudaLaunchKernelEx(&cfg, decode_quantize_kernel, a.x, (int)a.M, (int)a.K, pl.cw, pl.sw, pl.nt,
+        BITNET_CUDA(cudaLaunchKernelEx(&cfg, decode_quantize_kernel, a.x, (int)a.M, (int)a.K, pl.cw, pl.sw, pl.nt, p.mrows,
                                        static_cast<unsigned char *>(a.image_ws), a.amax_in, a.n_amax_in, a.q_out,
                                        a.a_scale_out));
         p.image = static_cast<const unsigned char *>(a.image_ws);
