@@ -234,7 +234,7 @@ def run_cuda(args):
             k = i % n_streams if use else 0
             with torch.cuda.stream(use[k] if use else cur):
                 ops.ffn_forward(Wg[l], S[l][0], Wu[l], S[l][1], Wd[l], S[l][2], X[M][l], FFN, out=Y[M][l], h_out=Hb[M][k],
-                                pdl=pdl)
+                                pdl=pdl, throughput=bool(use))   # small CTAs when launches of several streams share the SMs
         for st in use:
             cur.wait_stream(st)
 
@@ -273,7 +273,7 @@ def run_cuda(args):
     if args.eager or graph is None:
         graph, mode = None, "eager"
     if graph is not None and n_streams > 1:
-        mode += f", {n_streams} concurrent streams"
+        mode += f", {n_streams} concurrent streams, BITNET_FLAG_THROUGHPUT"
 
     def run_step():
         if graph is not None:

@@ -21,6 +21,7 @@ ERR_INCOMPATIBLE_SHAPES, ERR_PERFORMANCE, ERR_NULL_POINTER, ERR_WORKSPACE = 10, 
 
 PATH_AUTO, PATH_DECODE, PATH_PREFILL, PATH_GENERIC = 0, 1, 2, 3
 FLAG_PDL = 1
+FLAG_THROUGHPUT = 2
 
 
 class ForwardOpts(C.Structure):

@@ -191,7 +191,7 @@ __device__ __forceinline__ int quantize_any(float x, float scale, bool fast)
 // CW: consumer warps (8 leaves room for a second CTA on the SM; 16 hides more latency when one CTA
 // streams many blocks).
 template <int CW, int NT, int SW, bool BREG, bool IN_I8, bool DUAL>
-__global__ void __launch_bounds__((CW + 1) * 32, (CW == 8 && NT * (DUAL ? 2 : 1) <= 2 && !(BREG && SW >= 4)) ? 2 : 1)
+__global__ void __launch_bounds__((CW + 1) * 32, CW == 4 ? 4 : ((CW == 8 && NT * (DUAL ? 2 : 1) <= 2 && !(BREG && SW >= 4)) ? 2 : 1))
 decode_kernel(const DecodeParams p)
 {
     constexpr int DEC_CWARPS = CW;
@@ -774,6 +774,7 @@ static bitnet_status_t launch_one(DecodeParams p, uint32_t flags, cudaStream_t s
     int want = p.stages > 0 ? p.stages : DEC_MAX_STAGES;
     if (want > DEC_MAX_STAGES) want = DEC_MAX_STAGES;
     if (want > max_blocks) want = max_blocks;
+    if (CW == 4 && want > 2) want = 2;   // small CTAs: at most two stages, so that four CTAs fit an SM
 
     int stages = want, stages_free = want;
     size_t bst_offset = 0, smem = 0;
@@ -838,7 +839,7 @@ struct DecodePlan {
 
 static int round_sw(int sw) { return sw <= 1 ? 1 : (sw <= 2 ? 2 : (sw <= 4 ? 4 : 8)); }
 
-static DecodePlan decode_plan(size_t M, size_t K, size_t N, bool dual)
+static DecodePlan decode_plan(size_t M, size_t K, size_t N, bool dual, bool throughput)
 {
     DecodePlan pl;
     pl.nt = M > 8 ? 2 : 1;
@@ -851,6 +852,16 @@ static DecodePlan decode_plan(size_t M, size_t K, size_t N, bool dual)
     pl.wide = pl.breg && blocks_per_cta >= 6 && steps_needed(K, 16) <= 2;
     pl.cw = pl.wide ? 16 : 8;
     pl.sw = round_sw(steps_needed(K, pl.cw));
+    // throughput mode: four consumer warps, so that four CTAs (of different launches) share an SM
+    // (BITNET_FLAG_THROUGHPUT; the environment variable switches it on for every call of the process)
+    static const int small_env = getenv("BITNET_DECODE_SMALL_CTA") ? atoi(getenv("BITNET_DECODE_SMALL_CTA")) : 0;
+    if ((throughput || small_env) && !pl.breg) {
+        const int sw4 = round_sw(steps_needed(K, 4));
+        if (steps_needed(K, 4) <= 8 && (sw4 <= 4 || (pl.nt == 1 && !dual))) {
+            pl.cw = 4;
+            pl.sw = sw4;
+        }
+    }
     return pl;
 }
 
@@ -862,6 +873,14 @@ static bitnet_status_t launch_sw(const DecodePlan &pl, const DecodeParams &p, ui
         if constexpr (NT == 1 && !DUAL) {
             if (pl.sw == 1) return launch_one<16, 1, 1, true, IN_I8, false>(p, flags, stream);
             if (pl.sw == 2) return launch_one<16, 1, 2, true, IN_I8, false>(p, flags, stream);
+        }
+    }
+    if (pl.cw == 4) {
+        if (pl.sw == 1) return launch_one<4, NT, 1, false, IN_I8, DUAL>(p, flags, stream);
+        if (pl.sw == 2) return launch_one<4, NT, 2, false, IN_I8, DUAL>(p, flags, stream);
+        if (pl.sw == 4) return launch_one<4, NT, 4, false, IN_I8, DUAL>(p, flags, stream);
+        if constexpr (NT == 1 && !DUAL) {
+            if (pl.sw == 8) return launch_one<4, NT, 8, false, IN_I8, DUAL>(p, flags, stream);
         }
     }
 #define BITNET_DECODE_CASE(SWV)                                                                   \
@@ -898,8 +917,14 @@ static int decode_mrows(size_t M) { return M > 4 ? 8 : (M > 2 ? 4 : (M > 1 ? 2 :
 
 size_t decode_image_bytes_always(size_t M, size_t K, size_t N, bool dual)
 {
-    const DecodePlan pl = decode_plan(M, K, N, dual);
-    return align_up(DEC_IMG_HDR + (size_t)pl.cw * pl.sw * 4 * pl.nt * (size_t)decode_mrows(M) * 64, 256);
+    // the larger of the two plans' images, so that one workspace serves a call with or without the throughput flag
+    size_t bytes = 0;
+    for (int t = 0; t < 2; ++t) {
+        const DecodePlan pl = decode_plan(M, K, N, dual, t != 0);
+        const size_t b = align_up(DEC_IMG_HDR + (size_t)pl.cw * pl.sw * 4 * pl.nt * (size_t)decode_mrows(M) * 64, 256);
+        if (b > bytes) bytes = b;
+    }
+    return bytes;
 }
 
 size_t decode_image_bytes(size_t M, size_t K, size_t N, bool dual)
@@ -937,7 +962,7 @@ bitnet_status_t launch_decode(const ForwardArgs &a, cudaStream_t stream)
     p.n_peers = a.n_peers;
     for (int r = 0; r < a.n_peers && r < 8; ++r) p.y_peers[r] = a.y_peers[r];
     if (a.n_peers && dual) return fail(BITNET_ERR_UNSUPPORTED_OPERATION, "peer outputs are not available for the gate/up pair launch");
-    const DecodePlan pl = decode_plan(a.M, a.K, a.N, dual);
+    const DecodePlan pl = decode_plan(a.M, a.K, a.N, dual, (a.flags & BITNET_FLAG_THROUGHPUT) != 0);
 
     if (!in_i8 && a.image_ws && (a.force_split || use_split(a.M, a.K))) {
         // quantise once, then let every CTA fetch the result

@@ -48,19 +48,22 @@ def packed_len(n_values: int) -> int:
     return (n_values + 3) // 4
 
 
-def make_opts(path="auto", pdl=False, q_out=None, a_scale_out=None, acc_out=None, ldy=0, stages=0, y_peers=()) -> L.ForwardOpts:
+def make_opts(path="auto", pdl=False, q_out=None, a_scale_out=None, acc_out=None, ldy=0, stages=0, y_peers=(),
+              throughput=False) -> L.ForwardOpts:
     """``y_peers``: device addresses (ints) of the output slice in every GPU's full-width output."""
     if len(y_peers) > 8:
         raise InvalidConfig(f"at most 8 peer outputs (got {len(y_peers)})")
     peers = (C.c_void_p * 8)(*[C.c_void_p(int(p)) for p in y_peers])
-    return L.ForwardOpts(PATHS[path] if isinstance(path, str) else path, L.FLAG_PDL if pdl else 0,
+    return L.ForwardOpts(PATHS[path] if isinstance(path, str) else path,
+                         (L.FLAG_PDL if pdl else 0) | (L.FLAG_THROUGHPUT if throughput else 0),
                          q_out.data_ptr() if q_out is not None else None,
                          a_scale_out.data_ptr() if a_scale_out is not None else None,
                          acc_out.data_ptr() if acc_out is not None else None, ldy, stages, len(y_peers), peers)
 
 
 def bitlinear_forward(wp: torch.Tensor, w_scale: float, x: torch.Tensor, out_features: int, *, path="auto",
-                      pdl=False, debug=False, out: torch.Tensor | None = None, stages=0, stream=None, ldy=0, y_peers=()):
+                      pdl=False, debug=False, out: torch.Tensor | None = None, stages=0, stream=None, ldy=0, y_peers=(),
+                      throughput=False):
     """y[M,N] = BitLinear(x[M,K]) with packed ternary weights ``wp`` (uint8, ceil(N*K/4) bytes).
 
     With ``debug=True`` also returns the int8 activations, per-token scales and int32
@@ -81,7 +84,7 @@ def bitlinear_forward(wp: torch.Tensor, w_scale: float, x: torch.Tensor, out_fea
         dbg = {"q": torch.empty((M, K), dtype=torch.int8, device=x.device),
                "a_scale": torch.empty((M,), dtype=torch.float32, device=x.device),
                "acc": torch.empty((M, N), dtype=torch.int32, device=x.device)}
-    opts = make_opts(path, pdl, dbg.get("q"), dbg.get("a_scale"), dbg.get("acc"), ldy, stages, y_peers)
+    opts = make_opts(path, pdl, dbg.get("q"), dbg.get("a_scale"), dbg.get("acc"), ldy, stages, y_peers, throughput)
     need = C.c_size_t()
     check(L.load().bitnet_bitlinear_workspace_size(M, K, N, opts.path, C.byref(need)))
     ws = _workspace(need.value, x.device)
@@ -115,7 +118,7 @@ def quantize_activations(x: torch.Tensor, stream=None):
 
 
 def ffn_forward(w_gate, s_gate, w_up, s_up, w_down, s_down, x: torch.Tensor, ffn: int, *, path="auto", pdl=False,
-                out=None, h_out=None, stages=0, stream=None):
+                out=None, h_out=None, stages=0, stream=None, throughput=False):
     """FFN block y = down(up(x) * relu(gate(x))^2); returns (y [M,hidden], h [M,ffn])."""
     x = _require(x, torch.float32, "x")
     M, hidden = x.shape
@@ -125,7 +128,7 @@ def ffn_forward(w_gate, s_gate, w_up, s_up, w_down, s_down, x: torch.Tensor, ffn
             raise IncompatibleShapes(f"{name}: expected {packed_len(n * k)} packed bytes, got {w.numel()}")
     y = out if out is not None else torch.empty((M, hidden), dtype=torch.float32, device=x.device)
     h = h_out if h_out is not None else torch.empty((M, ffn), dtype=torch.float32, device=x.device)
-    opts = make_opts(path, pdl, stages=stages)
+    opts = make_opts(path, pdl, stages=stages, throughput=throughput)
     need = C.c_size_t()
     check(L.load().bitnet_ffn_workspace_size(M, hidden, ffn, opts.path, C.byref(need)))
     ws = _workspace(need.value, x.device)

@@ -68,9 +68,13 @@ enum {
 };
 
 enum {
-    BITNET_FLAG_PDL = 1u /* launch with programmatic dependent launch: the kernel starts
-                            fetching weights before the preceding kernel on the stream has
-                            finished and only then waits for it */
+    BITNET_FLAG_PDL = 1u, /* launch with programmatic dependent launch: the kernel starts
+                             fetching weights before the preceding kernel on the stream has
+                             finished and only then waits for it */
+    BITNET_FLAG_THROUGHPUT = 2u /* decode shapes: smaller CTAs (four consumer warps, at most two
+                                   weight stages), so that CTAs of four launches share an SM.
+                                   A single call gets slower; independent calls issued on
+                                   several streams get about a quarter more throughput */
 };
 
 /* Options of a forward call; zero-initialise for the defaults. */

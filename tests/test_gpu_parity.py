@@ -391,3 +391,28 @@ def test_backend_host_ffn_async_streams():
         assert np.array_equal(outs[0], oracle.ffn_forward(packs[0], scales[0], packs[1], scales[1], packs[2], scales[2], xs[0], ffn)[0])
     finally:
         b.close()
+
+
+@pytest.mark.parametrize("M,K,N", [(1, 2560, 6912), (4, 6912, 2560), (8, 2560, 6912), (3, 320, 129), (16, 1024, 144), (1, 8192, 3584)])
+def test_decode_throughput_flag_same_bits(M, K, N):
+    # the small-CTA plan (four consumer warps) gives the same bits as the default plan
+    wp, ws, x = case(11, M, K, N)
+    y0, d0 = ops.bitlinear_forward(dev(wp), ws, dev(x), N, debug=True, path="decode")
+    y1, d1 = ops.bitlinear_forward(dev(wp), ws, dev(x), N, debug=True, path="decode", throughput=True)
+    assert torch.equal(y0, y1) and torch.equal(d0["acc"], d1["acc"]) and torch.equal(d0["q"], d1["q"])
+    assert_parity(d1, y1, oracle.bitlinear_forward(wp, ws, x, N), M, N)
+
+
+def test_ffn_throughput_flag_same_bits():
+    z = np.load(GOLDEN / "ffn_m4_h128_f320.npz")
+    H, F = int(z["hidden"]), int(z["ffn"])
+    y, _ = ops.ffn_forward(dev(z["gate"]), float(z["s_gate"]), dev(z["up"]), float(z["s_up"]), dev(z["down"]), float(z["s_down"]),
+                           dev(z["x"]), F, throughput=True)
+    assert np.array_equal(y.cpu().numpy(), z["y"])
+    for M in (1, 4, 8):
+        wg, sg, x = case(12, M, 2560, 6912)
+        wu, su, _ = case(13, M, 2560, 6912)
+        wd, sd, _ = case(14, M, 6912, 2560)
+        a, _ = ops.ffn_forward(dev(wg), sg, dev(wu), su, dev(wd), sd, dev(x), 6912)
+        b, _ = ops.ffn_forward(dev(wg), sg, dev(wu), su, dev(wd), sd, dev(x), 6912, throughput=True)
+        assert torch.equal(a, b)
