@@ -449,6 +449,56 @@ def single_kernel_figures(torch, ops, gen, peak):
         out[name] = {"us": us, "gbs": gbs, "frac_of_peak": gbs / peak, "weight_copies": copies}
         del W
     out["cfg3_prefill_layer_m2048"] = prefill_layer_figures(torch, ops, gen)
+    out["cfg4_bitlinear_stack"] = decode_stack_figures(torch, ops, gen)
+    return out
+
+
+def decode_stack_figures(torch, ops, gen):
+    """BitLinear share of one decode step of the 2B architecture: 30 layers x (q 2560->2560, k and v
+    2560->640, o 2560->2560, FFN 2560->6912->2560) + the LM head 2560->128256, as ONE dependent chain
+    (CUDA graph, programmatic dependent launch) at M = sequences held by one GPU (64 sequences over
+    1/2/4/8 GPUs).  Attention, norms and sampling are not part of this path and not in the figure, so
+    tokens/s here is an upper bound for the full model's decode rate."""
+    H, F, V, L = HIDDEN, FFN, 128256, LAYERS
+    proj = [(H, H), (H, 640), (H, 640), (H, H)]
+    W = [[gen_packed_on_device(torch, n * k, gen) for (k, n) in proj] +
+         [gen_packed_on_device(torch, F * H, gen) for _ in range(3)] for _ in range(L)]
+    head = gen_packed_on_device(torch, V * H, gen)
+    out = {}
+    for M in (64, 32, 16, 8):
+        x = gen_activations_on_device(torch, (M, H), gen)
+        ys = [torch.empty((M, n), device="cuda") for (k, n) in proj]
+        yf, hf, logits = torch.empty((M, H), device="cuda"), torch.empty((M, F), device="cuda"), torch.empty((M, V), device="cuda")
+
+        def step():
+            for l in range(L):
+                for i, (k, n) in enumerate(proj):
+                    ops.bitlinear_forward(W[l][i], 0.01, x, n, out=ys[i], pdl=True)
+                ops.ffn_forward(W[l][4], 0.01, W[l][5], 0.01, W[l][6], 0.01, x, F, out=yf, h_out=hf, pdl=True)
+            ops.bitlinear_forward(head, 0.01, x, V, out=logits, pdl=True)
+
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            step()
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                step()
+        for _ in range(2):
+            g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 5
+        e0.record()
+        for _ in range(reps):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        nbytes = L * (sum(call_bytes(M, k, n) for (k, n) in proj) + ffn_bytes(M)) + call_bytes(M, H, V)
+        out[f"m{M}"] = {"ms_per_step": ms, "tokens_per_s_bitlinear_only": M / (ms * 1e-3), "gbs": nbytes / (ms * 1e-3) / 1e9,
+                        "sequences_per_gpu": M, "gpus_for_64_sequences": 64 // M}
+        del g
     return out
 
 
