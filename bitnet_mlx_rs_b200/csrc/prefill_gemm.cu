@@ -94,6 +94,9 @@ __global__ void __launch_bounds__(THREADS, THREADS == 128 ? 8 : 4) quantize_rows
     // the GEMM that follows may start (allocate tensor memory, fetch packed weights) while this runs;
     // it waits for this grid before it touches anything written here
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // launched with programmatic dependent launch itself (BITNET_FLAG_PDL): x and the scratch this grid
+    // overwrites belong to the kernels before it until they have finished
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     // the GEMM counts the parts of split tiles in these; they start at zero
     if (blockIdx.x == 0)
         for (int i = threadIdx.x; i < n_counters; i += THREADS) counters[i] = 0u;
@@ -451,6 +454,8 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     __shared__ __align__(8) unsigned long long s_in[4];   // per epilogue warp: a fetched part of a split tile has landed
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // a kernel launched behind this one with programmatic dependent launch may be scheduled as CTAs here retire
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(pf_smem_raw) + 1023) & ~uintptr_t(1023));
     // activation stages start 1024-byte aligned (the 128-byte swizzle needs it); the packed weights follow
     auto stage_x = [&](int s) { return smem + (size_t)s * PF_X_BYTES; };
@@ -968,12 +973,27 @@ bitnet_status_t launch_prefill(const ForwardArgs &a, void *workspace, size_t wor
 
     const PfPlan plan = pf_plan(a.M, a.K, a.N);
     const int tiles = (int)plan.tiles;
-    if (a.K / 16 <= 256)
-        quantize_rows_perm_kernel<128><<<(unsigned)a.M, 128, 0, stream>>>(a.x, a.K, q_perm, a_scale, rowsum, a.q_out, a.a_scale_out,
-                                                                           counters, 2 * tiles);
-    else
-        quantize_rows_perm_kernel<256><<<(unsigned)a.M, 256, 0, stream>>>(a.x, a.K, q_perm, a_scale, rowsum, a.q_out, a.a_scale_out,
-                                                                           counters, 2 * tiles);
+    {
+        cudaLaunchConfig_t qcfg = {};
+        cudaLaunchAttribute qattr[1];
+        const bool short_rows = a.K / 16 <= 256;
+        qcfg.gridDim = dim3((unsigned)a.M);
+        qcfg.blockDim = dim3(short_rows ? 128 : 256);
+        qcfg.stream = stream;
+        qcfg.attrs = qattr;
+        if (a.flags & BITNET_FLAG_PDL) {   // the caller chains launches: start while the previous kernel drains
+            qattr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            qattr[0].val.programmaticStreamSerializationAllowed = 1;
+            qcfg.numAttrs = 1;
+        }
+        const int n_counters = 2 * tiles;
+        if (short_rows)
+            BITNET_CUDA(cudaLaunchKernelEx(&qcfg, quantize_rows_perm_kernel<128>, a.x, a.K, q_perm, a_scale, rowsum, a.q_out,
+                                           a.a_scale_out, counters, n_counters));
+        else
+            BITNET_CUDA(cudaLaunchKernelEx(&qcfg, quantize_rows_perm_kernel<256>, a.x, a.K, q_perm, a_scale, rowsum, a.q_out,
+                                           a.a_scale_out, counters, n_counters));
+    }
     BITNET_TRY(check_launch("quantize_rows_perm_kernel"));
 
     CUtensorMap map_x, map_w, map_y;
