@@ -200,6 +200,7 @@ decode_kernel(const DecodeParams p)
     constexpr int NTD = NT * NW;
     constexpr int NP = 1;                     // accumulator sets per j class
     constexpr int U = 3;                      // 16-wide groups a lane has in flight in the quantiser
+    constexpr int DEC_DEFER = 1;              // a block is finished this many blocks after its sums were handed in
 
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ __align__(8) unsigned long long s_full[DEC_MAX_STAGES], s_done[DEC_MAX_STAGES], s_empty[DEC_MAX_STAGES];
@@ -493,12 +494,69 @@ decode_kernel(const DecodeParams p)
             off_b[w][s2] = ci < Cw ? (unsigned)(w * 16 + g + 8) * row_bytes + col : p.stage_bytes;
         }
 
+    bool alive = true;   // false once a bounded wait gave up: the CTA only drains from then on
+    // a stage is refilled only after its block was finished, so the deferral must stay below the ring depth
+    // (and a CTA with only a few blocks gains nothing from it: its last blocks would just end later)
+    const int want_defer = nb >= 6 ? DEC_DEFER : 0;
+    const int defer = NS > want_defer ? want_defer : NS - 1;
+    // Finishes block j if this warp is on duty for it: waits until every warp's partial sums of the block are
+    // in, adds them up, releases the stage, dequantises and stores.
+    auto finish_block = [&](int j) {
+        if (!alive || ((j + (int)blockIdx.x) & (DEC_CWARPS - 1)) != warp) return;
+        const int sj = j % NS;
+        if (!mbar_wait(&s_done[sj], (unsigned)(j / NS) & 1u)) { alive = false; return; }
+        const int4 *red = reinterpret_cast<const int4 *>(s_red) + (size_t)sj * (DEC_CWARPS * NTD * 32);
+        const int row_a = (b0 + j * bstride) * 16 + g, row_b = row_a + 8;
+        int tot[NTD][4];
+#pragma unroll
+        for (int u = 0; u < NTD; ++u) {
+            tot[u][0] = tot[u][1] = tot[u][2] = tot[u][3] = 0;
+#pragma unroll
+            for (int w2 = 0; w2 < DEC_CWARPS; ++w2) {
+                const int4 v = red[(w2 * NTD + u) * 32 + lane];
+                tot[u][0] += v.x; tot[u][1] += v.y; tot[u][2] += v.z; tot[u][3] += v.w;
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_empty[sj]);   // release: the stage and its sums may be reused
+#pragma unroll
+        for (int t = 0; t < NT; ++t)
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const int m = 8 * t + 2 * tig + (r & 1);
+                const int row = (r & 2) ? row_b : row_a;
+                if (m < p.M && row < p.N) {
+                    const size_t o = (size_t)m * p.ldy + row;
+                    float out;
+                    if constexpr (DUAL) {
+                        const float a = s_ascale[m];
+                        const float gate = __fmul_rn((float)tot[t][r], __fmul_rn(p.w_scale, a));
+                        const float up = __fmul_rn((float)tot[NT + t][r], __fmul_rn(p.w_scale2, a));
+                        const float rl = fmaxf(gate, 0.0f);
+                        out = __fmul_rn(up, __fmul_rn(rl, rl));
+                        p.y[o] = out;
+                    } else {
+                        if (p.acc_out) p.acc_out[o] = tot[t][r];
+                        out = __fmul_rn((float)tot[t][r], __fmul_rn(p.w_scale, s_ascale[m]));
+                        if (p.n_peers) {   // this GPU's column slice, stored into every GPU's full-width output
+                            for (int pr = 0; pr < p.n_peers; ++pr) p.y_peers[pr][o] = out;
+                        } else if (p.y) {
+                            p.y[o] = out;
+                        }
+                    }
+                    if (p.amax_out) {
+                        const unsigned key = abs_key(out);
+                        if (key > s_okey[m]) atomicMax(&s_okey[m], key);
+                    }
+                }
+            }
+    };
+
     for (int i = 0; i < nb; ++i) {
         const int s = i % NS;
         const unsigned parity = (unsigned)(i / NS) & 1u;
+        if (!alive) return;
         if (!mbar_wait(&s_full[s], parity)) return;
-        const int blk = b0 + i * bstride;
-        const int row_a = blk * 16 + g, row_b = row_a + 8;
         const unsigned char *stage = s_w + (size_t)s * p.stage_stride;
 
         int acc[NW][NT][NP][4][4];   // [matrix][token tile][chain][j class][fragment register]
@@ -565,54 +623,12 @@ decode_kernel(const DecodeParams p)
         __syncwarp();
         if (lane == 0) mbar_arrive(&s_done[s]);   // release: this warp's sums are in, its reads of the stage are over
 
-        // the warps take turns to finish a block: wait until all partial sums are in, add them up
-        if (((i + (int)blockIdx.x) & (DEC_CWARPS - 1)) == warp) {
-            if (!mbar_wait(&s_done[s], parity)) return;
-            int tot[NTD][4];
-#pragma unroll
-            for (int u = 0; u < NTD; ++u) {
-                tot[u][0] = tot[u][1] = tot[u][2] = tot[u][3] = 0;
-#pragma unroll
-                for (int w2 = 0; w2 < DEC_CWARPS; ++w2) {
-                    const int4 v = red[(w2 * NTD + u) * 32 + lane];
-                    tot[u][0] += v.x; tot[u][1] += v.y; tot[u][2] += v.z; tot[u][3] += v.w;
-                }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&s_empty[s]);   // release: the stage and its sums may be reused
-#pragma unroll
-            for (int t = 0; t < NT; ++t)
-#pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                    const int m = 8 * t + 2 * tig + (r & 1);
-                    const int row = (r & 2) ? row_b : row_a;
-                    if (m < p.M && row < p.N) {
-                        const size_t o = (size_t)m * p.ldy + row;
-                        float out;
-                        if constexpr (DUAL) {
-                            const float a = s_ascale[m];
-                            const float gate = __fmul_rn((float)tot[t][r], __fmul_rn(p.w_scale, a));
-                            const float up = __fmul_rn((float)tot[NT + t][r], __fmul_rn(p.w_scale2, a));
-                            const float rl = fmaxf(gate, 0.0f);
-                            out = __fmul_rn(up, __fmul_rn(rl, rl));
-                            p.y[o] = out;
-                        } else {
-                            if (p.acc_out) p.acc_out[o] = tot[t][r];
-                            out = __fmul_rn((float)tot[t][r], __fmul_rn(p.w_scale, s_ascale[m]));
-                            if (p.n_peers) {   // this GPU's column slice, stored into every GPU's full-width output
-                                for (int pr = 0; pr < p.n_peers; ++pr) p.y_peers[pr][o] = out;
-                            } else if (p.y) {
-                                p.y[o] = out;
-                            }
-                        }
-                        if (p.amax_out) {
-                            const unsigned key = abs_key(out);
-                            if (key > s_okey[m]) atomicMax(&s_okey[m], key);
-                        }
-                    }
-                }
-        }
+        // the warps take turns to finish a block -- DEC_DEFER blocks later, so that the warp on duty finds the
+        // other warps' sums already there instead of stalling its own next block behind the slowest warp
+        if (i >= defer) finish_block(i - defer);
     }
+    for (int j = nb > defer ? nb - defer : 0; j < nb; ++j) finish_block(j);
+    if (!alive) return;
     if (p.amax_out) {   // this CTA's share of the per-token absmax of what the launch wrote
         consumer_barrier<CW>();
         if (tid < DEC_MAX_TOKENS) p.amax_out[(size_t)tid * 256 + blockIdx.x] = s_okey[tid];   // [token][CTA slot]
