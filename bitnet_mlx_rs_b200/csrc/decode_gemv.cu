@@ -501,10 +501,9 @@ decode_kernel(const DecodeParams p)
     const int defer = NS > want_defer ? want_defer : NS - 1;
     // Finishes block j if this warp is on duty for it: waits until every warp's partial sums of the block are
     // in, adds them up, releases the stage, dequantises and stores.
-    auto finish_block = [&](int j) {
+    auto finish_block = [&](int j, int sj, unsigned pj) {   // sj = j % NS, pj = (j / NS) & 1, kept by the caller
         if (!alive || ((j + (int)blockIdx.x) & (DEC_CWARPS - 1)) != warp) return;
-        const int sj = j % NS;
-        if (!mbar_wait(&s_done[sj], (unsigned)(j / NS) & 1u)) { alive = false; return; }
+        if (!mbar_wait(&s_done[sj], pj)) { alive = false; return; }
         const int4 *red = reinterpret_cast<const int4 *>(s_red) + (size_t)sj * (DEC_CWARPS * NTD * 32);
         const int row_a = (b0 + j * bstride) * 16 + g, row_b = row_a + 8;
         int tot[NTD][4];
@@ -552,9 +551,13 @@ decode_kernel(const DecodeParams p)
             }
     };
 
-    for (int i = 0; i < nb; ++i) {
-        const int s = i % NS;
-        const unsigned parity = (unsigned)(i / NS) & 1u;
+    // stage index and barrier phase of block i and of the block being finished, advanced without divisions
+    int s = 0, sj = 0, jn = 0;
+    unsigned parity = 0, pj = 0;
+    auto advance = [&](int &stage, unsigned &phase) {
+        if (++stage == NS) { stage = 0; phase ^= 1u; }
+    };
+    for (int i = 0; i < nb; ++i, advance(s, parity)) {
         if (!alive) return;
         if (!mbar_wait(&s_full[s], parity)) return;
         const unsigned char *stage = s_w + (size_t)s * p.stage_stride;
@@ -625,9 +628,13 @@ decode_kernel(const DecodeParams p)
 
         // the warps take turns to finish a block -- DEC_DEFER blocks later, so that the warp on duty finds the
         // other warps' sums already there instead of stalling its own next block behind the slowest warp
-        if (i >= defer) finish_block(i - defer);
+        if (i >= defer) {
+            finish_block(jn, sj, pj);
+            ++jn;
+            advance(sj, pj);
+        }
     }
-    for (int j = nb > defer ? nb - defer : 0; j < nb; ++j) finish_block(j);
+    for (; jn < nb; ++jn, advance(sj, pj)) finish_block(jn, sj, pj);
     if (!alive) return;
     if (p.amax_out) {   // this CTA's share of the per-token absmax of what the launch wrote
         consumer_barrier<CW>();
