@@ -433,20 +433,35 @@ def single_kernel_figures(torch, ops, gen, peak):
         W = [gen_packed_on_device(torch, N * K, gen) for _ in range(copies)]
         x = gen_activations_on_device(torch, (M, K), gen)
         y = torch.empty((M, N), device="cuda")
-        for w in W[:3]:
-            ops.bitlinear_forward(w, 0.01, x, N, out=y, pdl=True)
+        def rotate():
+            for w in W:
+                ops.bitlinear_forward(w, 0.01, x, N, out=y, pdl=True)
+
+        rotate()
         torch.cuda.synchronize()
+        run, launch = rotate, "stream launches"
+        try:   # one pass over all copies as a CUDA graph: launch overhead stays out of the figure
+            side = torch.cuda.Stream()
+            with torch.cuda.stream(side):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    rotate()
+            g.replay()
+            torch.cuda.synchronize()
+            run, launch = g.replay, "cuda graph"
+        except Exception as ex:
+            print(f"single-kernel figure {name}: graph capture failed ({ex}); timing stream launches", file=sys.stderr)
+            torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         reps = 3
         e0.record()
         for _ in range(reps):
-            for w in W:
-                ops.bitlinear_forward(w, 0.01, x, N, out=y, pdl=True)
+            run()
         e1.record()
         torch.cuda.synchronize()
         us = e0.elapsed_time(e1) * 1e3 / (reps * copies)
         gbs = call_bytes(M, K, N) / us / 1e3
-        out[name] = {"us": us, "gbs": gbs, "frac_of_peak": gbs / peak, "weight_copies": copies}
+        out[name] = {"us": us, "gbs": gbs, "frac_of_peak": gbs / peak, "weight_copies": copies, "launch": launch}
         del W
     out["cfg3_prefill_layer_m2048"] = prefill_layer_figures(torch, ops, gen)
     out["cfg4_bitlinear_stack"] = decode_stack_figures(torch, ops, gen)
