@@ -26,26 +26,11 @@
 // (bitnet-inference/src/engine/ternary_operations.rs:117-172, :283-338) on the packed
 // layout of BitPacked2BitPacker (bitnet-quant/src/quantization/packing.rs:352-394);
 // replaces w2a8_gemv_kernel (bitnet-cuda/src/kernels/w2a8_gemv.cu:100-182).
-#include <cstdlib>
+#include <mutex>
 
 #include "common.cuh"
 
 namespace bitnet {
-
-#ifdef BITNET_PHASE_TIMERS
-// Debug builds record %globaltimer at phase boundaries (warps 0 and 1 of the first CTAs).
-__device__ unsigned long long g_phase_ns[512][16];
-#define PHASE(i)                                                                      \
-    do {                                                                              \
-        if ((threadIdx.x & 31) == 0 && (threadIdx.x >> 5) <= 1 && blockIdx.x < 512) { \
-            unsigned long long t_;                                                    \
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                    \
-            g_phase_ns[blockIdx.x][(i) + 8 * (threadIdx.x >> 5)] = t_;                \
-        }                                                                             \
-    } while (0)
-#else
-#define PHASE(i) do { } while (0)
-#endif
 
 constexpr int DEC_MAX_CWARPS = 16;                     // consumer warps: 8 (two CTAs per SM) or 16
 constexpr int DEC_MAX_STAGES = 8;
@@ -75,7 +60,8 @@ struct DecodeParams {
     int stages;          // depth of the weight ring
     int stages_free;     // stages that do not overlap the activation staging area
     unsigned stage_bytes;   // one block of one matrix is 16 * K/4 contiguous bytes; a stage holds NW of them
-    unsigned stage_stride;  // stage_bytes plus a 128-byte tail whose first 16 bytes stay zero
+    unsigned stage_stride;  // stage_bytes plus 128 bytes of padding
+    unsigned zero_offset;   // 16 zero bytes in dynamic shared memory that no stage and no staging area ever covers
     const unsigned *amax_in;   // optional: per-token absmax keys left by the producer kernel, [16 tokens][256 CTA slots]
     int n_amax_in;
     unsigned *amax_out;        // optional: this CTA's per-token absmax keys of what it wrote, same layout
@@ -119,9 +105,7 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned pari
             : "r"(addr), "r"(parity)
             : "memory");
         if (done) return true;
-#ifndef BITNET_NO_BACKOFF
         __nanosleep(n < 16 ? 32 : 128);   // a waiting warp must not take issue slots from the working ones
-#endif
     }
     atomicOr(&g_decode_error_flags, 1u);
     return false;
@@ -174,12 +158,7 @@ __device__ __noinline__ int quantize_one_slow(float x, float scale) { return qua
 
 __device__ __forceinline__ int quantize_any(float x, float scale, bool fast)
 {
-#ifdef BITNET_NO_SLOW_PATH
-    (void)fast;
-    return quantize_fast(x, scale);
-#else
     return fast ? quantize_fast(x, scale) : quantize_one_slow(x, scale);
-#endif
 }
 
 // Dynamic shared memory: the weight ring [stages x stage_bytes], the activation staging
@@ -215,19 +194,11 @@ decode_kernel(const DecodeParams p)
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, tig = lane & 3;
     const int NS = p.stages;
-    PHASE(0);
 
-#ifdef DEC_CONTIGUOUS_BLOCKS
-    const int b0 = (int)((long long)blockIdx.x * p.n_blocks / gridDim.x);
-    const int b1 = (int)((long long)(blockIdx.x + 1) * p.n_blocks / gridDim.x);
-    const int nb = b1 - b0;
-    const int bstride = 1;
-#else
     // blocks are dealt round-robin: every CTA's stream of 16-row blocks is spread over the whole
     // weight matrix in the same way, so no CTA sits on a slower set of memory channels
     const int b0 = (int)blockIdx.x, bstride = (int)gridDim.x;
     const int nb = (p.n_blocks - b0 + bstride - 1) / bstride;
-#endif
     const unsigned row_bytes = (unsigned)p.K / 4;
 
     unsigned char *s_w = smem;
@@ -247,7 +218,7 @@ decode_kernel(const DecodeParams p)
     }
     if (tid < DEC_MAX_TOKENS) { s_key[tid] = 0; s_okey[tid] = 0; }
     for (int i = tid; i < DEC_MAX_CWARPS * DEC_MAX_TOKENS; i += DEC_THREADS) (&s_sumq[0][0])[i] = 0;
-    if (tid < NS * 4) reinterpret_cast<unsigned *>(s_w + (size_t)(tid >> 2) * p.stage_stride + p.stage_bytes)[tid & 3] = 0;
+    if (tid < 4) reinterpret_cast<unsigned *>(smem + p.zero_offset)[tid] = 0;
     __syncthreads();
 
     // ======================= producer warp: keep the ring full ===============================
@@ -278,7 +249,6 @@ decode_kernel(const DecodeParams p)
 
     // ======================= consumer warps =====================================================
     asm volatile("griddepcontrol.wait;" ::: "memory");   // activations come from the previous kernel
-    PHASE(2);
 
     const int cw0 = (int)((long long)warp * p.chunks / DEC_CWARPS);
     const int cw1 = (int)((long long)(warp + 1) * p.chunks / DEC_CWARPS);
@@ -319,7 +289,6 @@ decode_kernel(const DecodeParams p)
         if (tid < DEC_CWARPS * DEC_MAX_TOKENS) (&s_sumq[0][0])[tid] = reinterpret_cast<const int *>(s_bst)[tid];
         if (tid < DEC_MAX_TOKENS) s_ascale[tid] = reinterpret_cast<const float *>(s_bst + DEC_MAX_CWARPS * DEC_MAX_TOKENS * 4)[tid];
         consumer_barrier<CW>();
-        PHASE(3);
     } else {
         // ---- pass 1: per-token absmax, folded CTA-wide ------------------------------------------------
         if constexpr (!IN_I8) {
@@ -385,7 +354,6 @@ decode_kernel(const DecodeParams p)
             if (tid < p.M) s_ascale[tid] = 1.0f;
             if (lane == 0) mbar_arrive(&s_x_issued);
         }
-        PHASE(3);
 
         // ---- pass 2: quantise this warp's slice into fragment order ---------------------------------------
         {
@@ -453,7 +421,6 @@ decode_kernel(const DecodeParams p)
             }
             if (cur_sum) atomicAdd(&s_sumq[warp][cur_m], cur_sum);
         }
-        PHASE(5);
     }
     __syncwarp();
 
@@ -470,19 +437,20 @@ decode_kernel(const DecodeParams p)
         __syncwarp();
         if (lane == 0) mbar_arrive(&s_bst_free);   // the staging area may be overwritten by weights
     }
-    PHASE(6);
     int sq[NT][2];
 #pragma unroll
     for (int t = 0; t < NT; ++t) {
         sq[t][0] = s_sumq[warp][8 * t + 2 * tig];
         sq[t][1] = s_sumq[warp][8 * t + 2 * tig + 1];
     }
-    PHASE(4);
 
     // ---- main loop over this CTA's blocks -----------------------------------------------------------------
-    // Byte offsets of this lane's 16-byte chunks inside a stage; a chunk beyond the slice reads the
-    // stage's zero tail instead.  Rows past N of the last block hold stale bytes: they only feed
-    // accumulators of rows that are never written.
+    // Byte offsets of this lane's 16-byte chunks inside a stage.  A chunk beyond the slice must read
+    // zeros as weights (its activation fragments were never written and hold stale bytes): it reads a
+    // zero region of its own, outside every stage -- not a stage's padding, which the activation
+    // staging area may cover when the ring grows over it.  Rows past N of the last block hold stale
+    // bytes: they only feed accumulators of rows that are never written.
+    constexpr unsigned OFF_ZERO = 0xffffffffu;
     unsigned off_a[NW][SW], off_b[NW][SW];
 #pragma unroll
     for (int w = 0; w < NW; ++w)
@@ -490,8 +458,8 @@ decode_kernel(const DecodeParams p)
         for (int s2 = 0; s2 < SW; ++s2) {
             const int ci = s2 * 4 + tig;
             const unsigned col = (unsigned)(cw0 + ci) * 16;
-            off_a[w][s2] = ci < Cw ? (unsigned)(w * 16 + g) * row_bytes + col : p.stage_bytes;
-            off_b[w][s2] = ci < Cw ? (unsigned)(w * 16 + g + 8) * row_bytes + col : p.stage_bytes;
+            off_a[w][s2] = ci < Cw ? (unsigned)(w * 16 + g) * row_bytes + col : OFF_ZERO;
+            off_b[w][s2] = ci < Cw ? (unsigned)(w * 16 + g + 8) * row_bytes + col : OFF_ZERO;
         }
 
     bool alive = true;   // false once a bounded wait gave up: the CTA only drains from then on
@@ -560,7 +528,7 @@ decode_kernel(const DecodeParams p)
     for (int i = 0; i < nb; ++i, advance(s, parity)) {
         if (!alive) return;
         if (!mbar_wait(&s_full[s], parity)) return;
-        const unsigned char *stage = s_w + (size_t)s * p.stage_stride;
+        const unsigned stage_off = (unsigned)s * p.stage_stride;
 
         int acc[NW][NT][NP][4][4];   // [matrix][token tile][chain][j class][fragment register]
 #pragma unroll
@@ -587,8 +555,8 @@ decode_kernel(const DecodeParams p)
                     }
 #pragma unroll
                 for (int w = 0; w < NW; ++w) {
-                    const uint4 wa = *reinterpret_cast<const uint4 *>(stage + off_a[w][s2]);
-                    const uint4 wb = *reinterpret_cast<const uint4 *>(stage + off_b[w][s2]);
+                    const uint4 wa = *reinterpret_cast<const uint4 *>(smem + (off_a[w][s2] != OFF_ZERO ? stage_off + off_a[w][s2] : p.zero_offset));
+                    const uint4 wb = *reinterpret_cast<const uint4 *>(smem + (off_b[w][s2] != OFF_ZERO ? stage_off + off_b[w][s2] : p.zero_offset));
 #pragma unroll
                     for (int pr = 0; pr < 2; ++pr) {
                         const unsigned a_lo0 = word_of(wa, 2 * pr), a_lo1 = word_of(wa, 2 * pr + 1);
@@ -606,7 +574,6 @@ decode_kernel(const DecodeParams p)
             }
         }
 
-        if (i == 0) PHASE(7);
         // exact partial sums of sum_k (code-1)*q over this warp's K slice, left in this warp's slot
         int4 *red = reinterpret_cast<int4 *>(s_red) + (size_t)s * (DEC_CWARPS * NTD * 32);
 #pragma unroll
@@ -640,15 +607,7 @@ decode_kernel(const DecodeParams p)
         consumer_barrier<CW>();
         if (tid < DEC_MAX_TOKENS) p.amax_out[(size_t)tid * 256 + blockIdx.x] = s_okey[tid];   // [token][CTA slot]
     }
-    PHASE(1);
 }
-
-#ifdef BITNET_PHASE_TIMERS
-extern "C" int bitnet_debug_read_phases(unsigned long long *host)
-{
-    return (int)cudaMemcpyFromSymbol(host, g_phase_ns, sizeof(g_phase_ns));
-}
-#endif
 
 // Quantises x[M,K] once for every CTA of the decode kernel that follows: one CTA per token,
 // one read of the row (it stays in registers between the absmax fold and the rounding), and
@@ -821,20 +780,33 @@ static bitnet_status_t launch_one(DecodeParams p, uint32_t flags, cudaStream_t s
         bst_offset = (size_t)stages * p.stage_stride;
         smem = bst_offset + bst_bytes + (size_t)stages * red_per_stage;
     }
-    if (smem > 227 * 1024 || stages_free < 1)
+    if (smem + 16 > 227 * 1024 || stages_free < 1)
         return fail(BITNET_ERR_UNSUPPORTED_OPERATION, "decode kernel: K=%d needs %zu bytes of shared memory", p.K, smem);
     p.stages = stages;
     p.stages_free = stages_free;
     p.bst_offset = (unsigned)bst_offset;
     p.red_offset = (unsigned)(smem - (size_t)stages * red_per_stage);
+    p.zero_offset = (unsigned)smem;   // after everything else: nothing is ever copied over it
+    smem += 16;
 
-    static size_t smem_set[64] = {0};   // per instantiation and device; one launching thread per process
-    int dev = 0;
-    BITNET_CUDA(cudaGetDevice(&dev));
-    const bool tracked = dev >= 0 && dev < 64;
-    if (smem > 40 * 1024 && (!tracked || smem > smem_set[dev])) {   // static shared memory counts against the default 48 KB too
-        BITNET_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        if (tracked) smem_set[dev] = smem;
+    // The attribute is raised once per instantiation and device to the most this kernel can ever ask
+    // for, under a lock: host threads launch concurrently (one per stream), and a smaller value set by
+    // one of them must never undercut a launch another one is about to make.
+    {
+        static std::mutex mu;
+        static bool raised[64] = {false};
+        int dev = 0;
+        BITNET_CUDA(cudaGetDevice(&dev));
+        const bool tracked = dev >= 0 && dev < 64;
+        std::lock_guard<std::mutex> lock(mu);
+        if (!tracked || !raised[dev]) {
+            cudaFuncAttributes fa;
+            int optin = 0;
+            BITNET_CUDA(cudaFuncGetAttributes(&fa, kernel));
+            BITNET_CUDA(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+            BITNET_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, optin - (int)fa.sharedSizeBytes));
+            if (tracked) raised[dev] = true;
+        }
     }
 
     cudaLaunchConfig_t cfg = {};
@@ -875,10 +847,8 @@ static DecodePlan decode_plan(size_t M, size_t K, size_t N, bool dual, bool thro
     pl.wide = pl.breg && blocks_per_cta >= 6 && steps_needed(K, 16) <= 2;
     pl.cw = pl.wide ? 16 : 8;
     pl.sw = round_sw(steps_needed(K, pl.cw));
-    // throughput mode: four consumer warps, so that four CTAs (of different launches) share an SM
-    // (BITNET_FLAG_THROUGHPUT; the environment variable switches it on for every call of the process)
-    static const int small_env = getenv("BITNET_DECODE_SMALL_CTA") ? atoi(getenv("BITNET_DECODE_SMALL_CTA")) : 0;
-    if ((throughput || small_env) && !pl.breg) {
+    // throughput mode (BITNET_FLAG_THROUGHPUT): four consumer warps, so that four CTAs (of different launches) share an SM
+    if (throughput && !pl.breg) {
         const int sw4 = round_sw(steps_needed(K, 4));
         if (steps_needed(K, 4) <= 8 && (sw4 <= 4 || (pl.nt == 1 && !dual))) {
             pl.cw = 4;
@@ -924,16 +894,7 @@ static bitnet_status_t launch_sw(const DecodePlan &pl, const DecodeParams &p, ui
 // Activation count (M*K) above which the activations are quantised by their own small launch
 // instead of by every CTA of the decode kernel: the redundant per-CTA quantiser work grows with
 // M*K, while the extra launch costs a fixed couple of microseconds in the dependency chain.
-static bool use_split(size_t M, size_t K)
-{
-    static long v = -1;
-    if (v < 0) {
-        const char *e = getenv("BITNET_DECODE_SPLIT_MIN_ELEMS");
-        v = e ? atol(e) : 8192;
-        if (v < 0) v = 0;
-    }
-    return M * K > (size_t)v;
-}
+static bool use_split(size_t M, size_t K) { return M * K > 8192; }
 
 // Token rows kept per 8-token tile of the staging area: the power of two that covers M (8 from 5 tokens on).
 static int decode_mrows(size_t M) { return M > 4 ? 8 : (M > 2 ? 4 : (M > 1 ? 2 : 1)); }

@@ -11,13 +11,18 @@
 // Cost and limits: every GPU that loads the library keeps BITNET_STATIC_SCRATCH_BYTES
 // (136 KiB) resident until the process exits.  The array is shared by all calls on a device:
 // two calls that can overlap on the GPU (different streams, no dependency) race on it.  It keeps
-// the previous call's bytes; nothing in it has to start at zero, because the quantiser
-// overwrites every byte the following kernel reads for real tokens, and the stale remainder
-// only feeds accumulator columns of tokens that do not exist and are never written.
+// the previous call's bytes, and nothing in it has to start at zero: the quantiser overwrites
+// every byte that stands for a real token and a real k, and the stale remainder is of two kinds,
+// both harmless.  Rows of tokens that do not exist feed accumulator columns that are never
+// written.  Fragment slots of k chunks past the end of a warp's K slice are multiplied by
+// weight words that the decode kernel reads from a zero region of its own in shared memory (never
+// from the ring or its padding), so their product is zero whatever the slots hold.
 //
 // The first call on a device looks up the array's device address (no allocation, but a
 // runtime call that is not a stream operation): make that first call before any stream
 // capture begins.
+#include <atomic>
+
 #include "common.cuh"
 
 namespace bitnet {
@@ -28,21 +33,22 @@ constexpr size_t kStaticScratchBytes = 136 * 1024;
 // address comes from cudaGetSymbolAddress below.
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
-// One address per device, filled by the first call made with that device current.
-static void *g_scratch_addr[64] = {nullptr};
+// One address per device, filled by the first call made with that device current.  Host threads
+// may make that first call at the same time: they resolve the same address, and the slot is atomic.
+static std::atomic<void *> g_scratch_addr[64];
 
 static bitnet_status_t static_scratch(void **out)
 {
     int dev = 0;
     BITNET_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return fail(BITNET_ERR_DEVICE, "device index %d out of range", dev);
-    if (!g_scratch_addr[dev]) {
-        void *ptr = nullptr;
+    void *ptr = g_scratch_addr[dev].load(std::memory_order_acquire);
+    if (!ptr) {
         const cudaError_t err = cudaGetSymbolAddress(&ptr, g_static_scratch);
         if (err != cudaSuccess || !ptr) return check_cuda(err == cudaSuccess ? cudaErrorInvalidSymbol : err, "cudaGetSymbolAddress(static scratch)");
-        g_scratch_addr[dev] = ptr;
+        g_scratch_addr[dev].store(ptr, std::memory_order_release);
     }
-    *out = g_scratch_addr[dev];
+    *out = ptr;
     return BITNET_OK;
 }
 

@@ -32,6 +32,7 @@
 // (transformer_layers.rs:119-202) computes for a [B*S, K] input.
 #include <cuda.h>
 #include <cstdlib>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -206,22 +207,6 @@ __global__ void __launch_bounds__(THREADS, THREADS == 128 ? 8 : 4) quantize_rows
         if (a_scale_out) a_scale_out[m] = dequant_scale(absmax);
     }
 }
-
-#ifdef BITNET_PHASE_TIMERS
-#ifndef PF_TS_CTA
-#define PF_TS_CTA 0
-#endif
-__device__ unsigned long long g_pf_ts[16][128];   // [role/point][iteration] of CTA 0
-#define PF_TS(point, it)                                                         \
-    do {                                                                         \
-        if (blockIdx.x == PF_TS_CTA && (it) < 128) {                                  \
-            g_pf_ts[point][it] = (unsigned long long)clock64();                                           \
-        }                                                                        \
-    } while (0)
-extern "C" int bitnet_debug_read_pf(unsigned long long *host) { return (int)cudaMemcpyFromSymbol(host, g_pf_ts, sizeof(g_pf_ts)); }
-#else
-#define PF_TS(point, it) do { } while (0)
-#endif
 
 // ---- PTX wrappers -------------------------------------------------------------------------------
 
@@ -481,7 +466,6 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const unsigned tmem_base = s_tmem_base;
-    if (tid == 0) PF_TS(15, 0);
 
     const long long units = (long long)p.m_tiles * p.n_tiles * p.k_tiles;
     const int whole_k = p.whole_tiles ? p.k_tiles : 0;
@@ -532,9 +516,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 const int cnt = n_slices - pp * PF_PAIR < PF_PAIR ? n_slices - pp * PF_PAIR : PF_PAIR;
                 // the pair that used these stages PF_RING pairs ago has been consumed; its packed
                 // weights (PF_WRING pairs behind the ones loaded below) as well
-                PF_TS(0, pp);
                 if (!pf_mbar_wait(&s_done[pp % PF_RING], ((unsigned)(pp / PF_RING) & 1u) ^ 1u, false)) break;
-                PF_TS(1, pp);
                 pf_mbar_expect_tx(&s_full_x[pp % PF_RING], (unsigned)cnt * (unsigned)(p.bt * PF_BK));
                 for (int h = 0; h < cnt; ++h) {
                     pf_tma_load_2d(stage_x((pp * PF_PAIR + h) % PF_XSTAGES), &map_x, cx.kt * PF_BK, cx.m_tile * p.bt,
@@ -565,7 +547,6 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                         // (the expanders wait for the pair's activations before they report, so one wait covers both)
                         if (!pf_mbar_wait(&s_full_a[pp % PF_ASLOTS], (unsigned)(pp / PF_ASLOTS) & 1u, false)) { ok = false; break; }
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                        PF_TS(4, pp);
                     }
                     const unsigned tmem_a = tmem_base + (unsigned)(PF_TMEM_A0 + ((pp % PF_ASLOTS) * PF_PAIR + h) * PF_A_COLS);
                     const unsigned long long b_desc = pf_smem_desc(pf_smem_u32(stage_x(s)));
@@ -574,7 +555,6 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                         pf_mma_i8_ts(tmem_d, tmem_a + 8u * ks, b_desc + 2ull * ks, idesc, (kt != sg.kb || ks != 0) ? 1u : 0u);
                     if (h == PF_PAIR - 1 || it == n_slices - 1) {
                         pf_commit(&s_done[pp % PF_RING]);   // TMA stages and the tensor-memory slot of the pair are free
-                        PF_TS(5, pp);
                     }
                 }
                 if (ok) pf_commit(&s_acc_full[buf]);
@@ -618,7 +598,6 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 if (!pf_warp_wait(&s_done[pd % PF_RING], (unsigned)(pd / PF_RING) & 1u)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             }
-            if (row == 0) PF_TS(2, pp);
             const unsigned ta = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(PF_TMEM_A0 + slot * PF_PAIR * PF_A_COLS);
             pf_tmem_st32(ta, r[0]);
             if (pp * PF_PAIR + 1 < n_slices) pf_tmem_st32(ta + PF_A_COLS, r[1]);
@@ -627,7 +606,6 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             // report the pair only when its activations have landed too: the MMA thread then needs one wait
             if (!pf_warp_wait(&s_full_x[pp % PF_RING], (unsigned)(pp / PF_RING) & 1u)) { ok = false; break; }
             if (lane == 0) pf_mbar_arrive(&s_full_a[slot]);
-            if (row == 0) PF_TS(3, pp);
         }
     } else {
         // ===================== epilogue (4 warps; a thread owns one feature row of the accumulator) =====================
@@ -729,7 +707,6 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             }
             ok = pf_epi_all(pf_warp_wait(&s_acc_full[buf], acc_ph));   // the four warps go on, or give up, together
             if (!ok) break;
-            if (epi_leader) PF_TS(6, sc - 1);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)buf * PF_BT;
 
@@ -832,7 +809,6 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) pf_mbar_arrive(&s_acc_empty[buf]);
-            if (epi_leader) PF_TS(7, sc - 1);
         }
         if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // shared memory outlives the stores
     }
@@ -840,7 +816,6 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     // everyone meets here, also after a wait that gave up, so that tensor memory is always freed
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (tid == 0) PF_TS(15, 1);
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
@@ -1016,12 +991,16 @@ bitnet_status_t launch_prefill(const ForwardArgs &a, void *workspace, size_t wor
     else
         map_y = map_w;   // unused by the kernel
 
-    static bool attr_set[64] = {false};
-    int dev = 0;
-    BITNET_CUDA(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-        BITNET_CUDA(cudaFuncSetAttribute(prefill_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM));
-        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    {   // once per device, under a lock: host threads launch concurrently (one per stream)
+        static std::mutex mu;
+        static bool attr_set[64] = {false};
+        int dev = 0;
+        BITNET_CUDA(cudaGetDevice(&dev));
+        std::lock_guard<std::mutex> lock(mu);
+        if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+            BITNET_CUDA(cudaFuncSetAttribute(prefill_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM));
+            if (dev >= 0 && dev < 64) attr_set[dev] = true;
+        }
     }
     const int grid = (int)plan.grid;
     // programmatic dependent launch: the GEMM's prologue and weight fetch overlap the quantiser's tail

@@ -20,11 +20,12 @@ def _stream(stream=None) -> int:
     return (stream or torch.cuda.current_stream()).cuda_stream
 
 
-def _workspace(nbytes: int, device: torch.device) -> torch.Tensor | None:
-    """A per-(device, stream) scratch buffer, grown on demand and 256-byte aligned."""
+def _workspace(nbytes: int, device: torch.device, stream=None) -> torch.Tensor | None:
+    """A scratch buffer per (device, stream the kernels are enqueued on), grown on demand and
+    256-byte aligned: calls on different streams may overlap on the GPU and must not share one."""
     if nbytes == 0:
         return None
-    key = (device.index or 0, torch.cuda.current_stream(device).cuda_stream)
+    key = (device.index or 0, _stream(stream))
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
         ws = torch.empty(nbytes + 256, dtype=torch.uint8, device=device)
@@ -87,7 +88,7 @@ def bitlinear_forward(wp: torch.Tensor, w_scale: float, x: torch.Tensor, out_fea
     opts = make_opts(path, pdl, dbg.get("q"), dbg.get("a_scale"), dbg.get("acc"), ldy, stages, y_peers, throughput)
     need = C.c_size_t()
     check(L.load().bitnet_bitlinear_workspace_size(M, K, N, opts.path, C.byref(need)))
-    ws = _workspace(need.value, x.device)
+    ws = _workspace(need.value, x.device, stream)
     check(L.load().bitnet_bitlinear_forward(wp.data_ptr(), w_scale, x.data_ptr(), y.data_ptr(), M, K, N, C.byref(opts),
                                             _aligned_ptr(ws), need.value, _stream(stream)))
     return (y, dbg) if debug else y
@@ -131,7 +132,7 @@ def ffn_forward(w_gate, s_gate, w_up, s_up, w_down, s_down, x: torch.Tensor, ffn
     opts = make_opts(path, pdl, stages=stages, throughput=throughput)
     need = C.c_size_t()
     check(L.load().bitnet_ffn_workspace_size(M, hidden, ffn, opts.path, C.byref(need)))
-    ws = _workspace(need.value, x.device)
+    ws = _workspace(need.value, x.device, stream)
     check(L.load().bitnet_ffn_forward(w_gate.data_ptr(), s_gate, w_up.data_ptr(), s_up, w_down.data_ptr(), s_down,
                                       x.data_ptr(), h.data_ptr(), y.data_ptr(), M, hidden, ffn, C.byref(opts),
                                       _aligned_ptr(ws), need.value, _stream(stream)))

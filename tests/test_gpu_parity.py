@@ -104,6 +104,25 @@ def test_decode_every_ring_depth(stages, M, K, N):
     assert ops.device_error_flags() == 0
 
 
+@pytest.mark.parametrize("M,K,N", [(1, 7168, 16384), (8, 6912, 12000), (8, 7168, 16384), (3, 8128, 16384), (5, 7168, 14336),
+                                   (1, 6912, 16000)])
+def test_decode_ragged_k_slices_with_the_ring_over_the_staging_area(M, K, N):
+    # Many blocks per CTA and a K that leaves some warps fewer chunks than their loop covers: the
+    # plans that keep activations in registers let the weight ring grow over the staging area, and
+    # the chunks past a warp's slice must still read zeros as weights.  The scratch buffer is filled
+    # with 0xFF first, and a call of another shape runs before, so that stale bytes would show.
+    wp, ws, x = case(400 + M + K // 64, M, K, N)
+    ref = oracle.bitlinear_forward(wp, ws, x, N)
+    dwp, dx = dev(wp), dev(x)
+    ops.bitlinear_forward(dev(oracle.gen_ternary_packed(5, 5, 3000 * 1024)), 0.1, torch.full((16, 1024), 127.0, device="cuda"), 3000)
+    for ws_buf in ops._workspaces.values():
+        ws_buf.fill_(0xFF)
+    for _ in range(2):
+        y, dbg = ops.bitlinear_forward(dwp, ws, dx, N, debug=True, path="decode")
+        assert_parity(dbg, y, ref, M, N)
+    assert ops.device_error_flags() == 0
+
+
 def test_decode_with_programmatic_dependent_launch_chain():
     # y1 = L1(x); y2 = L2(y1): the second launch may start before the first ends and must still see y1
     M, K, N = 8, 2560, 2560

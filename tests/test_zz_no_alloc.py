@@ -4,8 +4,12 @@ It serves callers that cannot allocate device memory or pass a workspace (a fixe
 budget, a host that forbids allocation calls at that moment): its scratch is an array built
 into the library.  The test calls it through the C ABI twice in a row with different shapes,
 so that the second call meets the first call's leftovers in the shared array, and compares
-each output with bitnet_bitlinear_forward on the same inputs (bit for bit, which is inside
-the 1e-5 relative tolerance the other parity tests use).  This file sorts last on purpose."""
+each output with bitnet_bitlinear_forward on the same inputs and with the CPU oracle (bit for bit,
+which is inside the 1e-5 relative tolerance the other parity tests use).  The shapes include
+layers wide and ragged enough (many 16-row blocks per CTA, a K that does not divide evenly over
+the warps) to reach the kernel plans that keep activations in registers and let the weight ring
+grow over the staging area, where stale bytes of the shared array would show if anything read
+them.  This file sorts last on purpose."""
 import ctypes as C
 
 import numpy as np
@@ -22,9 +26,12 @@ pytestmark = pytest.mark.gpu
 def test_static_scratch_forward_matches_regular_entry_point_twice():
     lib = L.load()
     stream = torch.cuda.current_stream().cuda_stream
-    for seed, (M, K, N) in enumerate([(8, 6912, 2560), (3, 2560, 700), (1, 2560, 6912), (16, 1024, 144)]):
-        wp = torch.from_numpy(oracle.gen_ternary_packed(40 + seed, 1, N * K)).cuda()
-        x = torch.from_numpy(oracle.gen_activations(40 + seed, 2, (M, K))).cuda()
+    shapes = [(8, 6912, 2560), (3, 2560, 700), (1, 2560, 6912), (16, 1024, 144),
+              (8, 7168, 16384), (1, 7168, 16384), (3, 8128, 16384), (8, 6912, 14400), (2, 64, 32)]
+    for seed, (M, K, N) in enumerate(shapes):
+        wp_h = oracle.gen_ternary_packed(40 + seed, 1, N * K)
+        x_h = oracle.gen_activations(40 + seed, 2, (M, K))
+        wp, x = torch.from_numpy(wp_h).cuda(), torch.from_numpy(x_h).cuda()
         ws = oracle.gen_weight_scale(40 + seed, 1, K)
         y_static = torch.full((M, N), float("nan"), device="cuda")
         cuda.check(lib.bitnet_bitlinear_forward_static(wp.data_ptr(), ws, x.data_ptr(), y_static.data_ptr(), M, K, N, stream))
@@ -32,6 +39,9 @@ def test_static_scratch_forward_matches_regular_entry_point_twice():
         torch.cuda.synchronize()
         np.testing.assert_allclose(y_static.cpu().numpy(), y_regular.cpu().numpy(), rtol=1e-5, atol=0)
         assert torch.equal(y_static, y_regular)
+        ref = oracle.bitlinear_forward_mt(wp_h, ws, x_h, N, 8)
+        np.testing.assert_allclose(y_static.cpu().numpy(), ref, rtol=1e-5, atol=0)
+        assert np.array_equal(y_static.cpu().numpy(), ref)
     assert ops.device_error_flags() == 0
 
 
