@@ -50,6 +50,10 @@ class PerformanceStats(C.Structure):
                 ("memory_utilization_percent", f32), ("peak_bandwidth_gbps", f32)]
 
 
+class FfnCall(C.Structure):
+    _fields_ = [("gate", vp), ("up", vp), ("down", vp), ("M", sz), ("x_host", vp), ("y_host", vp)]
+
+
 _P = C.POINTER
 SIGNATURES = {
     "bitnet_is_recoverable": (i32, [i32]),
@@ -90,6 +94,11 @@ SIGNATURES = {
     "bitnet_backend_bitlinear_forward_host": (i32, [vp, vp, vp, vp, sz, _P(ForwardOpts), sz]),
     "bitnet_backend_ffn_forward_host": (i32, [vp, vp, vp, vp, vp, vp, sz, _P(ForwardOpts), sz]),
     "bitnet_backend_ffn_forward_host_async": (i32, [vp, vp, vp, vp, vp, vp, sz, _P(ForwardOpts), sz]),
+    "bitnet_backend_pin_host": (i32, [vp, vp, sz]),
+    "bitnet_backend_unpin_host": (i32, [vp, vp]),
+    "bitnet_backend_ffn_plan_create": (i32, [vp, _P(FfnCall), sz, _P(ForwardOpts), sz, _P(vp)]),
+    "bitnet_backend_ffn_plan_run": (i32, [vp]),
+    "bitnet_backend_ffn_plan_destroy": (None, [vp]),
 }
 
 _lib = None

@@ -502,14 +502,17 @@ extern "C" bitnet_status_t bitnet_backend_bitlinear_forward_host(bitnet_backend 
     return BITNET_OK;
 }
 
-extern "C" bitnet_status_t bitnet_backend_ffn_forward_host(bitnet_backend *b, const bitnet_weights *gate,
-                                                           const bitnet_weights *up, const bitnet_weights *down,
-                                                           const float *x_host, float *y_host, size_t M,
-                                                           const bitnet_forward_opts *opts, size_t stream_idx)
+// FFN block on host buffers: x is staged through pinned memory, copied in, the block runs, y is
+// copied out -- all on the chosen stream.  wait = true: the call returns when y_host is complete;
+// false: it returns once everything is queued, and the result reaches y_host when the stream is next
+// joined (deliver_pending).
+static bitnet_status_t ffn_forward_host_common(bitnet_backend *b, const bitnet_weights *gate, const bitnet_weights *up,
+                                               const bitnet_weights *down, const float *x_host, float *y_host, size_t M,
+                                               const bitnet_forward_opts *opts, size_t stream_idx, bool wait, const char *who)
 {
-    if (!b || !gate || !up || !down) return fail(BITNET_ERR_NULL_POINTER, "bitnet_backend_ffn_forward_host: null argument");
+    if (!b || !gate || !up || !down) return fail(BITNET_ERR_NULL_POINTER, "%s: null argument", who);
     if (M == 0) return BITNET_OK;
-    if (!x_host || !y_host) return fail(BITNET_ERR_NULL_POINTER, "bitnet_backend_ffn_forward_host: null buffer");
+    if (!x_host || !y_host) return fail(BITNET_ERR_NULL_POINTER, "%s: null buffer", who);
     const size_t hidden = gate->impl.K, ffn = gate->impl.N;
     if (up->impl.K != hidden || up->impl.N != ffn || down->impl.K != ffn || down->impl.N != hidden)
         return fail(BITNET_ERR_INCOMPATIBLE_SHAPES, "FFN shapes disagree: gate %zux%zu, up %zux%zu, down %zux%zu", ffn, hidden,
@@ -533,54 +536,257 @@ extern "C" bitnet_status_t bitnet_backend_ffn_forward_host(bitnet_backend *b, co
                                   down->impl.packed_dev, down->impl.w_scale, x_dev, h_dev, y_dev, M, hidden, ffn, opts,
                                   ws ? dev + 2 * xb + hb : nullptr, ws, s->stream));
     BITNET_CUDA(cudaMemcpyAsync(pin + xb, y_dev, M * hidden * sizeof(float), cudaMemcpyDeviceToHost, s->stream));
-    const cudaError_t err = cudaStreamSynchronize(s->stream);
-    if (err != cudaSuccess) return fail(BITNET_ERR_STREAM_SYNC, "stream synchronize: %s", cudaGetErrorString(err));
-    memcpy(y_host, pin + xb, M * hidden * sizeof(float));
+    if (wait) {
+        const cudaError_t err = cudaStreamSynchronize(s->stream);
+        if (err != cudaSuccess) return fail(BITNET_ERR_STREAM_SYNC, "stream synchronize: %s", cudaGetErrorString(err));
+        memcpy(y_host, pin + xb, M * hidden * sizeof(float));
+    } else {
+        s->pending_dst = y_host;
+        s->pending_src = pin + xb;
+        s->pending_bytes = M * hidden * sizeof(float);
+    }
     b->impl.record(now_ns() - t0, 3 * (ffn * hidden / 4) + 4 * M * (2 * hidden + 2 * ffn) + 4 * M * (2 * ffn + hidden));
     s->operation_count.fetch_add(1, std::memory_order_relaxed);
     return BITNET_OK;
 }
 
-// Asynchronous form of the call above, the reference's usage model for its stream pool (launches are
-// asynchronous per stream, CudaBackend::synchronize joins them: bitnet-cuda/src/backend.rs:129-178):
-// the copies and launches are queued on the chosen stream and the call returns; y_host is complete after
-// bitnet_backend_synchronize, or after the next host-buffer call on the same stream.  x_host may be
+extern "C" bitnet_status_t bitnet_backend_ffn_forward_host(bitnet_backend *b, const bitnet_weights *gate,
+                                                           const bitnet_weights *up, const bitnet_weights *down,
+                                                           const float *x_host, float *y_host, size_t M,
+                                                           const bitnet_forward_opts *opts, size_t stream_idx)
+{
+    return ffn_forward_host_common(b, gate, up, down, x_host, y_host, M, opts, stream_idx, true, "bitnet_backend_ffn_forward_host");
+}
+
+// Asynchronous form, the reference's usage model for its stream pool (launches are asynchronous per
+// stream, CudaBackend::synchronize joins them: bitnet-cuda/src/backend.rs:129-178): y_host is complete
+// after bitnet_backend_synchronize, or after the next host-buffer call on the same stream.  x_host may be
 // reused at once (it is staged before the call returns).
 extern "C" bitnet_status_t bitnet_backend_ffn_forward_host_async(bitnet_backend *b, const bitnet_weights *gate,
                                                                  const bitnet_weights *up, const bitnet_weights *down,
                                                                  const float *x_host, float *y_host, size_t M,
                                                                  const bitnet_forward_opts *opts, size_t stream_idx)
 {
-    if (!b || !gate || !up || !down) return fail(BITNET_ERR_NULL_POINTER, "bitnet_backend_ffn_forward_host_async: null argument");
-    if (M == 0) return BITNET_OK;
-    if (!x_host || !y_host) return fail(BITNET_ERR_NULL_POINTER, "bitnet_backend_ffn_forward_host_async: null buffer");
-    const size_t hidden = gate->impl.K, ffn = gate->impl.N;
-    if (up->impl.K != hidden || up->impl.N != ffn || down->impl.K != ffn || down->impl.N != hidden)
-        return fail(BITNET_ERR_INCOMPATIBLE_SHAPES, "FFN shapes disagree: gate %zux%zu, up %zux%zu, down %zux%zu", ffn, hidden,
-                    up->impl.N, up->impl.K, down->impl.N, down->impl.K);
-    CudaStream *s = nullptr;
-    BITNET_TRY(b->impl.stream_at(stream_idx, &s));
-    std::lock_guard<std::mutex> lock(s->mu);
+    return ffn_forward_host_common(b, gate, up, down, x_host, y_host, M, opts, stream_idx, false,
+                                   "bitnet_backend_ffn_forward_host_async");
+}
+
+// ---- pinned host memory -------------------------------------------------------------------------------
+
+extern "C" bitnet_status_t bitnet_backend_pin_host(bitnet_backend *b, void *host_ptr, size_t bytes)
+{
+    if (!b) return fail(BITNET_ERR_NULL_POINTER, "bitnet_backend_pin_host: null backend");
+    if (bytes == 0) return BITNET_OK;
+    if (!host_ptr) return fail(BITNET_ERR_NULL_POINTER, "bitnet_backend_pin_host: null buffer");
     BITNET_CUDA(cudaSetDevice(b->impl.device));
-    BITNET_TRY(deliver_pending(*s));
-    const size_t xb = align_up(M * hidden * sizeof(float), 256), hb = align_up(M * ffn * sizeof(float), 256);
-    size_t ws = 0;
-    BITNET_TRY(bitnet_ffn_workspace_size(M, hidden, ffn, opts ? opts->path : BITNET_PATH_AUTO, &ws));
-    BITNET_TRY(b->impl.ensure_staging(*s, 2 * xb, 2 * xb + hb + ws));
-    char *pin = static_cast<char *>(s->pinned), *dev = static_cast<char *>(s->dev);
-    float *x_dev = reinterpret_cast<float *>(dev), *y_dev = reinterpret_cast<float *>(dev + xb);
-    float *h_dev = reinterpret_cast<float *>(dev + 2 * xb);
-    const uint64_t t0 = now_ns();
-    memcpy(pin, x_host, M * hidden * sizeof(float));
-    BITNET_CUDA(cudaMemcpyAsync(x_dev, pin, M * hidden * sizeof(float), cudaMemcpyHostToDevice, s->stream));
-    BITNET_TRY(bitnet_ffn_forward(gate->impl.packed_dev, gate->impl.w_scale, up->impl.packed_dev, up->impl.w_scale,
-                                  down->impl.packed_dev, down->impl.w_scale, x_dev, h_dev, y_dev, M, hidden, ffn, opts,
-                                  ws ? dev + 2 * xb + hb : nullptr, ws, s->stream));
-    BITNET_CUDA(cudaMemcpyAsync(pin + xb, y_dev, M * hidden * sizeof(float), cudaMemcpyDeviceToHost, s->stream));
-    s->pending_dst = y_host;
-    s->pending_src = pin + xb;
-    s->pending_bytes = M * hidden * sizeof(float);
-    b->impl.record(now_ns() - t0, 3 * (ffn * hidden / 4) + 4 * M * (2 * hidden + 2 * ffn) + 4 * M * (2 * ffn + hidden));
-    s->operation_count.fetch_add(1, std::memory_order_relaxed);
+    BITNET_CUDA(cudaHostRegister(host_ptr, bytes, cudaHostRegisterPortable));
     return BITNET_OK;
 }
+
+extern "C" bitnet_status_t bitnet_backend_unpin_host(bitnet_backend *b, void *host_ptr)
+{
+    if (!b) return fail(BITNET_ERR_NULL_POINTER, "bitnet_backend_unpin_host: null backend");
+    if (!host_ptr) return BITNET_OK;
+    BITNET_CUDA(cudaHostUnregister(host_ptr));
+    return BITNET_OK;
+}
+
+// ---- a fixed batch of FFN blocks as one replayable unit -------------------------------------------------
+
+namespace {
+
+bool host_ptr_is_pinned(const void *p)
+{
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return attr.type == cudaMemoryTypeHost;
+}
+
+struct PlanCall {
+    const Weights *gate, *up, *down;
+    size_t M;
+    const float *x_host;
+    float *y_host;
+    bool x_pinned, y_pinned;
+    const float *x_src;   // what the in-graph copy reads: the caller's pinned buffer or this plan's staging
+    float *y_dst;
+    float *x_dev, *h_dev, *y_dev;
+    void *ws;
+    size_t ws_bytes;
+};
+
+}  // namespace
+
+struct bitnet_ffn_plan {
+    bitnet_backend *backend = nullptr;
+    std::vector<PlanCall> calls;
+    void *dev_slab = nullptr;
+    void *pin_slab = nullptr;
+    std::vector<cudaStream_t> lanes;   // lanes[0] is the stream the graph is launched on
+    std::vector<cudaEvent_t> events;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    bitnet_forward_opts opts = {};
+    std::mutex mu;
+    size_t bytes_per_run = 0;
+};
+
+static void plan_release(bitnet_ffn_plan *p)
+{
+    if (!p) return;
+    if (p->backend) cudaSetDevice(p->backend->impl.device);
+    if (!p->lanes.empty()) cudaStreamSynchronize(p->lanes[0]);
+    if (p->exec) cudaGraphExecDestroy(p->exec);
+    if (p->graph) cudaGraphDestroy(p->graph);
+    for (cudaEvent_t e : p->events) cudaEventDestroy(e);
+    for (cudaStream_t s : p->lanes) cudaStreamDestroy(s);
+    if (p->pin_slab) cudaFreeHost(p->pin_slab);
+    if (p->dev_slab && p->backend) p->backend->impl.memory->release(p->dev_slab);
+    delete p;
+}
+
+// Queues every call of the plan on its lane: copy in, FFN block, copy out.  Used once eagerly (which
+// also sets every launch attribute outside the capture) and once under stream capture.
+static bitnet_status_t plan_enqueue(bitnet_ffn_plan *p)
+{
+    const size_t L = p->lanes.size();
+    cudaStream_t origin = p->lanes[0];
+    BITNET_CUDA(cudaEventRecord(p->events[0], origin));
+    for (size_t l = 1; l < L; ++l) BITNET_CUDA(cudaStreamWaitEvent(p->lanes[l], p->events[0], 0));
+    for (size_t i = 0; i < p->calls.size(); ++i) {
+        const PlanCall &c = p->calls[i];
+        cudaStream_t s = p->lanes[i % L];
+        const size_t hidden = c.gate->K, ffn = c.gate->N;
+        BITNET_CUDA(cudaMemcpyAsync(c.x_dev, c.x_src, c.M * hidden * sizeof(float), cudaMemcpyHostToDevice, s));
+        BITNET_TRY(bitnet_ffn_forward(c.gate->packed_dev, c.gate->w_scale, c.up->packed_dev, c.up->w_scale, c.down->packed_dev,
+                                      c.down->w_scale, c.x_dev, c.h_dev, c.y_dev, c.M, hidden, ffn, &p->opts, c.ws, c.ws_bytes, s));
+        BITNET_CUDA(cudaMemcpyAsync(c.y_dst, c.y_dev, c.M * hidden * sizeof(float), cudaMemcpyDeviceToHost, s));
+    }
+    for (size_t l = 1; l < L; ++l) {
+        BITNET_CUDA(cudaEventRecord(p->events[l], p->lanes[l]));
+        BITNET_CUDA(cudaStreamWaitEvent(origin, p->events[l], 0));
+    }
+    return BITNET_OK;
+}
+
+extern "C" bitnet_status_t bitnet_backend_ffn_plan_create(bitnet_backend *b, const bitnet_ffn_call *calls, size_t n_calls,
+                                                          const bitnet_forward_opts *opts, size_t n_lanes,
+                                                          bitnet_ffn_plan **out)
+{
+    if (!b || !out) return fail(BITNET_ERR_NULL_POINTER, "bitnet_backend_ffn_plan_create: null argument");
+    *out = nullptr;
+    if (n_calls == 0 || !calls) return fail(BITNET_ERR_INVALID_CONFIG, "bitnet_backend_ffn_plan_create: no calls");
+    if (opts && (opts->q_out_dev || opts->a_scale_out_dev || opts->acc_out_dev || opts->ldy || opts->n_peers))
+        return fail(BITNET_ERR_INVALID_CONFIG, "an FFN plan takes no device outputs");
+    if (n_lanes == 0) n_lanes = 8;
+    if (n_lanes > n_calls) n_lanes = n_calls;
+    if (n_lanes > 32) n_lanes = 32;
+    BITNET_CUDA(cudaSetDevice(b->impl.device));
+
+    bitnet_ffn_plan *p = new (std::nothrow) bitnet_ffn_plan();
+    if (!p) return fail(BITNET_ERR_MEMORY_ALLOCATION, "out of host memory");
+    p->backend = b;
+    if (opts) p->opts = *opts;
+    // blocks of different lanes share the SMs: small CTAs, launches chained inside a lane
+    if (n_lanes > 1) p->opts.flags |= BITNET_FLAG_THROUGHPUT;
+    p->opts.flags |= BITNET_FLAG_PDL;
+
+    size_t dev_bytes = 0, pin_bytes = 0;
+    bitnet_status_t st = BITNET_OK;
+    p->calls.resize(n_calls);
+    for (size_t i = 0; i < n_calls && st == BITNET_OK; ++i) {
+        const bitnet_ffn_call &in = calls[i];
+        PlanCall &c = p->calls[i];
+        if (!in.gate || !in.up || !in.down || !in.x_host || !in.y_host || in.M == 0) {
+            st = fail(BITNET_ERR_NULL_POINTER, "FFN plan: call %zu has a null member or no tokens", i);
+            break;
+        }
+        c.gate = &in.gate->impl; c.up = &in.up->impl; c.down = &in.down->impl;
+        c.M = in.M; c.x_host = in.x_host; c.y_host = in.y_host;
+        const size_t hidden = c.gate->K, ffn = c.gate->N;
+        if (c.up->K != hidden || c.up->N != ffn || c.down->K != ffn || c.down->N != hidden) {
+            st = fail(BITNET_ERR_INCOMPATIBLE_SHAPES, "FFN plan: shapes of call %zu disagree", i);
+            break;
+        }
+        c.x_pinned = host_ptr_is_pinned(c.x_host);
+        c.y_pinned = host_ptr_is_pinned(c.y_host);
+        const size_t xb = align_up(c.M * hidden * sizeof(float), 256), hb = align_up(c.M * ffn * sizeof(float), 256);
+        st = bitnet_ffn_workspace_size(c.M, hidden, ffn, p->opts.path, &c.ws_bytes);
+        dev_bytes += 2 * xb + hb + align_up(c.ws_bytes, 256);
+        pin_bytes += (c.x_pinned ? 0 : xb) + (c.y_pinned ? 0 : xb);
+        p->bytes_per_run += 3 * (ffn * hidden / 4) + 4 * c.M * (2 * hidden + 2 * ffn) + 4 * c.M * (2 * ffn + hidden);
+    }
+    if (st == BITNET_OK) st = b->impl.memory->allocate(dev_bytes, &p->dev_slab);
+    if (st == BITNET_OK && pin_bytes) st = check_cuda(cudaMallocHost(&p->pin_slab, pin_bytes), "cudaMallocHost");
+    if (st == BITNET_OK) {
+        char *dev = static_cast<char *>(p->dev_slab), *pin = static_cast<char *>(p->pin_slab);
+        for (PlanCall &c : p->calls) {
+            const size_t hidden = c.gate->K, ffn = c.gate->N;
+            const size_t xb = align_up(c.M * hidden * sizeof(float), 256), hb = align_up(c.M * ffn * sizeof(float), 256);
+            c.x_dev = reinterpret_cast<float *>(dev); dev += xb;
+            c.y_dev = reinterpret_cast<float *>(dev); dev += xb;
+            c.h_dev = reinterpret_cast<float *>(dev); dev += hb;
+            c.ws = c.ws_bytes ? dev : nullptr; dev += align_up(c.ws_bytes, 256);
+            if (c.x_pinned) c.x_src = c.x_host; else { c.x_src = reinterpret_cast<float *>(pin); pin += xb; }
+            if (c.y_pinned) c.y_dst = c.y_host; else { c.y_dst = reinterpret_cast<float *>(pin); pin += xb; }
+        }
+        for (size_t l = 0; l < n_lanes && st == BITNET_OK; ++l) {
+            cudaStream_t s = nullptr;
+            cudaEvent_t e = nullptr;
+            st = check_cuda(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking), "cudaStreamCreateWithFlags");
+            if (st == BITNET_OK) p->lanes.push_back(s);
+            if (st == BITNET_OK) st = check_cuda(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "cudaEventCreateWithFlags");
+            if (st == BITNET_OK) p->events.push_back(e);
+        }
+    }
+    // once eagerly (sets launch attributes, checks every call), then the same thing as a graph
+    if (st == BITNET_OK) st = plan_enqueue(p);
+    if (st == BITNET_OK) st = check_cuda(cudaStreamSynchronize(p->lanes[0]), "FFN plan: first run");
+    // with programmatic dependent launch inside the lanes first; if this driver cannot capture or
+    // instantiate that, with ordinary dependencies
+    for (int attempt = 0; st == BITNET_OK && attempt < 2 && !p->exec; ++attempt) {
+        if (attempt == 1) p->opts.flags &= ~BITNET_FLAG_PDL;
+        bitnet_status_t cs = check_cuda(cudaStreamBeginCapture(p->lanes[0], cudaStreamCaptureModeThreadLocal), "cudaStreamBeginCapture");
+        if (cs == BITNET_OK) {
+            const bitnet_status_t q = plan_enqueue(p);
+            const cudaError_t err = cudaStreamEndCapture(p->lanes[0], &p->graph);   // always end the capture
+            cs = q != BITNET_OK ? q : check_cuda(err, "cudaStreamEndCapture");
+        }
+        if (cs == BITNET_OK) cs = check_cuda(cudaGraphInstantiate(&p->exec, p->graph, 0), "cudaGraphInstantiate");
+        if (cs != BITNET_OK) {
+            cudaGetLastError();
+            if (p->exec) { cudaGraphExecDestroy(p->exec); p->exec = nullptr; }
+            if (p->graph) { cudaGraphDestroy(p->graph); p->graph = nullptr; }
+            if (attempt == 1) st = cs;
+        }
+    }
+    if (st != BITNET_OK) {
+        cudaGetLastError();
+        plan_release(p);
+        return st;
+    }
+    *out = p;
+    return BITNET_OK;
+}
+
+extern "C" bitnet_status_t bitnet_backend_ffn_plan_run(bitnet_ffn_plan *p)
+{
+    if (!p) return fail(BITNET_ERR_NULL_POINTER, "bitnet_backend_ffn_plan_run: null plan");
+    std::lock_guard<std::mutex> lock(p->mu);
+    BITNET_CUDA(cudaSetDevice(p->backend->impl.device));
+    const uint64_t t0 = now_ns();
+    for (const PlanCall &c : p->calls)
+        if (!c.x_pinned) memcpy(const_cast<float *>(c.x_src), c.x_host, c.M * c.gate->K * sizeof(float));
+    BITNET_CUDA(cudaGraphLaunch(p->exec, p->lanes[0]));
+    const cudaError_t err = cudaStreamSynchronize(p->lanes[0]);
+    if (err != cudaSuccess) return fail(BITNET_ERR_STREAM_SYNC, "stream synchronize: %s", cudaGetErrorString(err));
+    for (const PlanCall &c : p->calls)
+        if (!c.y_pinned) memcpy(c.y_host, c.y_dst, c.M * c.gate->K * sizeof(float));
+    p->backend->impl.record(now_ns() - t0, p->bytes_per_run);
+    return BITNET_OK;
+}
+
+extern "C" void bitnet_backend_ffn_plan_destroy(bitnet_ffn_plan *p) { plan_release(p); }

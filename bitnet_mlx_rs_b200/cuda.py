@@ -283,6 +283,17 @@ class CudaBackend:
                                                        x.shape[0], C.byref(opts) if opts else None, stream_idx))
         return y
 
+    def pin_host(self, array) -> None:
+        """Page-locks a numpy array's memory so that host-buffer calls copy from/to it directly."""
+        check(L.load().bitnet_backend_pin_host(self._h, array.ctypes.data, array.nbytes))
+
+    def unpin_host(self, array) -> None:
+        check(L.load().bitnet_backend_unpin_host(self._h, array.ctypes.data))
+
+    def ffn_plan(self, calls, opts: L.ForwardOpts | None = None, n_lanes: int = 0) -> "FfnPlan":
+        """`calls`: (gate, up, down, x_host, y_host) tuples; see FfnPlan."""
+        return FfnPlan(self, calls, opts, n_lanes)
+
     def ffn_forward_host_async(self, gate: DeviceWeights, up: DeviceWeights, down: DeviceWeights, x_host, out,
                                opts: L.ForwardOpts | None = None, stream_idx: int = 0) -> None:
         """Queues the FFN block on stream `stream_idx` and returns; `out` (a C-contiguous float32 numpy
@@ -296,6 +307,45 @@ class CudaBackend:
             raise IncompatibleShapes(f"out must be a C-contiguous float32 array [{x.shape[0]},{down.out_features}]")
         check(L.load().bitnet_backend_ffn_forward_host_async(self._h, gate._h, up._h, down._h, x.ctypes.data, out.ctypes.data,
                                                              x.shape[0], C.byref(opts) if opts else None, stream_idx))
+
+
+class FfnPlan:
+    """A fixed batch of independent FFN blocks bound to host buffers, replayed as one unit
+    (bitnet_backend_ffn_plan_*): the recorded form of a loop of asynchronous launches over the stream
+    pool followed by CudaBackend::synchronize (backend.rs:129-178)."""
+
+    def __init__(self, backend: "CudaBackend", calls, opts: L.ForwardOpts | None = None, n_lanes: int = 0):
+        import numpy as np
+        self._b, self._h = backend, None
+        self._keep = []
+        arr = (L.FfnCall * len(calls))()
+        for i, (gate, up, down, x, y) in enumerate(calls):
+            for name, a in (("x", x), ("y", y)):
+                if a.dtype != np.float32 or not a.flags["C_CONTIGUOUS"] or a.ndim != 2 or a.shape[1] != gate.in_features:
+                    raise IncompatibleShapes(f"call {i}: {name} must be a C-contiguous float32 array [M,{gate.in_features}]")
+            if x.shape != y.shape:
+                raise IncompatibleShapes(f"call {i}: x {x.shape} and y {y.shape} differ")
+            arr[i] = L.FfnCall(gate._h, up._h, down._h, x.shape[0], x.ctypes.data, y.ctypes.data)
+            self._keep.append((gate, up, down, x, y))
+        out = C.c_void_p()
+        check(L.load().bitnet_backend_ffn_plan_create(backend._h, arr, len(calls), C.byref(opts) if opts else None, n_lanes,
+                                                      C.byref(out)))
+        self._h = out.value
+
+    def run(self) -> None:
+        check(L.load().bitnet_backend_ffn_plan_run(self._h))
+
+    def close(self) -> None:
+        if self._h:
+            L.load().bitnet_backend_ffn_plan_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            if self._b._h:
+                self.close()
+        except Exception:
+            pass
 
 
 def device_count() -> int:          # lib.rs:56-64

@@ -307,6 +307,36 @@ bitnet_status_t bitnet_backend_ffn_forward_host_async(bitnet_backend *b, const b
                                                       const float *x_host, float *y_host, size_t M,
                                                       const bitnet_forward_opts *opts, size_t stream_idx);
 
+/* Page-locks / releases a host buffer of the caller (cudaHostRegister), so that the copies of the
+ * host-buffer calls read and write it directly.  The reference's memory manager has no pinned
+ * allocations (memory.rs:130-160 copies from pageable slices); this is an addition. */
+bitnet_status_t bitnet_backend_pin_host(bitnet_backend *b, void *host_ptr, size_t bytes);
+bitnet_status_t bitnet_backend_unpin_host(bitnet_backend *b, void *host_ptr);
+
+/* A fixed batch of independent FFN blocks as one replayable unit: what a caller of the reference
+ * writes as a loop of asynchronous launches spread over the stream pool followed by
+ * CudaBackend::synchronize (bitnet-cuda/src/backend.rs:129-178), with the loop recorded once.
+ * Creation binds, per call, the weights, the token count and the HOST buffers x [M,hidden] and
+ * y [M,hidden]; it allocates the device buffers from the backend's pool, runs the batch once, and
+ * records it as a CUDA graph: per call host->device copy of x, the block, device->host copy of y,
+ * the calls dealt round-robin to n_lanes streams (0 = 8) so that independent blocks overlap on the
+ * device.  Host buffers that are page-locked (bitnet_backend_pin_host, cudaMallocHost, ...) are
+ * copied from and to directly; others are staged through pinned memory inside the run.
+ * bitnet_backend_ffn_plan_run replays the batch and returns when every y_host is complete; the
+ * caller refreshes the bound x_host buffers between runs.  One run at a time per plan. */
+typedef struct bitnet_ffn_plan bitnet_ffn_plan;
+typedef struct bitnet_ffn_call {
+    const bitnet_weights *gate, *up, *down;
+    size_t M;
+    const float *x_host;
+    float *y_host;
+} bitnet_ffn_call;
+bitnet_status_t bitnet_backend_ffn_plan_create(bitnet_backend *b, const bitnet_ffn_call *calls, size_t n_calls,
+                                               const bitnet_forward_opts *opts, size_t n_lanes,
+                                               bitnet_ffn_plan **out);
+bitnet_status_t bitnet_backend_ffn_plan_run(bitnet_ffn_plan *plan);
+void bitnet_backend_ffn_plan_destroy(bitnet_ffn_plan *plan);
+
 #ifdef __cplusplus
 }
 #endif

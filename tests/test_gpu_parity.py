@@ -412,6 +412,41 @@ def test_backend_host_ffn_async_streams():
         b.close()
 
 
+@pytest.mark.parametrize("n_lanes", [1, 3])
+def test_backend_ffn_plan_replays_a_batch(n_lanes):
+    # a fixed batch of FFN blocks bound to host buffers (some page-locked, some not), replayed twice
+    # with refreshed inputs; every result equals the oracle's
+    hidden, ffn = 256, 640
+    b = cuda.CudaBackend(cuda.CudaBackendConfig(num_streams=2))
+    try:
+        layers = []
+        for l in range(3):
+            packs = [oracle.gen_ternary_packed(17, 10 * l + i, ffn * hidden) for i in range(3)]
+            scales = [oracle.gen_weight_scale(17, 10 * l + i, k) for i, k in ((0, hidden), (1, hidden), (2, ffn))]
+            layers.append((packs, scales, (b.upload_packed(packs[0], ffn, hidden, scales[0]), b.upload_packed(packs[1], ffn, hidden, scales[1]),
+                                           b.upload_packed(packs[2], hidden, ffn, scales[2]))))
+        Ms = [1, 4, 8, 2, 1, 16, 5]
+        xs = [np.zeros((M, hidden), dtype=np.float32) for M in Ms]
+        ys = [np.full((M, hidden), np.nan, dtype=np.float32) for M in Ms]
+        for i in (0, 2, 5):
+            b.pin_host(xs[i]); b.pin_host(ys[i])
+        plan = b.ffn_plan([(*layers[i % 3][2], xs[i], ys[i]) for i in range(len(Ms))], n_lanes=n_lanes)
+        for rnd in range(2):
+            for i, M in enumerate(Ms):
+                xs[i][...] = oracle.gen_activations(17, 100 + 10 * rnd + i, (M, hidden))
+            plan.run()
+            for i in range(len(Ms)):
+                packs, scales, _ = layers[i % 3]
+                ref, _ = oracle.ffn_forward(packs[0], scales[0], packs[1], scales[1], packs[2], scales[2], xs[i], ffn)
+                assert np.array_equal(ys[i], ref), (rnd, i)
+        plan.close()
+        for i in (0, 2, 5):
+            b.unpin_host(xs[i]); b.unpin_host(ys[i])
+        assert ops.device_error_flags() == 0
+    finally:
+        b.close()
+
+
 @pytest.mark.parametrize("M,K,N", [(1, 2560, 6912), (4, 6912, 2560), (8, 2560, 6912), (3, 320, 129), (16, 1024, 144), (1, 8192, 3584)])
 def test_decode_throughput_flag_same_bits(M, K, N):
     # the small-CTA plan (four consumer warps) gives the same bits as the default plan
