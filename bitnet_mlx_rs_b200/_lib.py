@@ -50,6 +50,35 @@ class PerformanceStats(C.Structure):
                 ("memory_utilization_percent", f32), ("peak_bandwidth_gbps", f32)]
 
 
+class RowGlue(C.Structure):
+    _fields_ = [("residual_dev", vp), ("sum_out_dev", vp), ("norm_weight_dev", vp), ("norm_bias_dev", vp),
+                ("norm_eps", f32), ("normed_out_dev", vp)]
+
+
+class Stack(C.Structure):
+    _fields_ = [("n_members", i32), ("rows", sz * 3), ("scales", f32 * 3)]
+
+
+class SamplingConfig(C.Structure):
+    _fields_ = [("temperature", f32), ("top_k", u32), ("top_p", f32), ("seed", C.c_uint64), ("deterministic", i32)]
+
+
+class DecoderConfig(C.Structure):
+    _fields_ = [("vocab_size", sz), ("hidden_size", sz), ("num_layers", sz), ("num_heads", sz), ("num_kv_heads", sz),
+                ("head_dim", sz), ("ffn_size", sz), ("max_seq_len", sz), ("max_batch", sz), ("norm_eps", f32)]
+
+
+class DecoderLayer(C.Structure):
+    _fields_ = [("q_packed", vp), ("k_packed", vp), ("v_packed", vp), ("o_packed", vp),
+                ("gate_packed", vp), ("up_packed", vp), ("down_packed", vp),
+                ("q_scale", f32), ("k_scale", f32), ("v_scale", f32), ("o_scale", f32),
+                ("gate_scale", f32), ("up_scale", f32), ("down_scale", f32),
+                ("input_norm_weight", vp), ("input_norm_bias", vp), ("post_norm_weight", vp), ("post_norm_bias", vp)]
+
+
+DECODER_LOGITS, DECODER_HIDDEN, DECODER_POSITIONS, DECODER_KEY_CACHE, DECODER_VALUE_CACHE = 0, 1, 2, 3, 4
+
+
 class FfnCall(C.Structure):
     _fields_ = [("gate", vp), ("up", vp), ("down", vp), ("M", sz), ("x_host", vp), ("y_host", vp)]
 
@@ -94,6 +123,29 @@ SIGNATURES = {
     "bitnet_backend_bitlinear_forward_host": (i32, [vp, vp, vp, vp, sz, _P(ForwardOpts), sz]),
     "bitnet_backend_ffn_forward_host": (i32, [vp, vp, vp, vp, vp, vp, sz, _P(ForwardOpts), sz]),
     "bitnet_backend_ffn_forward_host_async": (i32, [vp, vp, vp, vp, vp, vp, sz, _P(ForwardOpts), sz]),
+    "bitnet_bitlinear_forward_fused": (i32, [vp, _P(Stack), vp, _P(RowGlue), vp, sz, sz, _P(ForwardOpts), vp, sz, vp]),
+    "bitnet_bitlinear_fused_workspace_size": (i32, [sz, sz, sz, i32, _P(sz)]),
+    "bitnet_ffn_forward_fused": (i32, [vp, f32, vp, f32, vp, f32, vp, _P(RowGlue), vp, vp, sz, sz, sz, _P(ForwardOpts), vp, sz, vp]),
+    "bitnet_ffn_fused_workspace_size": (i32, [sz, sz, sz, i32, _P(sz)]),
+    "bitnet_row_glue_forward": (i32, [vp, sz, sz, _P(RowGlue), vp]),
+    "bitnet_attention_decode": (i32, [vp, sz, sz, sz, vp, vp, vp, vp, sz, sz, sz, sz, sz, i32, vp, sz, vp]),
+    "bitnet_attention_scratch_size": (i32, [sz, sz, sz, sz, i32, _P(sz)]),
+    "bitnet_attention_splits": (i32, [sz, sz, sz]),
+    "bitnet_sampling_config_default": (None, [_P(SamplingConfig)]),
+    "bitnet_sample_tokens": (i32, [vp, sz, sz, _P(SamplingConfig), vp, vp, vp]),
+    "bitnet_seed_sampler": (i32, [vp, sz, C.c_uint64, vp]),
+    "bitnet_decoder_config_default": (None, [_P(DecoderConfig)]),
+    "bitnet_decoder_create": (i32, [vp, _P(DecoderConfig), _P(vp)]),
+    "bitnet_decoder_destroy": (None, [vp]),
+    "bitnet_decoder_load_embedding": (i32, [vp, vp]),
+    "bitnet_decoder_load_layer": (i32, [vp, sz, _P(DecoderLayer)]),
+    "bitnet_decoder_load_lm_head": (i32, [vp, vp, f32]),
+    "bitnet_decoder_reset": (i32, [vp]),
+    "bitnet_decoder_set_graphs": (i32, [vp, i32]),
+    "bitnet_decoder_feed": (i32, [vp, vp, sz, sz]),
+    "bitnet_decoder_decode": (i32, [vp, vp, sz, sz, _P(SamplingConfig), i32, vp, _P(sz)]),
+    "bitnet_decoder_generate": (i32, [vp, vp, sz, sz, sz, _P(SamplingConfig), i32, vp, _P(sz)]),
+    "bitnet_decoder_read": (i32, [vp, i32, vp, sz]),
     "bitnet_backend_pin_host": (i32, [vp, vp, sz]),
     "bitnet_backend_unpin_host": (i32, [vp, vp]),
     "bitnet_backend_ffn_plan_create": (i32, [vp, _P(FfnCall), sz, _P(ForwardOpts), sz, _P(vp)]),

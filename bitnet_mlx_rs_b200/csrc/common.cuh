@@ -29,6 +29,19 @@ inline cudaStream_t as_stream(bitnet_stream_t s) { return reinterpret_cast<cudaS
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// Row-wise glue of a decoder layer that the activation quantiser applies on its way: the residual
+// add in front of a sub-layer, and the sub-layer normalisation (SubLNNormalization::forward,
+// bitnet-inference/src/engine/transformer_layers.rs:356-386: (x - mean) / sqrt(var + eps) * weight + bias,
+// var with the n - 1 divisor of candle's var_keepdim).  All members optional.
+struct RowPre {
+    const float *residual;   // [M,K]: the row that is normalised and quantised is x + residual
+    float *sum_out;          // [M,K]: receives x + residual (may alias x)
+    const float *norm_w;     // [K]: SubLN weight; null = no normalisation
+    const float *norm_b;     // [K]: SubLN bias
+    float eps;
+    float *normed_out;       // [M,K]: receives the normalised fp32 row (parity tests)
+};
+
 // Launchers of the kernel families (defined next to their kernels).
 struct ForwardArgs {
     const uint8_t *wp;
@@ -54,6 +67,13 @@ struct ForwardArgs {
     void *image_ws;
     size_t image_ws_bytes;
     bool force_split;    // quantise through the image even for a single token
+    bool image_ready;    // image_ws already holds this launch's image (an earlier launch of the same K and plan wrote it)
+    const RowPre *pre;   // decode path: residual add / normalisation done by the quantiser launch (needs image_ws)
+    // several BitLinears that share x, their weights stacked along N: rows [0, seg_end[0]) use w_scale,
+    // [seg_end[0], seg_end[1]) seg_scale[0], the rest seg_scale[1]; n_seg = 0 for a single matrix
+    int n_seg;
+    size_t seg_end[2];
+    float seg_scale[2];
     // output-feature split over several GPUs: the epilogue stores to every one of these (decode kernel)
     float *y_peers[8];
     int n_peers;
@@ -79,6 +99,24 @@ bitnet_status_t launch_prefill(const ForwardArgs &a, void *workspace, size_t wor
 bitnet_status_t prefill_take_error_flags(unsigned *flags);
 
 int device_sm_count();
+
+// Stand-alone row glue (residual add and/or SubLN) for the paths whose quantiser does not take it:
+// writes x + residual to pre.sum_out and the normalised row to pre.normed_out.  K % 16 == 0, K <= 16384.
+bitnet_status_t launch_row_pre(const float *x, size_t M, size_t K, const RowPre &pre, uint32_t flags, cudaStream_t stream);
+
+// Decode-step kernels around the projections (decoder_kernels.cu).
+bitnet_status_t launch_embed_gather(const int *ids, const float *table, float *x, size_t M, size_t hidden, size_t vocab,
+                                    cudaStream_t stream);
+size_t attention_scratch_bytes(size_t B, size_t n_heads, size_t n_kv, size_t head_dim, size_t n_splits);
+int attention_splits(size_t B, size_t n_kv, size_t max_context);
+bitnet_status_t launch_attention_decode(const float *qkv, size_t ldq, size_t k_off, size_t v_off, void *kcache, void *vcache,
+                                        const int *pos, float *out, size_t B, size_t n_heads, size_t n_kv, size_t head_dim,
+                                        size_t max_seq, int n_splits, void *scratch, size_t scratch_bytes, uint32_t flags,
+                                        cudaStream_t stream);
+bitnet_status_t launch_sample(const float *logits, size_t B, size_t vocab, const bitnet_sampling_config &cfg,
+                              unsigned long long *rng, int *next, int *ids_feed, int *pos, int *history, int *step_counter,
+                              int eos_id, int *finished, uint32_t flags, cudaStream_t stream);
+bitnet_status_t launch_seed_rng(unsigned long long *rng, size_t B, unsigned long long seed, cudaStream_t stream);
 
 #ifdef __CUDACC__
 
@@ -119,6 +157,90 @@ __device__ __forceinline__ unsigned abs_key(float x)
 {
     const unsigned b = __float_as_uint(x) & 0x7fffffffu;
     return b > 0x7f800000u ? 0u : b;
+}
+
+// The decoder-layer glue of RowPre on a row held in registers by a 512-thread CTA (thread t owns the
+// 16-wide groups t and t + 512 of row m, n_groups = K / 16 <= 1024): residual add, then SubLN.
+// Sums run in a fixed order (lane tree, then the sixteen warps in turn), mean first, then the centred
+// sum of squares with the n - 1 divisor.  Every thread of the CTA must call it.
+__device__ __forceinline__ void apply_row_pre(float4 (&f)[2][4], const RowPre &pre, int m, int K, int tid, float (&s_fsum)[2][16])
+{
+    const int n_groups = K / 16;
+    if (pre.residual) {   // the hidden state takes the sub-layer's output before it is normalised
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int G = tid + u * 512;
+            if (G < n_groups) {
+                const float4 *rsrc = reinterpret_cast<const float4 *>(pre.residual + (size_t)m * K + (size_t)G * 16);
+#pragma unroll
+                for (int v = 0; v < 4; ++v) {
+                    const float4 r4 = __ldg(rsrc + v);
+                    f[u][v].x = __fadd_rn(f[u][v].x, r4.x); f[u][v].y = __fadd_rn(f[u][v].y, r4.y);
+                    f[u][v].z = __fadd_rn(f[u][v].z, r4.z); f[u][v].w = __fadd_rn(f[u][v].w, r4.w);
+                }
+                if (pre.sum_out) {
+                    float4 *dst = reinterpret_cast<float4 *>(pre.sum_out + (size_t)m * K + (size_t)G * 16);
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) dst[v] = f[u][v];
+                }
+            }
+        }
+    }
+    if (pre.norm_w) {
+        auto block_sum = [&](float v, int slot) {
+#pragma unroll
+            for (int o = 16; o >= 1; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, o));
+            if ((tid & 31) == 0) s_fsum[slot][tid >> 5] = v;
+            __syncthreads();
+            float t = 0.0f;
+#pragma unroll
+            for (int w = 0; w < 16; ++w) t = __fadd_rn(t, s_fsum[slot][w]);
+            return t;
+        };
+        float part = 0.0f;
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+            if (tid + u * 512 < n_groups) {
+#pragma unroll
+                for (int v = 0; v < 4; ++v)
+                    part = __fadd_rn(part, __fadd_rn(__fadd_rn(f[u][v].x, f[u][v].y), __fadd_rn(f[u][v].z, f[u][v].w)));
+            }
+        const float mean = __fdiv_rn(block_sum(part, 0), (float)K);
+        part = 0.0f;
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+            if (tid + u * 512 < n_groups) {
+#pragma unroll
+                for (int v = 0; v < 4; ++v) {
+                    const float a = __fsub_rn(f[u][v].x, mean), b2 = __fsub_rn(f[u][v].y, mean);
+                    const float c = __fsub_rn(f[u][v].z, mean), d = __fsub_rn(f[u][v].w, mean);
+                    part = __fadd_rn(part, __fadd_rn(__fadd_rn(__fmul_rn(a, a), __fmul_rn(b2, b2)), __fadd_rn(__fmul_rn(c, c), __fmul_rn(d, d))));
+                }
+            }
+        const float var = __fdiv_rn(block_sum(part, 1), (float)(K > 1 ? K - 1 : 1));
+        const float sd = __fsqrt_rn(__fadd_rn(var, pre.eps));
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int G = tid + u * 512;
+            if (G < n_groups) {
+                const float4 *wsrc = reinterpret_cast<const float4 *>(pre.norm_w + (size_t)G * 16);
+                const float4 *bsrc = reinterpret_cast<const float4 *>(pre.norm_b + (size_t)G * 16);
+#pragma unroll
+                for (int v = 0; v < 4; ++v) {
+                    const float4 w4 = __ldg(wsrc + v), b4 = __ldg(bsrc + v);
+                    f[u][v].x = __fadd_rn(__fmul_rn(__fdiv_rn(__fsub_rn(f[u][v].x, mean), sd), w4.x), b4.x);
+                    f[u][v].y = __fadd_rn(__fmul_rn(__fdiv_rn(__fsub_rn(f[u][v].y, mean), sd), w4.y), b4.y);
+                    f[u][v].z = __fadd_rn(__fmul_rn(__fdiv_rn(__fsub_rn(f[u][v].z, mean), sd), w4.z), b4.z);
+                    f[u][v].w = __fadd_rn(__fmul_rn(__fdiv_rn(__fsub_rn(f[u][v].w, mean), sd), w4.w), b4.w);
+                }
+                if (pre.normed_out) {
+                    float4 *dst = reinterpret_cast<float4 *>(pre.normed_out + (size_t)m * K + (size_t)G * 16);
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) dst[v] = f[u][v];
+                }
+            }
+        }
+    }
 }
 
 #endif  // __CUDACC__

@@ -53,6 +53,8 @@ struct DecodeParams {
     int8_t *q_out;
     float *a_scale_out;
     float w_scale, w_scale2;
+    int seg_end0, seg_end1;       // stacked matrices: rows below seg_end0 use w_scale, below seg_end1 seg_scale1, the rest seg_scale2
+    float seg_scale1, seg_scale2;
     int M, K, N;
     size_t ldy;
     int chunks;          // K / 64: a chunk is the 16 bytes (64 weights) of one 128-bit load
@@ -504,7 +506,8 @@ decode_kernel(const DecodeParams p)
                         p.y[o] = out;
                     } else {
                         if (p.acc_out) p.acc_out[o] = tot[t][r];
-                        out = __fmul_rn((float)tot[t][r], __fmul_rn(p.w_scale, s_ascale[m]));
+                        const float ws = row < p.seg_end0 ? p.w_scale : (row < p.seg_end1 ? p.seg_scale1 : p.seg_scale2);
+                        out = __fmul_rn((float)tot[t][r], __fmul_rn(ws, s_ascale[m]));
                         if (p.n_peers) {   // this GPU's column slice, stored into every GPU's full-width output
                             for (int pr = 0; pr < p.n_peers; ++pr) p.y_peers[pr][o] = out;
                         } else if (p.y) {
@@ -615,13 +618,17 @@ decode_kernel(const DecodeParams p)
 // warps want (header: per-warp-slice sums and absmax/127; then fragment-ordered bytes), so that
 // kernel fetches it with a single bulk copy.  cw/sw/nt describe the consuming instantiation.
 // Semantics: TernaryProcessor::quantize_activations (ternary_operations.rs:130-163).
-__global__ void __launch_bounds__(512) decode_quantize_kernel(const float *__restrict__ x, int M, int K, int cw, int sw, int nt, int mrows,
+// pre: the decoder-layer glue in front of the quantiser (residual add, SubLN), applied to the row while it
+// sits in registers; sums run in a fixed order (lane tree, then the sixteen warps in turn).
+__global__ void __launch_bounds__(512) decode_quantize_kernel(const float *x, int M, int K, int cw, int sw, int nt, int mrows,
                                                               unsigned char *__restrict__ image,
                                                               const unsigned *__restrict__ amax_in, int n_amax_in,
-                                                              int8_t *__restrict__ q_out, float *__restrict__ a_scale_out)
+                                                              int8_t *__restrict__ q_out, float *__restrict__ a_scale_out,
+                                                              const RowPre pre)
 {
     __shared__ unsigned s_wkey[16];
     __shared__ int s_sum[DEC_MAX_CWARPS];
+    __shared__ float s_fsum[2][16];
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the decode kernel may start fetching weights
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int m = blockIdx.x, tid = threadIdx.x;
@@ -636,9 +643,10 @@ __global__ void __launch_bounds__(512) decode_quantize_kernel(const float *__res
         if (G < n_groups) {
             const float4 *src = reinterpret_cast<const float4 *>(row + (size_t)G * 16);
 #pragma unroll
-            for (int v = 0; v < 4; ++v) f[u][v] = __ldg(src + v);
+            for (int v = 0; v < 4; ++v) f[u][v] = src[v];   // plain loads: sum_out may alias x
         }
     }
+    apply_row_pre(f, pre, m, K, tid, s_fsum);
     unsigned key = 0;
     if (amax_in) {
         for (int i = tid; i < n_amax_in; i += 512) key = max(key, __ldg(amax_in + (size_t)m * 256 + i));
@@ -944,15 +952,29 @@ bitnet_status_t launch_decode(const ForwardArgs &a, cudaStream_t stream)
     p.weights_first = (a.flags & BITNET_FLAG_PDL) ? 1 : 0;
     p.mrows = decode_mrows(a.M);
     p.n_peers = a.n_peers;
+    p.seg_end0 = p.seg_end1 = 0x7fffffff;
+    if (a.n_seg > 0) {
+        if (dual || a.n_seg > 2) return fail(BITNET_ERR_INVALID_CONFIG, "at most three stacked matrices, and not with the gate/up pair");
+        p.seg_end0 = (int)a.seg_end[0]; p.seg_scale1 = a.seg_scale[0];
+        if (a.n_seg > 1) { p.seg_end1 = (int)a.seg_end[1]; p.seg_scale2 = a.seg_scale[1]; }
+    }
     for (int r = 0; r < a.n_peers && r < 8; ++r) p.y_peers[r] = a.y_peers[r];
     if (a.n_peers && dual) return fail(BITNET_ERR_UNSUPPORTED_OPERATION, "peer outputs are not available for the gate/up pair launch");
     const DecodePlan pl = decode_plan(a.M, a.K, a.N, dual, (a.flags & BITNET_FLAG_THROUGHPUT) != 0);
 
-    if (!in_i8 && a.image_ws && (a.force_split || use_split(a.M, a.K))) {
+    if (a.pre && (in_i8 || !a.image_ws || a.amax_in))
+        return fail(BITNET_ERR_INVALID_CONFIG, "row glue (residual, normalisation) runs in the quantiser launch: it needs the image workspace");
+    if (!in_i8 && a.image_ws && (a.force_split || a.pre || a.image_ready || use_split(a.M, a.K))) {
         // quantise once, then let every CTA fetch the result
         const size_t need = decode_image_bytes_always(a.M, a.K, a.N, dual);
         if (a.image_ws_bytes < need || misaligned(a.image_ws, 16))
             return fail(BITNET_ERR_WORKSPACE, "decode path needs %zu bytes of 16-byte aligned workspace", need);
+        const RowPre pre = a.pre ? *a.pre : RowPre{};
+        if (pre.norm_w && (!pre.norm_b || misaligned(pre.norm_w, 16) || misaligned(pre.norm_b, 16)))
+            return fail(BITNET_ERR_INVALID_CONFIG, "normalisation needs 16-byte aligned weight and bias vectors");
+        if ((pre.residual && misaligned(pre.residual, 16)) || (pre.sum_out && misaligned(pre.sum_out, 16)) ||
+            (pre.normed_out && misaligned(pre.normed_out, 16)))
+            return fail(BITNET_ERR_INVALID_CONFIG, "row glue buffers must be 16-byte aligned");
         cudaLaunchConfig_t cfg = {};
         cudaLaunchAttribute attrs[1];
         cfg.gridDim = dim3((unsigned)a.M);
@@ -964,9 +986,10 @@ bitnet_status_t launch_decode(const ForwardArgs &a, cudaStream_t stream)
             attrs[0].val.programmaticStreamSerializationAllowed = 1;
             cfg.numAttrs = 1;
         }
-        BITNET_CUDA(cudaLaunchKernelEx(&cfg, decode_quantize_kernel, a.x, (int)a.M, (int)a.K, pl.cw, pl.sw, pl.nt, p.mrows,
-                                       static_cast<unsigned char *>(a.image_ws), a.amax_in, a.n_amax_in, a.q_out,
-                                       a.a_scale_out));
+        if (!a.image_ready)
+            BITNET_CUDA(cudaLaunchKernelEx(&cfg, decode_quantize_kernel, a.x, (int)a.M, (int)a.K, pl.cw, pl.sw, pl.nt, p.mrows,
+                                           static_cast<unsigned char *>(a.image_ws), a.amax_in, a.n_amax_in, a.q_out,
+                                           a.a_scale_out, pre));
         p.image = static_cast<const unsigned char *>(a.image_ws);
         p.q_out = nullptr; p.a_scale_out = nullptr; p.amax_in = nullptr;
         p.weights_first = 1;   // the image does not exist before the quantiser ends: fetch weights meanwhile

@@ -183,3 +183,102 @@ def prepare_weights(packed: torch.Tensor, out_features: int, in_features: int, l
     check(L.load().bitnet_prepare_weights(packed.data_ptr(), out_features, in_features, layout_id, count.data_ptr(),
                                           C.byref(mask), _stream(stream)))
     return int(count.item()), {"decode": bool(mask.value & 1), "prefill": bool(mask.value & 2)}
+
+
+# ---- decoder-layer glue and decode-step pieces -----------------------------------------------------------
+
+def make_glue(residual=None, sum_out=None, norm_weight=None, norm_bias=None, eps=1e-5, normed_out=None) -> L.RowGlue:
+    p = lambda t: t.data_ptr() if t is not None else None   # noqa: E731
+    return L.RowGlue(p(residual), p(sum_out), p(norm_weight), p(norm_bias), eps, p(normed_out))
+
+
+def bitlinear_forward_fused(wp_stacked: torch.Tensor, rows, scales, x: torch.Tensor, *, glue: L.RowGlue | None = None,
+                            path="auto", pdl=False, out=None, debug=False, stream=None):
+    """Up to three BitLinears that share x, weights stacked along the output features (`rows` features and one
+    scale each), with optional row glue (residual add, SubLN) applied to x first.  Returns y [M, sum(rows)]."""
+    wp_stacked = _require(wp_stacked, torch.uint8, "weights")
+    x = _require(x, torch.float32, "x")
+    M, K = x.shape
+    N = int(sum(rows))
+    if wp_stacked.numel() != packed_len(N * K):
+        raise IncompatibleShapes(f"Weight tensor size mismatch: expected {packed_len(N * K)} bytes, got {wp_stacked.numel()}")
+    st = L.Stack(len(rows), (C.c_size_t * 3)(*rows), (C.c_float * 3)(*scales))
+    y = out if out is not None else torch.empty((M, N), dtype=torch.float32, device=x.device)
+    dbg = {}
+    if debug:
+        dbg = {"q": torch.empty((M, K), dtype=torch.int8, device=x.device),
+               "a_scale": torch.empty((M,), dtype=torch.float32, device=x.device),
+               "acc": torch.empty((M, N), dtype=torch.int32, device=x.device)}
+    opts = make_opts(path, pdl, dbg.get("q"), dbg.get("a_scale"), dbg.get("acc"))
+    need = C.c_size_t()
+    check(L.load().bitnet_bitlinear_fused_workspace_size(M, K, N, opts.path, C.byref(need)))
+    ws = _workspace(need.value, x.device, stream)
+    check(L.load().bitnet_bitlinear_forward_fused(wp_stacked.data_ptr(), C.byref(st), x.data_ptr(), C.byref(glue) if glue else None,
+                                                  y.data_ptr(), M, K, C.byref(opts), _aligned_ptr(ws), need.value, _stream(stream)))
+    return (y, dbg) if debug else y
+
+
+def ffn_forward_fused(w_gate, s_gate, w_up, s_up, w_down, s_down, x: torch.Tensor, ffn: int, *, glue: L.RowGlue | None = None,
+                      path="auto", pdl=False, out=None, h_out=None, stream=None):
+    """FFN block with row glue in front of the gate and up projections; returns (y, h)."""
+    x = _require(x, torch.float32, "x")
+    M, hidden = x.shape
+    y = out if out is not None else torch.empty((M, hidden), dtype=torch.float32, device=x.device)
+    h = h_out if h_out is not None else torch.empty((M, ffn), dtype=torch.float32, device=x.device)
+    opts = make_opts(path, pdl)
+    need = C.c_size_t()
+    check(L.load().bitnet_ffn_fused_workspace_size(M, hidden, ffn, opts.path, C.byref(need)))
+    ws = _workspace(need.value, x.device, stream)
+    check(L.load().bitnet_ffn_forward_fused(w_gate.data_ptr(), s_gate, w_up.data_ptr(), s_up, w_down.data_ptr(), s_down,
+                                            x.data_ptr(), C.byref(glue) if glue else None, h.data_ptr(), y.data_ptr(), M, hidden,
+                                            ffn, C.byref(opts), _aligned_ptr(ws), need.value, _stream(stream)))
+    return y, h
+
+
+def row_glue(x: torch.Tensor, glue: L.RowGlue, stream=None) -> None:
+    """The glue alone: writes x + residual to glue.sum_out and SubLN(x + residual) to glue.normed_out."""
+    x = _require(x, torch.float32, "x")
+    check(L.load().bitnet_row_glue_forward(x.data_ptr(), x.shape[0], x.shape[1], C.byref(glue), _stream(stream)))
+
+
+def attention_decode(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, pos: torch.Tensor, n_heads: int,
+                     n_kv_heads: int, head_dim: int, *, n_splits: int = 0, stream=None) -> torch.Tensor:
+    """One new token per sequence over bf16 caches [B, n_kv_heads, max_seq, head_dim]: qkv [B, (n_heads + 2 n_kv_heads) *
+    head_dim] holds q, k, v side by side; the new k and v are stored at position pos[b], which is not advanced."""
+    qkv = _require(qkv, torch.float32, "qkv")
+    B = qkv.shape[0]
+    qd, kd = n_heads * head_dim, n_kv_heads * head_dim
+    if qkv.shape[1] != qd + 2 * kd:
+        raise IncompatibleShapes(f"qkv must be [B,{qd + 2 * kd}], got {list(qkv.shape)}")
+    for name, t in (("k_cache", k_cache), ("v_cache", v_cache)):
+        if t.dtype != torch.bfloat16 or not t.is_contiguous() or t.dim() != 4 or t.shape[0] < B or t.shape[1] != n_kv_heads or t.shape[3] != head_dim:
+            raise IncompatibleShapes(f"{name} must be a contiguous bf16 tensor [>=B,{n_kv_heads},max_seq,{head_dim}]")
+    if pos.dtype != torch.int32:
+        raise UnsupportedDataType("pos must be int32")
+    max_seq = k_cache.shape[2]
+    if n_splits <= 0:
+        n_splits = L.load().bitnet_attention_splits(B, n_kv_heads, max_seq)
+    need = C.c_size_t()
+    check(L.load().bitnet_attention_scratch_size(B, n_heads, n_kv_heads, head_dim, n_splits, C.byref(need)))
+    key = ("attn", qkv.device.index or 0, _stream(stream), need.value)
+    scratch = _workspaces.get(key)
+    if scratch is None:
+        scratch = torch.zeros(need.value + 256, dtype=torch.uint8, device=qkv.device)   # the arrival counters start at zero
+        _workspaces[key] = scratch
+    out = torch.empty((B, qd), dtype=torch.float32, device=qkv.device)
+    check(L.load().bitnet_attention_decode(qkv.data_ptr(), qd + 2 * kd, qd, qd + kd, k_cache.data_ptr(), v_cache.data_ptr(),
+                                           pos.data_ptr(), out.data_ptr(), B, n_heads, n_kv_heads, head_dim, max_seq, n_splits,
+                                           _aligned_ptr(scratch), need.value, _stream(stream)))
+    return out
+
+
+def sample_tokens(logits: torch.Tensor, rng_state: torch.Tensor | None = None, *, temperature=1.0, top_k=0, top_p=1.0,
+                  deterministic=False, stream=None) -> torch.Tensor:
+    """TokenSampler::sample for every row of logits [B, vocab]; rng_state: int64 [B] generator states (updated)."""
+    logits = _require(logits, torch.float32, "logits")
+    B, V = logits.shape
+    cfg = L.SamplingConfig(temperature, top_k, top_p, 0, 1 if deterministic else 0)
+    out = torch.empty((B,), dtype=torch.int32, device=logits.device)
+    check(L.load().bitnet_sample_tokens(logits.data_ptr(), B, V, C.byref(cfg), rng_state.data_ptr() if rng_state is not None else None,
+                                        out.data_ptr(), _stream(stream)))
+    return out

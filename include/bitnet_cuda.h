@@ -188,6 +188,99 @@ bitnet_status_t bitnet_ffn_forward(const uint8_t *w_gate_dev, float s_gate,
 bitnet_status_t bitnet_ffn_workspace_size(size_t M, size_t hidden, size_t ffn, int32_t path,
                                           size_t *bytes);
 
+/* ---- decoder-layer glue fused around the projections ------------------------------------------ */
+
+/* Row-wise operations applied to x on its way into a projection, inside the launch that quantises it
+ * (TransformerBlock::forward, bitnet-inference/src/engine/transformer_layers.rs:675-709: the residual add
+ * in front of a sub-layer, and SubLNNormalization::forward, :356-386: (x - mean) / sqrt(var + eps) *
+ * weight + bias over the feature dimension, var with the n - 1 divisor of candle-core 0.8's var_keepdim).
+ * All members optional; zero-initialise.  Needs K % 16 == 0 and K <= 16384. */
+typedef struct bitnet_row_glue {
+    const float *residual_dev;    /* [M,K]: the row that is normalised and quantised is x + residual */
+    float *sum_out_dev;           /* [M,K]: receives x + residual (may be x itself: the hidden state updated in place) */
+    const float *norm_weight_dev; /* [K]: SubLN weight; NULL = no normalisation */
+    const float *norm_bias_dev;   /* [K]: SubLN bias (required with the weight) */
+    float norm_eps;
+    float *normed_out_dev;        /* [M,K]: receives the normalised fp32 row (for parity tests) */
+} bitnet_row_glue;
+
+/* Up to three BitLinear layers that read the same x (the q, k and v projections of
+ * MultiHeadAttention::forward, transformer_layers.rs:469-475), their packed weights stacked along the
+ * output features in one buffer; every member but the last must end on a 16-byte boundary of the packed
+ * stream (rows * K % 64 == 0).  Each keeps its own weight scale. */
+typedef struct bitnet_stack {
+    int32_t n_members;   /* 1..3 */
+    size_t rows[3];      /* output features of each member */
+    float scales[3];
+} bitnet_stack;
+
+/* y[M, sum(rows)] = the stacked BitLinears applied to glue(x).  Same semantics as one
+ * bitnet_bitlinear_forward per member on the glued row; for M <= 16 everything runs in two launches (the
+ * quantiser launch carries the glue, one decode launch streams all members).  workspace_dev:
+ * bitnet_bitlinear_fused_workspace_size() bytes. */
+bitnet_status_t bitnet_bitlinear_forward_fused(const uint8_t *weights_dev, const bitnet_stack *stack,
+                                               const float *x_dev, const bitnet_row_glue *glue, float *y_dev,
+                                               size_t M, size_t K, const bitnet_forward_opts *opts,
+                                               void *workspace_dev, size_t workspace_bytes, bitnet_stream_t stream);
+bitnet_status_t bitnet_bitlinear_fused_workspace_size(size_t M, size_t K, size_t N_total, int32_t path, size_t *bytes);
+
+/* bitnet_ffn_forward with row glue in front of the gate and up projections (the post-attention
+ * normalisation and the attention residual of TransformerBlock::forward, transformer_layers.rs:690-701). */
+bitnet_status_t bitnet_ffn_forward_fused(const uint8_t *w_gate_dev, float s_gate,
+                                         const uint8_t *w_up_dev, float s_up,
+                                         const uint8_t *w_down_dev, float s_down,
+                                         const float *x_dev, const bitnet_row_glue *glue, float *h_dev, float *y_dev,
+                                         size_t M, size_t hidden, size_t ffn,
+                                         const bitnet_forward_opts *opts,
+                                         void *workspace_dev, size_t workspace_bytes, bitnet_stream_t stream);
+bitnet_status_t bitnet_ffn_fused_workspace_size(size_t M, size_t hidden, size_t ffn, int32_t path, size_t *bytes);
+
+/* The glue alone: sum_out = x + residual, normed_out = SubLN(x + residual). */
+bitnet_status_t bitnet_row_glue_forward(const float *x_dev, size_t M, size_t K, const bitnet_row_glue *glue,
+                                        bitnet_stream_t stream);
+
+/* ---- decode-step kernels around the projections ------------------------------------------------- */
+
+/* Attention of ONE new token per sequence over a bf16 KV cache, grouped-query form
+ * (MultiHeadAttention::forward, transformer_layers.rs:460-547: softmax(q k^T / sqrt(head_dim)) v; RoPE is
+ * the identity in the reference, :278-289; cache shape [batch, kv_heads, max_seq, head_dim] as
+ * KVCache::initialize_cache, bitnet-inference/src/cache/kv_cache.rs:104-121, in bf16 instead of f32).
+ * qkv_dev [B, ldq] holds the new token's q at column 0 (n_heads * head_dim values), k at k_off, v at v_off
+ * (n_kv_heads * head_dim each).  pos_dev[b] = tokens already cached for sequence b: the kernel stores the
+ * new k and v (rounded to bf16) at that position and attends over positions 0..pos[b].  It does not
+ * advance pos_dev.  out_dev [B, n_heads * head_dim].  head_dim 64 or 128; n_heads / n_kv_heads in
+ * {1,2,4,8}.  n_splits: CTAs per (sequence, KV head) along the keys (bitnet_attention_splits suggests
+ * one); scratch_dev: bitnet_attention_scratch_size() bytes, zero-filled once by the caller before the
+ * first launch, 256-byte aligned (NULL allowed when n_splits == 1). */
+bitnet_status_t bitnet_attention_decode(const float *qkv_dev, size_t ldq, size_t k_off, size_t v_off,
+                                        void *k_cache_dev, void *v_cache_dev, const int32_t *pos_dev, float *out_dev,
+                                        size_t B, size_t n_heads, size_t n_kv_heads, size_t head_dim, size_t max_seq,
+                                        int32_t n_splits, void *scratch_dev, size_t scratch_bytes, bitnet_stream_t stream);
+bitnet_status_t bitnet_attention_scratch_size(size_t B, size_t n_heads, size_t n_kv_heads, size_t head_dim,
+                                              int32_t n_splits, size_t *bytes);
+int32_t bitnet_attention_splits(size_t B, size_t n_kv_heads, size_t max_context);
+
+/* SamplingConfig (bitnet-inference/src/engine/sampling.rs:11-45). */
+typedef struct bitnet_sampling_config {
+    float temperature;      /* 1.0 */
+    uint32_t top_k;         /* 0 = off */
+    float top_p;            /* 1.0 = off */
+    uint64_t seed;          /* sequence i draws from a generator seeded with seed + i (BatchSampler::new, :419-426) */
+    int32_t deterministic;  /* 1 = argmax */
+} bitnet_sampling_config;
+void bitnet_sampling_config_default(bitnet_sampling_config *cfg);
+
+/* TokenSampler::sample for B sequences (sampling.rs:106-189): argmax (first index on ties) when
+ * deterministic; otherwise logits / temperature, top-k and top-p filters (ties with the cut-off value are
+ * kept), softmax, and one draw per sequence with the reference's generator (state * 1103515245 + 12345,
+ * :273-276; u = bits 16..39 of the state / 2^24), taking the first index whose running probability exceeds
+ * u.  The reference's filters and softmax are stubs and its draw ignores the logits; this does what its
+ * doc comments describe.  rng_state_dev [B] uint64 (bitnet_seed_sampler), next_ids_dev [B] int32. */
+bitnet_status_t bitnet_sample_tokens(const float *logits_dev, size_t B, size_t vocab,
+                                     const bitnet_sampling_config *cfg, uint64_t *rng_state_dev,
+                                     int32_t *next_ids_dev, bitnet_stream_t stream);
+bitnet_status_t bitnet_seed_sampler(uint64_t *rng_state_dev, size_t B, uint64_t seed, bitnet_stream_t stream);
+
 /* ---- packed-weight helpers (device) -------------------------------------------------- */
 
 /* BitPacked2BitPacker::pack / unpack (packing.rs:352-394) on device buffers.
@@ -336,6 +429,65 @@ bitnet_status_t bitnet_backend_ffn_plan_create(bitnet_backend *b, const bitnet_f
                                                bitnet_ffn_plan **out);
 bitnet_status_t bitnet_backend_ffn_plan_run(bitnet_ffn_plan *plan);
 void bitnet_backend_ffn_plan_destroy(bitnet_ffn_plan *plan);
+
+/* ---- decode step of a whole model (handle based) ------------------------------------------------- */
+/* ForwardPassPipeline (bitnet-inference/src/engine/forward_pass_pipeline.rs:146-362) for one new token per
+ * sequence with a KV cache: token embedding, num_layers transformer blocks (TransformerBlock::forward,
+ * transformer_layers.rs:675-709: SubLN -> attention -> residual -> SubLN -> FFN -> residual), the
+ * language-model head (a BitLinear on the last hidden state, no final normalisation, :283-291) and the
+ * sampler.  Device memory comes from the backend's pool (size it for the model: packed weights, the fp32
+ * embedding table, 2 x layers x max_batch x kv_heads x max_seq x head_dim bf16 of cache, max_batch x vocab
+ * fp32 logits).  All sequences of a batch advance together, one token per step. */
+typedef struct bitnet_decoder bitnet_decoder;
+
+typedef struct bitnet_decoder_config {   /* ForwardPassConfig + TransformerConfig, forward_pass_pipeline.rs:80-118 */
+    size_t vocab_size, hidden_size, num_layers, num_heads, num_kv_heads, head_dim, ffn_size, max_seq_len, max_batch;
+    float norm_eps;                       /* rms_norm_eps */
+} bitnet_decoder_config;
+
+typedef struct bitnet_decoder_layer {     /* one TransformerBlock's parameters, HOST pointers */
+    const uint8_t *q_packed, *k_packed, *v_packed, *o_packed;   /* [heads*head_dim, hidden], [kv*head_dim, hidden] x2, [hidden, heads*head_dim] */
+    const uint8_t *gate_packed, *up_packed, *down_packed;       /* [ffn, hidden] x2, [hidden, ffn] */
+    float q_scale, k_scale, v_scale, o_scale, gate_scale, up_scale, down_scale;
+    const float *input_norm_weight, *input_norm_bias;           /* input_layernorm, [hidden] */
+    const float *post_norm_weight, *post_norm_bias;             /* post_attention_layernorm, [hidden] */
+} bitnet_decoder_layer;
+
+enum {
+    BITNET_DECODER_LOGITS = 0,      /* fp32 [batch, vocab] of the last generation step */
+    BITNET_DECODER_HIDDEN = 1,      /* fp32 [batch, hidden]: the last hidden state */
+    BITNET_DECODER_POSITIONS = 2,   /* int32 [batch]: tokens cached per sequence */
+    BITNET_DECODER_KEY_CACHE = 3,   /* bf16 [layers, max_batch, kv_heads, max_seq, head_dim] */
+    BITNET_DECODER_VALUE_CACHE = 4
+};
+
+void bitnet_decoder_config_default(bitnet_decoder_config *cfg);
+bitnet_status_t bitnet_decoder_create(bitnet_backend *b, const bitnet_decoder_config *cfg, bitnet_decoder **out);
+void bitnet_decoder_destroy(bitnet_decoder *d);
+bitnet_status_t bitnet_decoder_load_embedding(bitnet_decoder *d, const float *table_host);      /* [vocab, hidden] */
+bitnet_status_t bitnet_decoder_load_layer(bitnet_decoder *d, size_t index, const bitnet_decoder_layer *weights);
+bitnet_status_t bitnet_decoder_load_lm_head(bitnet_decoder *d, const uint8_t *packed_host, float scale);  /* [vocab, hidden] */
+/* KVCache::reset (kv_cache.rs:168-172): forget every cached token. */
+bitnet_status_t bitnet_decoder_reset(bitnet_decoder *d);
+/* Steps are replayed as CUDA graphs recorded on first use (default); 0 launches kernel by kernel. */
+bitnet_status_t bitnet_decoder_set_graphs(bitnet_decoder *d, int32_t enabled);
+/* Context tokens: ids_host [B, T] row-major; each of the T steps caches one token per sequence, nothing
+ * is sampled.  Returns when done. */
+bitnet_status_t bitnet_decoder_feed(bitnet_decoder *d, const int32_t *ids_host, size_t B, size_t T);
+/* Generation (ForwardPassPipeline::generate, forward_pass_pipeline.rs:311-362): ids_host [B] is the last
+ * known token of each sequence; n_new steps, each feeding its sampled token to the next, without a host
+ * round trip in between; out_host [B, n_new].  eos_id >= 0: a sequence that samples it is finished and
+ * keeps emitting it (GenerationState::should_stop); the loop ends early once every sequence has.
+ * *steps_run receives the steps taken. */
+bitnet_status_t bitnet_decoder_decode(bitnet_decoder *d, const int32_t *ids_host, size_t B, size_t n_new,
+                                      const bitnet_sampling_config *sampling, int32_t eos_id,
+                                      int32_t *out_host, size_t *steps_run);
+/* reset + feed(prompt[:, :-1]) + decode(prompt[:, -1]): prompt_host [B, prompt_len], out_host [B, max_new_tokens]. */
+bitnet_status_t bitnet_decoder_generate(bitnet_decoder *d, const int32_t *prompt_host, size_t B, size_t prompt_len,
+                                        size_t max_new_tokens, const bitnet_sampling_config *sampling,
+                                        int32_t eos_id, int32_t *out_host, size_t *steps_run);
+/* Copies an internal buffer (BITNET_DECODER_*) to the host, for parity tests. */
+bitnet_status_t bitnet_decoder_read(bitnet_decoder *d, int32_t what, void *host, size_t bytes);
 
 #ifdef __cplusplus
 }
