@@ -534,6 +534,72 @@ def decode_stack_figures(torch, ops, gen):
     return out
 
 
+MODEL = dict(num_layers=30, vocab_size=128256, hidden_size=2560, num_heads=20, num_kv_heads=5, head_dim=128,
+             ffn_intermediate_size=6912)
+MODEL_CONTEXT, MODEL_NEW_TOKENS, MODEL_SEQUENCES = 512, 128, 64
+
+
+def model_step_bytes(seqs, context):
+    """HBM bytes one decode step must move: every packed weight once (layers + language-model head), and each
+    sequence's cached keys and values (bf16) at the given context length."""
+    H, F, V, L = MODEL["hidden_size"], MODEL["ffn_intermediate_size"], MODEL["vocab_size"], MODEL["num_layers"]
+    qd, kd = MODEL["num_heads"] * MODEL["head_dim"], MODEL["num_kv_heads"] * MODEL["head_dim"]
+    weights = L * ((qd + 2 * kd) * H + H * qd + 3 * F * H) // 4 + V * H // 4
+    kv = L * 2 * kd * 2 * context * seqs
+    return weights, kv
+
+
+def model_decode_figures(local, seqs, peak_gbs, context=MODEL_CONTEXT, new_tokens=MODEL_NEW_TOKENS, layers=None):
+    """Decode of the random-init 2B-shaped model (30 layers, hidden 2560, 20 heads / 5 KV heads, head_dim 128, FFN 6912,
+    vocabulary 128256, bf16 KV cache) for `seqs` sequences on this GPU: `context` random tokens are cached first (not
+    timed), then `new_tokens` tokens per sequence are generated greedily through bitnet_decoder_decode (host token ids in,
+    host token ids out: the wall time of that call is the figure).  Returns tokens/s of this GPU."""
+    import numpy as np
+
+    import oracle
+    from bitnet_mlx_rs_b200 import cuda
+    from bitnet_mlx_rs_b200.pipeline import ForwardPassConfig, ForwardPassPipeline, SamplingConfig
+
+    cfgd = dict(MODEL)
+    if layers:
+        cfgd["num_layers"] = layers
+    cfg = ForwardPassConfig(max_seq_len=context + new_tokens, max_batch=seqs, **cfgd)
+    H, F, V = cfg.hidden_size, cfg.ffn_intermediate_size, cfg.vocab_size
+    qd, kd = cfg.num_heads * cfg.head_dim, cfg.num_kv_heads * cfg.head_dim
+    backend = cuda.CudaBackend(cuda.CudaBackendConfig(device_id=local, memory_pool_size=24 << 30))
+    pipe = ForwardPassPipeline(backend, cfg)
+    block = oracle.gen_activations(0, 7000, (8192, H))
+    pipe.load_embedding(np.tile(block, (V // 8192 + 1, 1))[:V])
+    ones, zeros = np.ones(H, np.float32), np.zeros(H, np.float32)
+    for l in range(cfg.num_layers):
+        shapes = {"q": (qd, H), "k": (kd, H), "v": (kd, H), "o": (H, qd), "gate": (F, H), "up": (F, H), "down": (H, F)}
+        lw = {}
+        for i, (name, (n, k)) in enumerate(shapes.items()):
+            lw[name] = oracle.gen_ternary_packed(0, 8000 + 10 * l + i, n * k)
+            lw["s_" + {"gate": "g", "up": "u", "down": "d"}.get(name, name)] = oracle.gen_weight_scale(0, 8000 + 10 * l + i, k)
+        lw.update(n1w=ones, n1b=zeros, n2w=ones, n2b=zeros)     # SubLNNormalization::new: ones and zeros
+        pipe.load_layer(l, lw)
+    pipe.load_lm_head(oracle.gen_ternary_packed(0, 8999, V * H), oracle.gen_weight_scale(0, 8999, H))
+    rng = np.random.default_rng(local)
+    ids = rng.integers(0, V, size=(seqs, context)).astype(np.int32)
+    pipe.reset()
+    pipe.feed(ids[:, :context - 1])
+    warm, _ = pipe.decode(ids[:, context - 1], 3, SamplingConfig(deterministic=True))     # records the step graph
+    t0 = time.perf_counter()
+    toks, steps = pipe.decode(warm[:, -1], new_tokens - 3, SamplingConfig(deterministic=True))
+    dt = time.perf_counter() - t0
+    assert steps == new_tokens - 3 and (toks >= 0).all() and (toks < V).all()
+    ms_step = dt * 1e3 / steps
+    weights, kv = model_step_bytes(seqs, context + new_tokens // 2)
+    pipe.close()
+    backend.close()
+    return {"sequences": seqs, "context": context, "new_tokens": steps, "ms_per_step": ms_step, "tokens_per_s": seqs * steps / dt,
+            "hbm_bytes_per_step": weights + kv, "gbs": (weights + kv) / (ms_step * 1e-3) / 1e9,
+            "frac_of_hbm_peak": (weights + kv) / (ms_step * 1e-3) / 1e9 / peak_gbs,
+            "roofline_ms_per_step": (weights + kv) / (peak_gbs * 1e9) * 1e3,
+            "io": "token ids host->device before, generated ids device->host after; sampling (argmax) on the device"}
+
+
 def prefill_layer_figures(torch, ops, gen):
     """The seven BitLinear projections of one 2B decoder layer at M = 2048 tokens through the
     tensor-core path (quantiser launch + tcgen05 GEMM each), replayed from a CUDA graph."""
@@ -600,8 +666,13 @@ def main():
     ap.add_argument("--streams", type=int, default=8, help="streams the step's independent FFN blocks are dealt to (1 = one chain)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-extra", action="store_true", help="skip the single-kernel figures")
+    ap.add_argument("--model-only", type=int, default=0, metavar="SEQS",
+                    help="run only the model decode figure for this many sequences on GPU 0 and print it")
+    ap.add_argument("--model-layers", type=int, default=0, help="with --model-only: fewer layers (quick look)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.model_only:
+        print(json.dumps(model_decode_figures(0, args.model_only, measured_peaks()[0], layers=args.model_layers or None)))
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_cuda(args)
