@@ -655,6 +655,65 @@ def prefill_layer_figures(torch, ops, gen):
             "note": "no measured int8 peak on this pool; 4500 TOPS is the nominal dense figure"}
 
 
+def run_case(spec):
+    """One BitLinear (or FFN) shape on cuda:0, timed with CUDA events -- the small, self-ending workload that the
+    profiling commands under profiles/ run.  spec = kind:M:K:N[:copies[:iters]] with kind one of auto, decode, cluster,
+    prefill, generic (a single BitLinear through that path) or ffn (K = hidden, N = ffn).  `copies` distinct weight
+    buffers are rotated so that every launch streams its weights from HBM rather than L2."""
+    import torch
+
+    from bitnet_mlx_rs_b200 import ops
+    parts = spec.split(":")
+    kind, M, K, N = parts[0], int(parts[1]), int(parts[2]), int(parts[3])
+    copies = int(parts[4]) if len(parts) > 4 else 3
+    iters = int(parts[5]) if len(parts) > 5 else 2
+    torch.cuda.set_device(0)
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    x = gen_activations_on_device(torch, (M, K), gen)
+    if kind == "ffn":
+        W = [tuple(gen_packed_on_device(torch, K * N, gen) for _ in range(3)) for _ in range(copies)]
+        y, h = torch.empty((M, K), device="cuda"), torch.empty((M, N), device="cuda")
+        call = lambda i: ops.ffn_forward(W[i][0], 0.02, W[i][1], 0.02, W[i][2], 0.02, x, N, out=y, h_out=h, pdl=True)   # noqa: E731
+        nbytes = 2 * call_bytes(M, K, N) + call_bytes(M, N, K)
+        int_ops = 6.0 * M * K * N
+    else:
+        W = [gen_packed_on_device(torch, N * K, gen) for _ in range(copies)]
+        y = torch.empty((M, N), device="cuda")
+        call = lambda i: ops.bitlinear_forward(W[i], 0.02, x, N, out=y, path=kind, pdl=True)   # noqa: E731
+        nbytes = call_bytes(M, K, N)
+        int_ops = 2.0 * M * K * N
+    call(0)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # a graph of one pass over the copies keeps launch overhead out of the figure
+    run, mode = None, "stream launches"
+    try:
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                for i in range(copies):
+                    call(i)
+        g.replay()
+        torch.cuda.synchronize()
+        run, mode = g.replay, "cuda graph"
+    except Exception as ex:
+        print(f"graph capture failed ({ex}); timing stream launches", file=sys.stderr)
+        torch.cuda.synchronize()
+    e0.record()
+    for _ in range(iters):
+        if run:
+            run()
+        else:
+            for i in range(copies):
+                call(i)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (iters * copies)
+    print(json.dumps({"case": spec, "us_per_call": us, "gbs": nbytes / us / 1e3, "tops": int_ops / us / 1e6, "launch": mode,
+                      "device_flags": ops.device_error_flags()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -666,11 +725,15 @@ def main():
     ap.add_argument("--streams", type=int, default=8, help="streams the step's independent FFN blocks are dealt to (1 = one chain)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-extra", action="store_true", help="skip the single-kernel figures")
+    ap.add_argument("--case", default="", metavar="kind:M:K:N[:copies[:iters]]",
+                    help="time one BitLinear/FFN shape on GPU 0 and print it (the workload of the profiling commands)")
     ap.add_argument("--model-only", type=int, default=0, metavar="SEQS",
                     help="run only the model decode figure for this many sequences on GPU 0 and print it")
     ap.add_argument("--model-layers", type=int, default=0, help="with --model-only: fewer layers (quick look)")
     args = ap.parse_args()
-    if args.model_only:
+    if args.case:
+        run_case(args.case)
+    elif args.model_only:
         print(json.dumps(model_decode_figures(0, args.model_only, measured_peaks()[0], layers=args.model_layers or None)))
     elif args.impl == "reference":
         run_reference(args)

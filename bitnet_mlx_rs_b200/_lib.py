@@ -19,7 +19,7 @@ ERR_CUDA_NOT_ENABLED, ERR_CUDA_DRIVER, ERR_DEVICE, ERR_MEMORY_ALLOCATION, ERR_KE
 ERR_INVALID_CONFIG, ERR_UNSUPPORTED_OPERATION, ERR_STREAM_SYNC, ERR_UNSUPPORTED_DTYPE = 6, 7, 8, 9
 ERR_INCOMPATIBLE_SHAPES, ERR_PERFORMANCE, ERR_NULL_POINTER, ERR_WORKSPACE = 10, 11, 12, 13
 
-PATH_AUTO, PATH_DECODE, PATH_PREFILL, PATH_GENERIC = 0, 1, 2, 3
+PATH_AUTO, PATH_DECODE, PATH_PREFILL, PATH_GENERIC, PATH_CLUSTER = 0, 1, 2, 3, 4
 FLAG_PDL = 1
 FLAG_THROUGHPUT = 2
 

@@ -58,6 +58,7 @@ static int resolve_path(int path, size_t M, size_t K, size_t N)
 {
     if (path != BITNET_PATH_AUTO) return path;
     if (M <= 16 && decode_supports(M, K, N)) return BITNET_PATH_DECODE;
+    if (M <= 128 && midm_can_run(M, K, N, false)) return BITNET_PATH_CLUSTER;
     if (prefill_supports(M, K, N)) return BITNET_PATH_PREFILL;
     return BITNET_PATH_GENERIC;
 }
@@ -185,6 +186,7 @@ static size_t forward_workspace(size_t M, size_t K, size_t N, int path, bool glu
         case BITNET_PATH_DECODE: return glue ? decode_image_bytes_always(M, K, N, false) : decode_image_bytes(M, K, N, false);
         case BITNET_PATH_PREFILL: return prefill_workspace_bytes(M, K, N) + (glue ? glue_bytes(M, K) : 0);
         case BITNET_PATH_GENERIC: return quant_workspace_bytes(M, K) + (glue ? glue_bytes(M, K) : 0);
+        case BITNET_PATH_CLUSTER: return midm_workspace_bytes(M, K);
     }
     return 0;
 }
@@ -194,7 +196,7 @@ extern "C" bitnet_status_t bitnet_bitlinear_workspace_size(size_t M, size_t K, s
     if (!bytes) return fail(BITNET_ERR_NULL_POINTER, "bitnet_bitlinear_workspace_size: null output");
     *bytes = 0;
     if (M == 0 || N == 0) return BITNET_OK;
-    if (path < BITNET_PATH_AUTO || path > BITNET_PATH_GENERIC) return fail(BITNET_ERR_INVALID_CONFIG, "unknown path %d", path);
+    if (path < BITNET_PATH_AUTO || path > BITNET_PATH_CLUSTER) return fail(BITNET_ERR_INVALID_CONFIG, "unknown path %d", path);
     *bytes = forward_workspace(M, K, N, path, false);
     return BITNET_OK;
 }
@@ -204,7 +206,7 @@ extern "C" bitnet_status_t bitnet_bitlinear_fused_workspace_size(size_t M, size_
     if (!bytes) return fail(BITNET_ERR_NULL_POINTER, "bitnet_bitlinear_fused_workspace_size: null output");
     *bytes = 0;
     if (M == 0 || N_total == 0) return BITNET_OK;
-    if (path < BITNET_PATH_AUTO || path > BITNET_PATH_GENERIC) return fail(BITNET_ERR_INVALID_CONFIG, "unknown path %d", path);
+    if (path < BITNET_PATH_AUTO || path > BITNET_PATH_CLUSTER) return fail(BITNET_ERR_INVALID_CONFIG, "unknown path %d", path);
     *bytes = forward_workspace(M, K, N_total, path, true);
     return BITNET_OK;
 }
@@ -262,6 +264,22 @@ static bitnet_status_t forward_impl(const uint8_t *weights_dev, const size_t *ro
         return launch_decode(a, s);
     }
 
+    if (path == BITNET_PATH_CLUSTER) {
+        // quantiser launch (with the glue) + one cluster launch over all stacked members
+        ForwardArgs a = {};
+        a.wp = weights_dev; a.w_scale = scales[0]; a.x = x_dev; a.y = y_dev;
+        a.acc_out = o.acc_out_dev; a.q_out = o.q_out_dev; a.a_scale_out = o.a_scale_out_dev;
+        a.M = M; a.K = K; a.N = N; a.ldy = ldy; a.flags = o.flags;
+        if (n_members > 1) {
+            a.n_seg = n_members - 1;
+            a.seg_end[0] = rows[0]; a.seg_scale[0] = scales[1];
+            if (n_members > 2) { a.seg_end[1] = rows[0] + rows[1]; a.seg_scale[1] = scales[2]; }
+        }
+        if (glue) a.pre = &pre;
+        BITNET_TRY(check_workspace(workspace_dev, workspace_bytes, midm_workspace_bytes(M, K)));
+        return launch_midm(a, workspace_dev, workspace_bytes, false, s);
+    }
+
     const size_t path_ws = path == BITNET_PATH_PREFILL ? prefill_workspace_bytes(M, K, N) : quant_workspace_bytes(M, K);
     BITNET_TRY(check_workspace(workspace_dev, workspace_bytes, path_ws + (glue ? glue_bytes(M, K) : 0)));
     char *ws = static_cast<char *>(workspace_dev);
@@ -317,7 +335,7 @@ extern "C" bitnet_status_t bitnet_bitlinear_forward(const uint8_t *weights_dev, 
     if (M == 0 || N == 0) return BITNET_OK;   // empty batch: nothing to do
     if (K == 0) return fail(BITNET_ERR_INCOMPATIBLE_SHAPES, "bitnet_bitlinear_forward: K == 0");
     if (!weights_dev || !x_dev || !y_dev) return fail(BITNET_ERR_NULL_POINTER, "bitnet_bitlinear_forward: null buffer");
-    if (o.path < BITNET_PATH_AUTO || o.path > BITNET_PATH_GENERIC) return fail(BITNET_ERR_INVALID_CONFIG, "unknown path %d", o.path);
+    if (o.path < BITNET_PATH_AUTO || o.path > BITNET_PATH_CLUSTER) return fail(BITNET_ERR_INVALID_CONFIG, "unknown path %d", o.path);
     const size_t rows[1] = {N};
     const float scales[1] = {w_scale};
     return forward_impl(weights_dev, rows, scales, 1, x_dev, RowPre{}, y_dev, M, K, N, o, workspace_dev, workspace_bytes,
@@ -344,7 +362,7 @@ extern "C" bitnet_status_t bitnet_bitlinear_forward_fused(const uint8_t *weights
     if (M == 0) return BITNET_OK;
     if (K == 0) return fail(BITNET_ERR_INCOMPATIBLE_SHAPES, "bitnet_bitlinear_forward_fused: K == 0");
     if (!weights_dev || !x_dev || !y_dev) return fail(BITNET_ERR_NULL_POINTER, "bitnet_bitlinear_forward_fused: null buffer");
-    if (o.path < BITNET_PATH_AUTO || o.path > BITNET_PATH_GENERIC) return fail(BITNET_ERR_INVALID_CONFIG, "unknown path %d", o.path);
+    if (o.path < BITNET_PATH_AUTO || o.path > BITNET_PATH_CLUSTER) return fail(BITNET_ERR_INVALID_CONFIG, "unknown path %d", o.path);
     const RowPre pre = to_row_pre(glue);
     if (pre.norm_w && !pre.norm_b) return fail(BITNET_ERR_NULL_POINTER, "normalisation needs weight and bias");
     return forward_impl(weights_dev, stack->rows, stack->scales, stack->n_members, x_dev, pre, y_dev, M, K, N, o, workspace_dev,
@@ -361,7 +379,9 @@ static size_t ffn_workspace(size_t M, size_t hidden, size_t ffn, int path, bool 
     const int p1 = resolve_path(path, M, hidden, ffn), p2 = resolve_path(path, M, ffn, hidden);
     const size_t w1 = forward_workspace(M, hidden, ffn, p1, false), w2 = forward_workspace(M, ffn, hidden, p2, false);
     size_t need = kAmaxBytes + (w1 > w2 ? w1 : w2);
-    if (p1 != BITNET_PATH_DECODE || !decode_supports_dual(M, hidden, ffn))
+    if (p1 == BITNET_PATH_CLUSTER && midm_can_run(M, hidden, ffn, true))
+        need += 0;   // the pair launch gates in its epilogue: no gate/up buffers, the glue rides in its quantiser
+    else if (p1 != BITNET_PATH_DECODE || !decode_supports_dual(M, hidden, ffn))
         need += 2 * ffn_pair_bytes(M, ffn) + (glue ? glue_bytes(M, hidden) : 0);
     else
         need += (glue ? decode_image_bytes_always(M, hidden, ffn, true) : decode_image_bytes(M, hidden, ffn, true)) +
@@ -374,7 +394,7 @@ extern "C" bitnet_status_t bitnet_ffn_workspace_size(size_t M, size_t hidden, si
     if (!bytes) return fail(BITNET_ERR_NULL_POINTER, "bitnet_ffn_workspace_size: null output");
     *bytes = 0;
     if (M == 0) return BITNET_OK;
-    if (path < BITNET_PATH_AUTO || path > BITNET_PATH_GENERIC) return fail(BITNET_ERR_INVALID_CONFIG, "unknown path %d", path);
+    if (path < BITNET_PATH_AUTO || path > BITNET_PATH_CLUSTER) return fail(BITNET_ERR_INVALID_CONFIG, "unknown path %d", path);
     *bytes = ffn_workspace(M, hidden, ffn, path, false);
     return BITNET_OK;
 }
@@ -384,7 +404,7 @@ extern "C" bitnet_status_t bitnet_ffn_fused_workspace_size(size_t M, size_t hidd
     if (!bytes) return fail(BITNET_ERR_NULL_POINTER, "bitnet_ffn_fused_workspace_size: null output");
     *bytes = 0;
     if (M == 0) return BITNET_OK;
-    if (path < BITNET_PATH_AUTO || path > BITNET_PATH_GENERIC) return fail(BITNET_ERR_INVALID_CONFIG, "unknown path %d", path);
+    if (path < BITNET_PATH_AUTO || path > BITNET_PATH_CLUSTER) return fail(BITNET_ERR_INVALID_CONFIG, "unknown path %d", path);
     *bytes = ffn_workspace(M, hidden, ffn, path, true);
     return BITNET_OK;
 }
@@ -400,7 +420,7 @@ static bitnet_status_t ffn_impl(const uint8_t *w_gate_dev, float s_gate, const u
         return fail(BITNET_ERR_NULL_POINTER, "%s: null buffer", who);
     if (o.q_out_dev || o.a_scale_out_dev || o.acc_out_dev || o.ldy)
         return fail(BITNET_ERR_INVALID_CONFIG, "%s: per-projection debug outputs are not available", who);
-    if (o.path < BITNET_PATH_AUTO || o.path > BITNET_PATH_GENERIC) return fail(BITNET_ERR_INVALID_CONFIG, "unknown path %d", o.path);
+    if (o.path < BITNET_PATH_AUTO || o.path > BITNET_PATH_CLUSTER) return fail(BITNET_ERR_INVALID_CONFIG, "unknown path %d", o.path);
     const bool glue = has_glue(pre);
     BITNET_TRY(check_workspace(workspace_dev, workspace_bytes, ffn_workspace(M, hidden, ffn, o.path, glue)));
     cudaStream_t s = as_stream(stream);
@@ -412,7 +432,14 @@ static bitnet_status_t ffn_impl(const uint8_t *w_gate_dev, float s_gate, const u
     const bool fused_pair = p1 == BITNET_PATH_DECODE && decode_supports_dual(M, hidden, ffn);
     // the gate/up launch leaves per-CTA absmax keys of h; the down launch folds them instead of re-reading h
     const bool chain_amax = fused_pair && p2 == BITNET_PATH_DECODE && decode_grid(ffn) <= 256;
-    if (fused_pair) {
+    if (p1 == BITNET_PATH_CLUSTER && midm_can_run(M, hidden, ffn, true)) {
+        // gate and up as the two halves of one cluster launch; its epilogue applies up * relu(gate)^2
+        ForwardArgs a = {};
+        a.wp = w_gate_dev; a.w_scale = s_gate; a.wp2 = w_up_dev; a.w_scale2 = s_up;
+        a.x = x_dev; a.y = h_dev; a.M = M; a.K = hidden; a.N = ffn; a.ldy = ffn; a.flags = o.flags;
+        if (glue) a.pre = &pre;
+        BITNET_TRY(launch_midm(a, ws + off, workspace_bytes - off, false, s));
+    } else if (fused_pair) {
         // gate and up stream through one launch; its epilogue applies up * relu(gate)^2
         ForwardArgs a = {};
         a.wp = w_gate_dev; a.w_scale = s_gate; a.wp2 = w_up_dev; a.w_scale2 = s_up;

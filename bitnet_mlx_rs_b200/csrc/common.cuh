@@ -42,6 +42,13 @@ struct RowPre {
     float *normed_out;       // [M,K]: receives the normalised fp32 row (parity tests)
 };
 
+// Row-major output of the activation quantiser for the tensor-core kernels.
+struct RowsOut {
+    int8_t *q_perm;   // [M,K] int8, every 16-wide k group transposed (byte 4j+i holds k = 4i+j)
+    int *rowsum;      // [M] sum_k q[m,k]
+    float *a_scale;   // [M] absmax / 127
+};
+
 // Launchers of the kernel families (defined next to their kernels).
 struct ForwardArgs {
     const uint8_t *wp;
@@ -98,7 +105,16 @@ size_t prefill_workspace_bytes(size_t M, size_t K, size_t N);
 bitnet_status_t launch_prefill(const ForwardArgs &a, void *workspace, size_t workspace_bytes, cudaStream_t stream);
 bitnet_status_t prefill_take_error_flags(unsigned *flags);
 
+// Cluster split-K tensor-core GEMM for a few dozen tokens (midm_gemm.cu).
+bool midm_supports(size_t M, size_t K, size_t N);
+bool midm_can_run(size_t M, size_t K, size_t N, bool pair);
+size_t midm_workspace_bytes(size_t M, size_t K);
+bitnet_status_t launch_midm(const ForwardArgs &a, void *workspace, size_t workspace_bytes, bool ready, cudaStream_t stream);
+bitnet_status_t midm_take_error_flags(unsigned *flags);
+
 int device_sm_count();
+bitnet_status_t launch_quantize_rows_glued(const float *x, size_t M, size_t K, const RowPre *pre, const RowsOut &rows,
+                                           int8_t *q_out, float *a_scale_out, uint32_t flags, cudaStream_t stream);
 
 // Stand-alone row glue (residual add and/or SubLN) for the paths whose quantiser does not take it:
 // writes x + residual to pre.sum_out and the normalised row to pre.normed_out.  K % 16 == 0, K <= 16384.

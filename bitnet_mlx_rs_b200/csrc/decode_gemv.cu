@@ -624,7 +624,7 @@ __global__ void __launch_bounds__(512) decode_quantize_kernel(const float *x, in
                                                               unsigned char *__restrict__ image,
                                                               const unsigned *__restrict__ amax_in, int n_amax_in,
                                                               int8_t *__restrict__ q_out, float *__restrict__ a_scale_out,
-                                                              const RowPre pre)
+                                                              const RowPre pre, const RowsOut rows)
 {
     __shared__ unsigned s_wkey[16];
     __shared__ int s_sum[DEC_MAX_CWARPS];
@@ -669,6 +669,7 @@ __global__ void __launch_bounds__(512) decode_quantize_kernel(const float *x, in
     const float scale = quant_scale(absmax);
     const bool fast = scale >= 1e-30f && scale <= 1e30f;
     const int C = K / 64;
+    int row_total = 0;
     const unsigned frag_blk = (unsigned)mrows * 64u;
     const unsigned region = (unsigned)sw * 4 * nt * frag_blk;
 
@@ -700,6 +701,11 @@ __global__ void __launch_bounds__(512) decode_quantize_kernel(const float *x, in
             int sum = 0;
 #pragma unroll
             for (int e = 0; e < 16; ++e) sum += q[e];
+            if (rows.q_perm) {   // row-major form for the tensor-core kernels: groups stay in row order
+                *reinterpret_cast<uint4 *>(rows.q_perm + (size_t)m * K + (size_t)G * 16) = frag;
+                row_total += sum;
+                continue;
+            }
             // which consumer warp owns this chunk, and where in its region the group goes
             const int chunk = G >> 2, i = G & 3;
             const int w = (int)((((long long)chunk + 1) * cw - 1) / C);
@@ -710,12 +716,52 @@ __global__ void __launch_bounds__(512) decode_quantize_kernel(const float *x, in
             if (sum) atomicAdd(&s_sum[w], sum);
         }
     }
+    if (rows.q_perm) {
+        row_total = __reduce_add_sync(0xffffffffu, row_total);
+        if ((tid & 31) == 0 && row_total) atomicAdd(&s_sum[0], row_total);
+    }
     __syncthreads();
+    if (rows.q_perm) {
+        if (tid == 0) {
+            rows.rowsum[m] = s_sum[0];
+            rows.a_scale[m] = dequant_scale(absmax);
+            if (a_scale_out) a_scale_out[m] = dequant_scale(absmax);
+        }
+        return;
+    }
     if (tid < cw) reinterpret_cast<int *>(image)[tid * DEC_MAX_TOKENS + m] = s_sum[tid];
     if (tid == 0) {
         reinterpret_cast<float *>(image + DEC_MAX_CWARPS * DEC_MAX_TOKENS * 4)[m] = dequant_scale(absmax);
         if (a_scale_out) a_scale_out[m] = dequant_scale(absmax);
     }
+}
+
+// The same quantiser writing the row-major form the tensor-core kernels read: int8 rows with every 16-wide
+// k group stored transposed (byte 4j+i holds k = 4i+j), the row sums and the scales.  K % 16 == 0, K <= 16384.
+bitnet_status_t launch_quantize_rows_glued(const float *x, size_t M, size_t K, const RowPre *pre, const RowsOut &rows,
+                                           int8_t *q_out, float *a_scale_out, uint32_t flags, cudaStream_t stream)
+{
+    if (M == 0) return BITNET_OK;
+    if (K == 0 || K % 16 || K > 16384) return fail(BITNET_ERR_UNSUPPORTED_OPERATION, "row quantiser needs K %% 16 == 0 and K <= 16384 (got %zu)", K);
+    auto mis = [](const void *ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) != 0; };
+    const RowPre rp = pre ? *pre : RowPre{};
+    if (mis(x) || mis(rows.q_perm) || mis(q_out) || mis(rp.residual) || mis(rp.sum_out) || mis(rp.norm_w) || mis(rp.norm_b) || mis(rp.normed_out))
+        return fail(BITNET_ERR_INVALID_CONFIG, "row quantiser buffers must be 16-byte aligned");
+    if (!rows.q_perm || !rows.rowsum || !rows.a_scale) return fail(BITNET_ERR_NULL_POINTER, "row quantiser: null output");
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attrs[1];
+    cfg.gridDim = dim3((unsigned)M);
+    cfg.blockDim = dim3(512);
+    cfg.stream = stream;
+    cfg.attrs = attrs;
+    if (flags & BITNET_FLAG_PDL) {
+        attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attrs[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.numAttrs = 1;
+    }
+    BITNET_CUDA(cudaLaunchKernelEx(&cfg, decode_quantize_kernel, x, (int)M, (int)K, 1, 1, 1, 1, static_cast<unsigned char *>(nullptr),
+                                   static_cast<const unsigned *>(nullptr), 0, q_out, a_scale_out, rp, rows));
+    return BITNET_OK;
 }
 
 // ---- launcher -----------------------------------------------------------------------------------------
@@ -989,7 +1035,7 @@ bitnet_status_t launch_decode(const ForwardArgs &a, cudaStream_t stream)
         if (!a.image_ready)
             BITNET_CUDA(cudaLaunchKernelEx(&cfg, decode_quantize_kernel, a.x, (int)a.M, (int)a.K, pl.cw, pl.sw, pl.nt, p.mrows,
                                            static_cast<unsigned char *>(a.image_ws), a.amax_in, a.n_amax_in, a.q_out,
-                                           a.a_scale_out, pre));
+                                           a.a_scale_out, pre, RowsOut{}));
         p.image = static_cast<const unsigned char *>(a.image_ws);
         p.q_out = nullptr; p.a_scale_out = nullptr; p.amax_in = nullptr;
         p.weights_first = 1;   // the image does not exist before the quantiser ends: fetch weights meanwhile
@@ -1013,8 +1059,9 @@ extern "C" bitnet_status_t bitnet_device_error_flags(uint32_t *flags_out)
     unsigned v = 0, zero = 0;
     BITNET_CUDA(cudaMemcpyFromSymbol(&v, bitnet::g_decode_error_flags, sizeof(v)));
     if (v) BITNET_CUDA(cudaMemcpyToSymbol(bitnet::g_decode_error_flags, &zero, sizeof(zero)));
-    unsigned pf = 0;
+    unsigned pf = 0, mm = 0;
     BITNET_TRY(bitnet::prefill_take_error_flags(&pf));
-    *flags_out = v | pf;
+    BITNET_TRY(bitnet::midm_take_error_flags(&mm));
+    *flags_out = v | pf | mm;
     return BITNET_OK;
 }

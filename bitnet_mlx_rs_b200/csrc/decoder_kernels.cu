@@ -196,7 +196,7 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
         for (int d = 0; d < DPL / 2; ++d) { kw[d] = kn[d]; vw[d] = vn[d]; }
     }
 
-    const int my_g = (lane >> SH) % G;           // the head whose running maximum and sum this lane keeps
+    // a lane keeps the running maximum and sum of the head (lane >> SH) % G
     float m_run = NEG_INF, l_run = 0.0f;
     float o[G][DPL];
 #pragma unroll

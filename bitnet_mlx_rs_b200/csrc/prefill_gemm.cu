@@ -925,6 +925,14 @@ static bitnet_status_t encode_map(CUtensorMap *map, const void *base, uint64_t i
     return BITNET_OK;
 }
 
+// The same encoder for the other tensor-core kernel of the library (uint8 elements).
+bitnet_status_t tensor_map_2d(void *map_out, const void *base, uint64_t inner, uint64_t rows, uint64_t row_stride_bytes,
+                              uint32_t box_inner, uint32_t box_rows, int swizzle_128b)
+{
+    return encode_map(static_cast<CUtensorMap *>(map_out), base, inner, rows, row_stride_bytes, box_inner, box_rows,
+                      swizzle_128b ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE);
+}
+
 bitnet_status_t launch_prefill(const ForwardArgs &a, void *workspace, size_t workspace_bytes, cudaStream_t stream)
 {
     if (!prefill_supports(a.M, a.K, a.N))

@@ -12,7 +12,8 @@ import torch
 from . import _lib as L
 from .cuda import IncompatibleShapes, InvalidConfig, UnsupportedDataType, check
 
-PATHS = {"auto": L.PATH_AUTO, "decode": L.PATH_DECODE, "prefill": L.PATH_PREFILL, "generic": L.PATH_GENERIC}
+PATHS = {"auto": L.PATH_AUTO, "decode": L.PATH_DECODE, "prefill": L.PATH_PREFILL, "generic": L.PATH_GENERIC,
+         "cluster": L.PATH_CLUSTER}
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
 
 

@@ -61,10 +61,11 @@ const char *bitnet_last_error_string(void);
 
 /* Which kernel family runs a forward call. */
 enum {
-    BITNET_PATH_AUTO = 0,    /* decode kernel for M <= 16, tensor-core GEMM for larger M */
+    BITNET_PATH_AUTO = 0,    /* decode kernel for M <= 16, cluster GEMM up to 128 tokens, persistent GEMM beyond */
     BITNET_PATH_DECODE = 1,  /* weight-streaming GEMV family, M <= 16, K % 64 == 0 */
     BITNET_PATH_PREFILL = 2, /* TMA + tcgen05 int8 GEMM, K % 128 == 0 */
-    BITNET_PATH_GENERIC = 3  /* any M, K, N (rows may start mid-byte); slow, exact */
+    BITNET_PATH_GENERIC = 3, /* any M, K, N (rows may start mid-byte); slow, exact */
+    BITNET_PATH_CLUSTER = 4  /* TMA + tcgen05 int8 GEMM with K split over a thread-block cluster, 1 <= M <= 128, K % 128 == 0 */
 };
 
 enum {
