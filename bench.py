@@ -64,6 +64,18 @@ def measured_peaks():
     return 6650.0, "fallback"
 
 
+def profiled_traffic():
+    """DRAM bytes per launch of the dominant kernel as the committed ncu summary records them (a line
+    `traffic_bytes_per_launch: N` in profiles/decode_kernel_ffn_gate_up_m1_ncu.md); (None, None) without it."""
+    import re
+    f = ROOT / "profiles" / "decode_kernel_ffn_gate_up_m1_ncu.md"
+    if f.exists():
+        m = re.search(r"traffic_bytes_per_launch\s*[:=]\s*(\d+)", f.read_text())
+        if m:
+            return int(m.group(1)), f"profiles/{f.name}"
+    return None, None
+
+
 class ClockSampler:
     """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
@@ -393,10 +405,21 @@ def run_cuda(args):
     extra = {}
     if rank == 0 and not args.no_extra:
         extra = single_kernel_figures(torch, ops, gen, peak)
+    # ---- the sharded configs: the oversized layer split over the ranks, the model's sequences row-sharded ----
+    del Wg, Wu, Wd, X, Y, Hb, dw
+    torch.cuda.empty_cache()
+    nsplit = model = None
+    if world > 1 and not args.no_extra:
+        barrier()
+        nsplit = nsplit_figures(torch, dist, ops, world, rank)
+    if not args.no_model:
+        barrier()
+        model = model_figures(torch, dist, local, world, peak, layers=args.model_layers or None)
 
+    traffic, traffic_source = profiled_traffic()
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
-        r = cpu_ffn_sample(steps=3, warmup=1)
+        r = cpu_ffn_sample(steps=max(args.steps, 1), warmup=max(args.warmup, 1))   # as many passes as the reference arm times
         cpu = {"value": r["value"], "unit": "GB/s", "cores": r["threads"], "kind": "port", "sample": r["sample"],
                "native_build": r["native"]}
 
@@ -411,10 +434,9 @@ def run_cuda(args):
                        "parallelism": f"row-sharded x{world}, weights replicated, no collective"},
             "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
                          "peak_kind": peak_kind,
-                         # dram__bytes_read.sum + dram__bytes_write.sum of one gate/up launch at M = 1 from an ncu
-                         # capture of the same kernel (summary under profiles/); its algorithmic
-                         # bytes are 8.89 MB, so nothing is read twice
-                         "traffic": 8923392,
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one gate/up launch at M = 1, read from the
+                         # committed ncu summary of that kernel (not measured by this run); algorithmic 8.89 MB
+                         "traffic": traffic, "traffic_source": traffic_source,
                          "kernel": "decode_kernel (gate/up pair and down launches; algorithmic bytes per launch "
                                    f"{step_bytes() / launches_per_step:.0f} on average); achieved = bytes of the whole "
                                    "step / CUDA-event time of the whole graph-replayed step (every launch in it is "
@@ -435,6 +457,10 @@ def run_cuda(args):
             line["cpu_baseline"] = cpu
         if extra:
             line["kernels"] = extra
+        if nsplit:
+            line["nsplit"] = nsplit
+        if model:
+            line["cfg4_model_decode"] = model
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -481,56 +507,6 @@ def single_kernel_figures(torch, ops, gen, peak):
         out[name] = {"us": us, "gbs": gbs, "frac_of_peak": gbs / peak, "weight_copies": copies, "launch": launch}
         del W
     out["cfg3_prefill_layer_m2048"] = prefill_layer_figures(torch, ops, gen)
-    out["cfg4_bitlinear_stack"] = decode_stack_figures(torch, ops, gen)
-    return out
-
-
-def decode_stack_figures(torch, ops, gen):
-    """BitLinear share of one decode step of the 2B architecture: 30 layers x (q 2560->2560, k and v
-    2560->640, o 2560->2560, FFN 2560->6912->2560) + the LM head 2560->128256, as ONE dependent chain
-    (CUDA graph, programmatic dependent launch) at M = sequences held by one GPU (64 sequences over
-    1/2/4/8 GPUs).  Attention, norms and sampling are not part of this path and not in the figure, so
-    tokens/s here is an upper bound for the full model's decode rate."""
-    H, F, V, L = HIDDEN, FFN, 128256, LAYERS
-    proj = [(H, H), (H, 640), (H, 640), (H, H)]
-    W = [[gen_packed_on_device(torch, n * k, gen) for (k, n) in proj] +
-         [gen_packed_on_device(torch, F * H, gen) for _ in range(3)] for _ in range(L)]
-    head = gen_packed_on_device(torch, V * H, gen)
-    out = {}
-    for M in (64, 32, 16, 8):
-        x = gen_activations_on_device(torch, (M, H), gen)
-        ys = [torch.empty((M, n), device="cuda") for (k, n) in proj]
-        yf, hf, logits = torch.empty((M, H), device="cuda"), torch.empty((M, F), device="cuda"), torch.empty((M, V), device="cuda")
-
-        def step():
-            for l in range(L):
-                for i, (k, n) in enumerate(proj):
-                    ops.bitlinear_forward(W[l][i], 0.01, x, n, out=ys[i], pdl=True)
-                ops.ffn_forward(W[l][4], 0.01, W[l][5], 0.01, W[l][6], 0.01, x, F, out=yf, h_out=hf, pdl=True)
-            ops.bitlinear_forward(head, 0.01, x, V, out=logits, pdl=True)
-
-        side = torch.cuda.Stream()
-        with torch.cuda.stream(side):
-            step()
-            torch.cuda.synchronize()
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=side):
-                step()
-        for _ in range(2):
-            g.replay()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        reps = 5
-        e0.record()
-        for _ in range(reps):
-            g.replay()
-        e1.record()
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / reps
-        nbytes = L * (sum(call_bytes(M, k, n) for (k, n) in proj) + ffn_bytes(M)) + call_bytes(M, H, V)
-        out[f"m{M}"] = {"ms_per_step": ms, "tokens_per_s_bitlinear_only": M / (ms * 1e-3), "gbs": nbytes / (ms * 1e-3) / 1e9,
-                        "sequences_per_gpu": M, "gpus_for_64_sequences": 64 // M}
-        del g
     return out
 
 
@@ -549,55 +525,175 @@ def model_step_bytes(seqs, context):
     return weights, kv
 
 
-def model_decode_figures(local, seqs, peak_gbs, context=MODEL_CONTEXT, new_tokens=MODEL_NEW_TOKENS, layers=None):
-    """Decode of the random-init 2B-shaped model (30 layers, hidden 2560, 20 heads / 5 KV heads, head_dim 128, FFN 6912,
-    vocabulary 128256, bf16 KV cache) for `seqs` sequences on this GPU: `context` random tokens are cached first (not
-    timed), then `new_tokens` tokens per sequence are generated greedily through bitnet_decoder_decode (host token ids in,
-    host token ids out: the wall time of that call is the figure).  Returns tokens/s of this GPU."""
-    import numpy as np
+class ModelBench:
+    """The random-init 2B-shaped model (30 layers, hidden 2560, 20 heads / 5 KV heads, head_dim 128, FFN 6912, vocabulary
+    128256, bf16 KV cache) on one GPU, built once; `run(seqs)` caches `context` random tokens per sequence (not timed),
+    then generates `new_tokens` tokens per sequence greedily through bitnet_decoder_decode -- host token ids in, host
+    token ids out: the wall time of that call is the figure."""
 
-    import oracle
-    from bitnet_mlx_rs_b200 import cuda
-    from bitnet_mlx_rs_b200.pipeline import ForwardPassConfig, ForwardPassPipeline, SamplingConfig
+    def __init__(self, local, max_seqs, context=MODEL_CONTEXT, new_tokens=MODEL_NEW_TOKENS, layers=None):
+        import numpy as np
 
-    cfgd = dict(MODEL)
-    if layers:
-        cfgd["num_layers"] = layers
-    cfg = ForwardPassConfig(max_seq_len=context + new_tokens, max_batch=seqs, **cfgd)
-    H, F, V = cfg.hidden_size, cfg.ffn_intermediate_size, cfg.vocab_size
-    qd, kd = cfg.num_heads * cfg.head_dim, cfg.num_kv_heads * cfg.head_dim
-    backend = cuda.CudaBackend(cuda.CudaBackendConfig(device_id=local, memory_pool_size=24 << 30))
-    pipe = ForwardPassPipeline(backend, cfg)
-    block = oracle.gen_activations(0, 7000, (8192, H))
-    pipe.load_embedding(np.tile(block, (V // 8192 + 1, 1))[:V])
-    ones, zeros = np.ones(H, np.float32), np.zeros(H, np.float32)
-    for l in range(cfg.num_layers):
-        shapes = {"q": (qd, H), "k": (kd, H), "v": (kd, H), "o": (H, qd), "gate": (F, H), "up": (F, H), "down": (H, F)}
-        lw = {}
-        for i, (name, (n, k)) in enumerate(shapes.items()):
-            lw[name] = oracle.gen_ternary_packed(0, 8000 + 10 * l + i, n * k)
-            lw["s_" + {"gate": "g", "up": "u", "down": "d"}.get(name, name)] = oracle.gen_weight_scale(0, 8000 + 10 * l + i, k)
-        lw.update(n1w=ones, n1b=zeros, n2w=ones, n2b=zeros)     # SubLNNormalization::new: ones and zeros
-        pipe.load_layer(l, lw)
-    pipe.load_lm_head(oracle.gen_ternary_packed(0, 8999, V * H), oracle.gen_weight_scale(0, 8999, H))
-    rng = np.random.default_rng(local)
-    ids = rng.integers(0, V, size=(seqs, context)).astype(np.int32)
-    pipe.reset()
-    pipe.feed(ids[:, :context - 1])
-    warm, _ = pipe.decode(ids[:, context - 1], 3, SamplingConfig(deterministic=True))     # records the step graph
-    t0 = time.perf_counter()
-    toks, steps = pipe.decode(warm[:, -1], new_tokens - 3, SamplingConfig(deterministic=True))
-    dt = time.perf_counter() - t0
-    assert steps == new_tokens - 3 and (toks >= 0).all() and (toks < V).all()
-    ms_step = dt * 1e3 / steps
-    weights, kv = model_step_bytes(seqs, context + new_tokens // 2)
-    pipe.close()
-    backend.close()
-    return {"sequences": seqs, "context": context, "new_tokens": steps, "ms_per_step": ms_step, "tokens_per_s": seqs * steps / dt,
-            "hbm_bytes_per_step": weights + kv, "gbs": (weights + kv) / (ms_step * 1e-3) / 1e9,
-            "frac_of_hbm_peak": (weights + kv) / (ms_step * 1e-3) / 1e9 / peak_gbs,
-            "roofline_ms_per_step": (weights + kv) / (peak_gbs * 1e9) * 1e3,
-            "io": "token ids host->device before, generated ids device->host after; sampling (argmax) on the device"}
+        import oracle
+        from bitnet_mlx_rs_b200 import cuda
+        from bitnet_mlx_rs_b200.pipeline import ForwardPassConfig, ForwardPassPipeline
+
+        self.local, self.context, self.new_tokens = local, context, new_tokens
+        cfgd = dict(MODEL)
+        if layers:
+            cfgd["num_layers"] = layers
+        cfg = self.cfg = ForwardPassConfig(max_seq_len=context + new_tokens, max_batch=max_seqs, **cfgd)
+        H, F, V = cfg.hidden_size, cfg.ffn_intermediate_size, cfg.vocab_size
+        qd, kd = cfg.num_heads * cfg.head_dim, cfg.num_kv_heads * cfg.head_dim
+        self.backend = cuda.CudaBackend(cuda.CudaBackendConfig(device_id=local, memory_pool_size=24 << 30))
+        self.pipe = pipe = ForwardPassPipeline(self.backend, cfg)
+        block = oracle.gen_activations(0, 7000, (8192, H))
+        pipe.load_embedding(np.tile(block, (V // 8192 + 1, 1))[:V])
+        ones, zeros = np.ones(H, np.float32), np.zeros(H, np.float32)
+        for l in range(cfg.num_layers):
+            shapes = {"q": (qd, H), "k": (kd, H), "v": (kd, H), "o": (H, qd), "gate": (F, H), "up": (F, H), "down": (H, F)}
+            lw = {}
+            for i, (name, (n, k)) in enumerate(shapes.items()):
+                lw[name] = oracle.gen_ternary_packed(0, 8000 + 10 * l + i, n * k)
+                lw["s_" + {"gate": "g", "up": "u", "down": "d"}.get(name, name)] = oracle.gen_weight_scale(0, 8000 + 10 * l + i, k)
+            lw.update(n1w=ones, n1b=zeros, n2w=ones, n2b=zeros)     # SubLNNormalization::new: ones and zeros
+            pipe.load_layer(l, lw)
+        pipe.load_lm_head(oracle.gen_ternary_packed(0, 8999, V * H), oracle.gen_weight_scale(0, 8999, H))
+
+    def run(self, seqs, peak_gbs):
+        import numpy as np
+
+        from bitnet_mlx_rs_b200.pipeline import SamplingConfig
+        V, context, new_tokens = self.cfg.vocab_size, self.context, self.new_tokens
+        rng = np.random.default_rng(self.local)
+        ids = rng.integers(0, V, size=(seqs, context)).astype(np.int32)
+        self.pipe.reset()
+        self.pipe.feed(ids[:, :context - 1])
+        warm, _ = self.pipe.decode(ids[:, context - 1], 3, SamplingConfig(deterministic=True))     # records the step graph
+        t0 = time.perf_counter()
+        toks, steps = self.pipe.decode(warm[:, -1], new_tokens - 3, SamplingConfig(deterministic=True))
+        dt = time.perf_counter() - t0
+        assert steps == new_tokens - 3 and (toks >= 0).all() and (toks < V).all()
+        ms_step = dt * 1e3 / steps
+        weights, kv = model_step_bytes(seqs, context + new_tokens // 2)
+        return {"sequences": seqs, "context": context, "new_tokens": steps, "ms_per_step": ms_step, "tokens_per_s": seqs * steps / dt,
+                "seconds": dt, "hbm_bytes_per_step": weights + kv, "gbs": (weights + kv) / (ms_step * 1e-3) / 1e9,
+                "frac_of_hbm_peak": (weights + kv) / (ms_step * 1e-3) / 1e9 / peak_gbs,
+                "roofline_ms_per_step": (weights + kv) / (peak_gbs * 1e9) * 1e3}
+
+    def close(self):
+        self.pipe.close()
+        self.backend.close()
+
+
+def model_figures(torch, dist, local, world, peak_gbs, layers=None):
+    """cfg4: 64 sequences with a 512-token context generating 128 tokens each.  weak = 64 sequences on EVERY GPU;
+    strong = the 64 sequences row-sharded over the GPUs (64 / N each), weights replicated, no collective.  Times are
+    the maximum over ranks; tokens/s are whole-job figures."""
+    bench = ModelBench(local, MODEL_SEQUENCES, layers=layers)
+    full = bench.run(MODEL_SEQUENCES, peak_gbs)
+    share = full if world == 1 else bench.run(max(1, MODEL_SEQUENCES // world), peak_gbs)
+    bench.close()
+
+    def slowest(seconds):
+        t = torch.tensor([seconds], device="cuda", dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    t_full, t_share = slowest(full["seconds"]), slowest(share["seconds"])
+    steps = full["new_tokens"]
+    w, kv = model_step_bytes(MODEL_SEQUENCES, MODEL_CONTEXT + MODEL_NEW_TOKENS // 2)
+    out = {"model": "random-init BitNet b1.58 2B shape: 30 layers, hidden 2560, 20 heads / 5 KV heads, head_dim 128, FFN 6912, "
+                    "vocabulary 128256, bf16 KV cache; LM head as a BitLinear; greedy sampling on the device",
+           "io": "token ids host->device before the call, generated ids device->host after it (bitnet_decoder_decode)",
+           "weak": {"sequences_per_gpu": MODEL_SEQUENCES, "tokens_per_s": world * MODEL_SEQUENCES * steps / t_full,
+                    "ms_per_step": t_full * 1e3 / steps, "frac_of_hbm_roofline": full["roofline_ms_per_step"] / (t_full * 1e3 / steps)},
+           "strong": {"sequences_total": MODEL_SEQUENCES, "sequences_per_gpu": share["sequences"],
+                      "tokens_per_s": world * share["sequences"] * steps / t_share, "ms_per_step": t_share * 1e3 / steps,
+                      "speedup_vs_one_gpu": t_full / t_share,
+                      "roofline_predicted_speedup": (w + kv) / (w + kv / world),
+                      "frac_of_hbm_roofline": share["roofline_ms_per_step"] / (t_share * 1e3 / steps)}}
+    return out
+
+
+def nsplit_figures(torch, dist, ops, world, rank):
+    """cfg5: the oversized layer K = 8192, N = 28672 at M in {1, 16, 256}, output features split over the ranks.  Two forms:
+    every rank computes its column slice and the fp32 slices are all-gathered with NCCL; or (decode shapes) every rank's
+    kernel stores its slice straight into every GPU's output over NVLink and a barrier replaces the collective.  Before
+    any timing each form's result is compared bit for bit with the single-GPU result of the same layer on this rank.
+    Times: CUDA events, graph replay where it captures, maximum over ranks."""
+    from bitnet_mlx_rs_b200 import parallel
+    K, N = 8192, 28672
+    n_local = N // world
+    gen = torch.Generator(device="cuda").manual_seed(7)   # the same weights on every rank; each keeps its slice
+    copies = max(2, -(-(160 << 20) // (n_local * K // 4)))   # rotate enough slices to exceed L2
+    layers, fused, full0 = [], [], None
+    for c in range(copies):
+        full = gen_packed_on_device(torch, N * K, gen)
+        layers.append(parallel.NSplitBitLinear(full, 0.01, N, K))
+        fused.append(parallel.FusedNSplitBitLinear(full, 0.01, N, K))
+        if c == 0:
+            full0 = full
+        del full
+    out = {"layer": "K=8192 -> N=28672, N-split over %d GPUs (%d columns each)" % (world, n_local), "weight_copies_rotated": copies}
+
+    def timed(fn, reps):
+        for _ in range(2):
+            fn()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / reps], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) * 1e3
+
+    def graphed(body):
+        """`body` replayed as one CUDA graph when it captures (launch overhead off the clock), else as it is."""
+        try:
+            side = torch.cuda.Stream()
+            with torch.cuda.stream(side):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    body()
+            g.replay()
+            torch.cuda.synchronize()
+            return g.replay, "cuda graph"
+        except Exception as ex:   # capture is an optimisation of the measurement, not of the result
+            print(f"N-split: graph capture failed ({type(ex).__name__}); timing eager launches", file=sys.stderr)
+            torch.cuda.synchronize()
+            return body, "eager"
+
+    for M in (1, 16, 256):
+        x = gen_activations_on_device(torch, (M, K), gen)
+        y_one = ops.bitlinear_forward(full0, 0.01, x, N)          # the whole layer on this GPU alone
+        y_ag = layers[0].forward(x)
+        same_ag = bool(torch.equal(y_ag, y_one))
+        same_fused = None
+        if M <= 16:
+            y_f = fused[0].forward(x).clone()
+            same_fused = bool(torch.equal(y_f, y_one))
+        flags = torch.tensor([int(same_ag), int(same_fused is not False)], device="cuda")
+        dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+        entry = {"equals_single_gpu": bool(flags[0].item()) and bool(flags[1].item()),
+                 "allgather_bytes_per_gpu": 4 * M * N * (world - 1) // world}
+        y_buf = torch.empty((M, N), device="cuda")
+        run1, mode1 = graphed(lambda: ops.bitlinear_forward(full0, 0.01, x, N, out=y_buf, pdl=True))
+        entry["us_one_gpu"] = timed(run1, 20)
+        entry["us_allgather"] = timed(lambda: [layers[i].forward(x) for i in range(copies)], 4) / copies
+        if M <= 16:
+            runf, modef = graphed(lambda: [fused[i].forward(x) for i in range(copies)])
+            entry["us_fused"] = timed(runf, 4) / copies
+            entry["fused_launch"] = modef
+        else:
+            entry["us_fused"] = None
+        out[f"m{M}"] = entry
+    return out
 
 
 def prefill_layer_figures(torch, ops, gen):
@@ -670,7 +766,17 @@ def run_case(spec):
     torch.cuda.set_device(0)
     gen = torch.Generator(device="cuda").manual_seed(0)
     x = gen_activations_on_device(torch, (M, K), gen)
-    if kind == "ffn":
+    if kind == "attn":
+        # decode attention of the 2B shape: M sequences, K cached tokens each, bf16 cache, rotating `copies` caches
+        nh, nkv, hd = MODEL["num_heads"], MODEL["num_kv_heads"], MODEL["head_dim"]
+        caches = [(torch.randn((M, nkv, K + 8, hd), device="cuda", generator=gen).to(torch.bfloat16),
+                   torch.randn((M, nkv, K + 8, hd), device="cuda", generator=gen).to(torch.bfloat16)) for _ in range(copies)]
+        qkv = torch.randn((M, (nh + 2 * nkv) * hd), device="cuda", generator=gen)
+        pos = torch.full((M,), K, dtype=torch.int32, device="cuda")
+        call = lambda i: ops.attention_decode(qkv, caches[i][0], caches[i][1], pos, nh, nkv, hd)   # noqa: E731
+        nbytes = 2 * M * nkv * (K + 1) * hd * 2
+        int_ops = 4.0 * M * nh * (K + 1) * hd
+    elif kind == "ffn":
         W = [tuple(gen_packed_on_device(torch, K * N, gen) for _ in range(3)) for _ in range(copies)]
         y, h = torch.empty((M, K), device="cuda"), torch.empty((M, N), device="cuda")
         call = lambda i: ops.ffn_forward(W[i][0], 0.02, W[i][1], 0.02, W[i][2], 0.02, x, N, out=y, h_out=h, pdl=True)   # noqa: E731
@@ -725,6 +831,7 @@ def main():
     ap.add_argument("--streams", type=int, default=8, help="streams the step's independent FFN blocks are dealt to (1 = one chain)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-extra", action="store_true", help="skip the single-kernel figures")
+    ap.add_argument("--no-model", action="store_true", help="skip the model decode figure (cfg4)")
     ap.add_argument("--case", default="", metavar="kind:M:K:N[:copies[:iters]]",
                     help="time one BitLinear/FFN shape on GPU 0 and print it (the workload of the profiling commands)")
     ap.add_argument("--model-only", type=int, default=0, metavar="SEQS",
@@ -734,7 +841,9 @@ def main():
     if args.case:
         run_case(args.case)
     elif args.model_only:
-        print(json.dumps(model_decode_figures(0, args.model_only, measured_peaks()[0], layers=args.model_layers or None)))
+        mb = ModelBench(0, args.model_only, layers=args.model_layers or None)
+        print(json.dumps(mb.run(args.model_only, measured_peaks()[0])))
+        mb.close()
     elif args.impl == "reference":
         run_reference(args)
     else:

@@ -204,18 +204,20 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
 #pragma unroll
         for (int d = 0; d < DPL; ++d) o[g][d] = 0.0f;
 
-    for (int base = p0 + warp * NB; base < p1; base += 4 * NB) {
-        unsigned kraw[NB][DPL / 2], vraw[NB][DPL / 2];
+    // rows of NB positions: loaded one batch ahead of the arithmetic, so that a warp always has loads in flight
+    auto load_batch = [&](unsigned (&kraw)[NB][DPL / 2], unsigned (&vraw)[NB][DPL / 2], int base) {
 #pragma unroll
         for (int j = 0; j < NB; ++j) {
             const int pos = base + j;
             const bool cached = pos < p1 && pos != L - 1;
 #pragma unroll
             for (int d = 0; d < DPL / 2; ++d) {
-                kraw[j][d] = cached ? __ldg(kc + (size_t)pos * (HD / 2) + d) : (pos == L - 1 ? kn[d] : 0u);
-                vraw[j][d] = cached ? __ldg(vc + (size_t)pos * (HD / 2) + d) : (pos == L - 1 ? vn[d] : 0u);
+                kraw[j][d] = cached ? __ldcs(kc + (size_t)pos * (HD / 2) + d) : (pos == L - 1 ? kn[d] : 0u);
+                vraw[j][d] = cached ? __ldcs(vc + (size_t)pos * (HD / 2) + d) : (pos == L - 1 ? vn[d] : 0u);
             }
         }
+    };
+    auto process_batch = [&](const unsigned (&kraw)[NB][DPL / 2], const unsigned (&vraw)[NB][DPL / 2], int base) {
         float part[NV];
 #pragma unroll
         for (int j = 0; j < NB; ++j) {
@@ -268,6 +270,25 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
             }
         }
         __syncwarp();
+    };
+    {
+        unsigned k0[NB][DPL / 2], v0[NB][DPL / 2], k1[NB][DPL / 2], v1[NB][DPL / 2];
+        int base = p0 + warp * NB;
+        if (base < p1) {
+            load_batch(k0, v0, base);
+            while (true) {
+                int next = base + 4 * NB;
+                if (next < p1) load_batch(k1, v1, next);
+                process_batch(k0, v0, base);
+                base = next;
+                if (base >= p1) break;
+                next = base + 4 * NB;
+                if (next < p1) load_batch(k0, v0, next);
+                process_batch(k1, v1, base);
+                base = next;
+                if (base >= p1) break;
+            }
+        }
     }
 
     // the four warps' partial results meet in shared memory
@@ -313,19 +334,46 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
     __syncthreads();
     if (!s_last) return;
     __threadfence();
+    // the last CTA to arrive folds the splits: all maxima and sums first (one load per thread, all in flight at
+    // once), a weight per split and head, then the weighted partial outputs
+    float *s_w = &s_o[0][0][0];                 // [G][32] weights, then [G] sums: the warps' outputs are consumed
+    float *s_lsum = s_w + G * 32;
+    __syncthreads();
+    for (int i = tid; i < G * p.n_splits; i += 128) {
+        const int g = i / p.n_splits, s2 = i - g * p.n_splits;
+        const size_t slot = ((size_t)b * p.n_heads + h0 + g) * p.n_splits + s2;
+        s_w[g * 32 + s2] = __ldcg(p.part_ml + slot * 2);
+        s_w[G * 32 + G + g * 32 + s2] = __ldcg(p.part_ml + slot * 2 + 1);
+    }
+    __syncthreads();
+    if (tid < G) {
+        float mx = NEG_INF;
+        for (int s2 = 0; s2 < p.n_splits; ++s2) mx = fmaxf(mx, s_w[tid * 32 + s2]);
+        float l = 0.0f;
+        for (int s2 = 0; s2 < p.n_splits; ++s2) {
+            const float ms = s_w[tid * 32 + s2];
+            const float f = ms > NEG_INF ? expf(ms - mx) : 0.0f;
+            l += s_w[G * 32 + G + tid * 32 + s2] * f;
+            s_w[tid * 32 + s2] = f;
+        }
+        s_lsum[tid] = l;
+    }
+    __syncthreads();
     for (int e = tid; e < G * HD; e += 128) {
         const int g = e / HD, d = e - g * HD;
         const size_t slot0 = ((size_t)b * p.n_heads + h0 + g) * p.n_splits;
-        float mx = NEG_INF;
-        for (int s2 = 0; s2 < p.n_splits; ++s2) mx = fmaxf(mx, __ldcg(p.part_ml + (slot0 + s2) * 2));
-        float l = 0.0f, acc = 0.0f;
-        for (int s2 = 0; s2 < p.n_splits; ++s2) {
-            const float ms = __ldcg(p.part_ml + (slot0 + s2) * 2);
-            const float f = ms > NEG_INF ? expf(ms - mx) : 0.0f;
-            l += __ldcg(p.part_ml + (slot0 + s2) * 2 + 1) * f;
-            acc += __ldcg(p.part_o + (slot0 + s2) * HD + d) * f;
+        float acc = 0.0f;
+        int s2 = 0;
+        for (; s2 + 4 <= p.n_splits; s2 += 4) {
+            const float v0 = __ldcg(p.part_o + (slot0 + s2) * HD + d), v1 = __ldcg(p.part_o + (slot0 + s2 + 1) * HD + d);
+            const float v2 = __ldcg(p.part_o + (slot0 + s2 + 2) * HD + d), v3 = __ldcg(p.part_o + (slot0 + s2 + 3) * HD + d);
+            acc += v0 * s_w[g * 32 + s2];
+            acc += v1 * s_w[g * 32 + s2 + 1];
+            acc += v2 * s_w[g * 32 + s2 + 2];
+            acc += v3 * s_w[g * 32 + s2 + 3];
         }
-        p.out[(size_t)b * p.n_heads * HD + (size_t)(h0 + g) * HD + d] = acc / l;
+        for (; s2 < p.n_splits; ++s2) acc += __ldcg(p.part_o + (slot0 + s2) * HD + d) * s_w[g * 32 + s2];
+        p.out[(size_t)b * p.n_heads * HD + (size_t)(h0 + g) * HD + d] = acc / s_lsum[g];
     }
     if (tid == 0) p.counters[b * p.n_kv + kvh] = 0u;   // ready for the next launch
 }
@@ -336,11 +384,12 @@ size_t attention_scratch_bytes(size_t B, size_t n_heads, size_t n_kv, size_t hea
     return align_up(B * n_heads * n_splits * head_dim * 4, 256) + align_up(B * n_heads * n_splits * 8, 256) + align_up(B * n_kv * 4, 256);
 }
 
-// Splits per (sequence, KV head): enough CTAs for two per SM, at least 64 keys per split at the longest context.
+// Splits per (sequence, KV head): enough CTAs for four per SM (sixteen warps with loads in flight), at least 64 keys
+// per split at the longest context.
 int attention_splits(size_t B, size_t n_kv, size_t max_context)
 {
     const size_t pairs = B * n_kv;
-    size_t want = (2 * (size_t)device_sm_count() + pairs - 1) / pairs;
+    size_t want = (4 * (size_t)device_sm_count() + pairs - 1) / pairs;
     const size_t by_len = max_context / 64 > 0 ? max_context / 64 : 1;
     if (want > by_len) want = by_len;
     if (want > 32) want = 32;

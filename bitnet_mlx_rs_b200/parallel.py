@@ -117,103 +117,3 @@ def row_sharded_forward(forward: Callable[[torch.Tensor], torch.Tensor], x_all: 
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     b, e = shard_range(x_all.shape[0], world, rank)
     return forward(x_all[b:e].contiguous())
-
-
-def _bench_nsplit() -> None:
-    """Times the output-feature-split oversized layer (K = 8192, N = 28672, M in {1, 16, 256}) on the
-    ranks of this job: local column slice + all-gather, CUDA events, maximum over ranks.  Run as
-
-        python -m torch.distributed.run --nnodes=1 --nproc-per-node G --master-addr 127.0.0.1 \\
-            -m bitnet_mlx_rs_b200.parallel
-
-    Rank 0 prints one JSON line per token count."""
-    import json
-    import os
-
-    from . import ops
-
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    world, rank = dist.get_world_size(), dist.get_rank()
-    K, N = 8192, 28672
-    n_local = N // world
-    gen = torch.Generator(device="cuda").manual_seed(7)   # same weights on every rank; each keeps its slice
-    copies = max(2, -(-(160 << 20) // (n_local * K // 4)))   # rotate enough slices to exceed L2
-    layers, fulls = [], []
-    for _ in range(copies):
-        full = torch.randint(0, 256, (N * K // 4,), dtype=torch.uint8, device="cuda", generator=gen)
-        ops.sanitize_packed(full)
-        layers.append(NSplitBitLinear(full, 0.01, N, K))
-        fulls.append(full)
-    fused = [FusedNSplitBitLinear(l_full, 0.01, N, K) for l_full in fulls]
-    del fulls
-    for M in (1, 16, 256):
-        x = torch.randn((M, K), device="cuda", generator=gen)
-        if M <= 16:   # the same layer with the slices stored straight into every GPU's output
-            for i in range(3):
-                yf = fused[i % copies].forward(x)
-            same = bool(torch.equal(yf, layers[(3 - 1) % copies].forward(x)))
-            dist.barrier()
-            torch.cuda.synchronize()
-            f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            f0.record()
-            for i in range(4 * copies):
-                yf = fused[i % copies].forward(x)
-            f1.record()
-            torch.cuda.synchronize()
-            tf = torch.tensor([f0.elapsed_time(f1) / (4 * copies)], device="cuda")
-            dist.all_reduce(tf, op=dist.ReduceOp.MAX)
-            line = {"workload": "N-split BitLinear 8192->28672, slices stored into peer outputs (no collective)",
-                    "n_gpus": world, "M": M, "us_per_call": round(float(tf.item()) * 1e3, 2),
-                    "equals_allgather_result": same, "launch": "eager"}
-            try:   # the same calls replayed as one CUDA graph (launch overhead off the critical path)
-                side = torch.cuda.Stream()
-                with torch.cuda.stream(side):
-                    graph = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(graph, stream=side):
-                        for i in range(copies):
-                            yf = fused[i].forward(x)
-                for _ in range(2):
-                    graph.replay()
-                dist.barrier()
-                torch.cuda.synchronize()
-                f0.record()
-                for _ in range(4):
-                    graph.replay()
-                f1.record()
-                torch.cuda.synchronize()
-                tg = torch.tensor([f0.elapsed_time(f1) / (4 * copies)], device="cuda")
-                dist.all_reduce(tg, op=dist.ReduceOp.MAX)
-                line["us_per_call_graph"] = round(float(tg.item()) * 1e3, 2)
-                line["algorithmic_gbs_whole_job_graph"] = round((N * K // 4 + 4 * M * K + 4 * M * N) / (float(tg.item()) * 1e3) / 1e3, 1)
-            except Exception as ex:   # capture is an optimisation of the measurement, not of the result
-                line["graph"] = f"not captured: {type(ex).__name__}"
-                torch.cuda.synchronize()
-            if rank == 0:
-                print(json.dumps(line))
-        for i in range(3):
-            y = layers[i % copies].forward(x)
-        dist.barrier()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        iters = 4 * copies
-        e0.record()
-        for i in range(iters):
-            y = layers[i % copies].forward(x)
-        e1.record()
-        torch.cuda.synchronize()
-        t = torch.tensor([e0.elapsed_time(e1) / iters], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        us = float(t.item()) * 1e3
-        nbytes = N * K // 4 + 4 * M * K + 4 * M * N
-        if rank == 0:
-            print(json.dumps({"workload": "N-split BitLinear 8192->28672 + all-gather", "n_gpus": world, "M": M,
-                              "us_per_call": round(us, 2), "algorithmic_gbs_whole_job": round(nbytes / us / 1e3, 1),
-                              "int_tops": round(2.0 * M * K * N / us / 1e6, 1), "allgather_bytes_per_gpu": 4 * M * N * (world - 1) // world,
-                              "launch": "eager", "checksum": float(y.double().sum().item())}))
-    dist.destroy_process_group()
-
-
-if __name__ == "__main__":
-    _bench_nsplit()

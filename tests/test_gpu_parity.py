@@ -332,7 +332,7 @@ def test_backend_host_ffn():
 
 # ---- full-size properties -------------------------------------------------------------------------------------
 
-@pytest.mark.parametrize("M", [1, 16])
+@pytest.mark.parametrize("M", [1, 16, 64, 256])
 def test_oversized_layer_checksum_and_row_samples(M):
     # K=8192, N=28672 is too large for the oracle in seconds: check a size-independent identity
     # (sum_n acc[m,n] == q[m,:] . colsum(W)) with torch integer ops, and compare sampled row
