@@ -117,6 +117,10 @@ SIGNATURES = {
     "bitnet_backend_w2a8_gemv": (i32, [vp, vp, sz, vp, sz, vp, sz, sz, sz, sz]),
     "bitnet_backend_upload_packed": (i32, [vp, vp, sz, sz, f32, _P(vp)]),
     "bitnet_backend_upload_ternary": (i32, [vp, vp, sz, sz, f32, _P(vp)]),
+    "bitnet_backend_upload_f32": (i32, [vp, vp, sz, sz, _P(vp)]),
+    "bitnet_backend_upload_gguf_ternary": (i32, [vp, vp, sz, sz, sz, _P(f32), _P(vp)]),
+    "bitnet_quantize_pack_weights": (i32, [vp, sz, vp, vp, vp, sz, vp]),
+    "bitnet_quantize_pack_weights_workspace_size": (i32, [sz, _P(sz)]),
     "bitnet_backend_free_weights": (i32, [vp, vp]),
     "bitnet_weights_info": (i32, [vp, _P(sz), _P(sz), _P(f32), _P(vp)]),
     "bitnet_backend_bitlinear_forward": (i32, [vp, vp, vp, vp, sz, _P(ForwardOpts), sz]),
@@ -146,6 +150,11 @@ SIGNATURES = {
     "bitnet_decoder_decode": (i32, [vp, vp, sz, sz, _P(SamplingConfig), i32, vp, _P(sz)]),
     "bitnet_decoder_generate": (i32, [vp, vp, sz, sz, sz, _P(SamplingConfig), i32, vp, _P(sz)]),
     "bitnet_decoder_read": (i32, [vp, i32, vp, sz]),
+    "bitnet_allgather_output": (i32, [vp, sz, sz, sz, _P(vp), i32, sz, vp]),
+    "bitnet_nccl_unique_id": (i32, [vp]),
+    "bitnet_nccl_comm_create": (i32, [vp, i32, i32, _P(vp)]),
+    "bitnet_nccl_comm_destroy": (i32, [vp]),
+    "bitnet_allgather_output_nccl": (i32, [vp, vp, sz, sz, vp, vp, i32, sz, vp]),
     "bitnet_backend_pin_host": (i32, [vp, vp, sz]),
     "bitnet_backend_unpin_host": (i32, [vp, vp]),
     "bitnet_backend_ffn_plan_create": (i32, [vp, _P(FfnCall), sz, _P(ForwardOpts), sz, _P(vp)]),

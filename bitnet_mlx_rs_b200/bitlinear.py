@@ -86,9 +86,8 @@ class BitLinear:
             self.cache_hits += 1
             return self._packed
         self.cache_misses += 1
-        qw = absmean_quantize_weights(self._weights)
-        t = torch.from_numpy(qw.values).to(self.device)
-        self._packed = (ops.pack_ternary(t), qw.scale)
+        # absmean quantisation and packing on the device (weights.rs:807-857, packing.rs:352-388)
+        self._packed = ops.quantize_pack_weights(self._weights.to(self.device))
         return self._packed
 
     # layer.rs:299-326

@@ -17,7 +17,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 OBJ = PKG / "build"
 LIB = PKG / "libbitnet_cuda_kernels.so"
-SOURCES = ["abi.cu", "backend.cu", "quant_kernels.cu", "generic_gemm.cu", "decode_gemv.cu", "prefill_gemm.cu", "midm_gemm.cu", "noalloc.cu", "decoder_kernels.cu", "decoder.cu"]
+SOURCES = ["abi.cu", "backend.cu", "quant_kernels.cu", "generic_gemm.cu", "decode_gemv.cu", "prefill_gemm.cu", "midm_gemm.cu", "noalloc.cu", "decoder_kernels.cu", "decoder.cu", "weights_kernels.cu", "collective.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -72,7 +72,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         objs = list(pool.map(compile_one, _sources()))
     if force or _stale(LIB, objs):
         cmd = [nvcc, "-shared", *extra, "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(LIB),
-               *map(str, objs)]
+               *map(str, objs), "-ldl"]
         r = subprocess.run(cmd, capture_output=True, text=True, env=env)
         if r.returncode != 0:
             sys.stderr.write(r.stdout + r.stderr)

@@ -366,9 +366,12 @@ extern "C" bitnet_status_t bitnet_backend_w2a8_gemv(bitnet_backend *b, const uin
     return BITNET_OK;
 }
 
-static bitnet_status_t upload_common(bitnet_backend *b, const void *host, bool is_ternary, size_t N, size_t K,
+enum UploadKind { UPLOAD_PACKED, UPLOAD_TERNARY, UPLOAD_F32 };
+
+static bitnet_status_t upload_common(bitnet_backend *b, const void *host, UploadKind kind, size_t N, size_t K,
                                      float w_scale, bitnet_weights **out)
 {
+    const bool is_ternary = kind == UPLOAD_TERNARY;
     if (!b || !out) return fail(BITNET_ERR_NULL_POINTER, "upload: null argument");
     *out = nullptr;
     if (!host) return fail(BITNET_ERR_NULL_POINTER, "upload: null host buffer");
@@ -384,6 +387,19 @@ static bitnet_status_t upload_common(bitnet_backend *b, const void *host, bool i
             st = b->impl.memory->allocate(n_values, &tmp);
             if (st == BITNET_OK) st = check_cuda(cudaMemcpyAsync(tmp, host, n_values, cudaMemcpyHostToDevice, s), "upload ternary");
             if (st == BITNET_OK) st = bitnet_pack_ternary(static_cast<const int8_t *>(tmp), n_values, static_cast<uint8_t *>(packed), s);
+        } else if (kind == UPLOAD_F32) {
+            // full-precision weights: absmean quantisation and packing on the device; the scale comes back with the counter
+            size_t wsb = 0;
+            bitnet_quantize_pack_weights_workspace_size(n_values, &wsb);
+            void *qws = nullptr;
+            st = b->impl.memory->allocate(n_values * sizeof(float), &tmp);
+            if (st == BITNET_OK) st = b->impl.memory->allocate(wsb, &qws);
+            if (st == BITNET_OK) st = check_cuda(cudaMemcpyAsync(tmp, host, n_values * sizeof(float), cudaMemcpyHostToDevice, s), "upload fp32 weights");
+            float *scale_dev = reinterpret_cast<float *>(static_cast<char *>(counter) + 128);
+            if (st == BITNET_OK) st = bitnet_quantize_pack_weights(static_cast<const float *>(tmp), n_values, static_cast<uint8_t *>(packed), scale_dev, qws, wsb, s);
+            if (st == BITNET_OK) st = check_cuda(cudaMemcpyAsync(&w_scale, scale_dev, sizeof(float), cudaMemcpyDeviceToHost, s), "read weight scale");
+            if (st == BITNET_OK) st = check_cuda(cudaStreamSynchronize(s), "quantise sync");
+            if (qws) b->impl.memory->release(qws);
         } else {
             st = check_cuda(cudaMemcpyAsync(packed, host, n_bytes, cudaMemcpyHostToDevice, s), "upload packed");
         }
@@ -418,13 +434,39 @@ static bitnet_status_t upload_common(bitnet_backend *b, const void *host, bool i
 extern "C" bitnet_status_t bitnet_backend_upload_packed(bitnet_backend *b, const uint8_t *packed_host, size_t N,
                                                         size_t K, float w_scale, bitnet_weights **out)
 {
-    return upload_common(b, packed_host, false, N, K, w_scale, out);
+    return upload_common(b, packed_host, UPLOAD_PACKED, N, K, w_scale, out);
+}
+
+extern "C" bitnet_status_t bitnet_backend_upload_f32(bitnet_backend *b, const float *weights_host, size_t N, size_t K,
+                                                     bitnet_weights **out)
+{
+    return upload_common(b, weights_host, UPLOAD_F32, N, K, 1.0f, out);
+}
+
+// A ternary tensor as GgufLoader::decode_ternary_weights reads it (bitnet-inference/src/gguf.rs:1089-1165): eight bytes of
+// metadata (f32 scale, f32 offset, little endian), then the 2-bit codes in the layout the kernels consume; the payload goes
+// to the device as it is (code 3 becomes weight 0 there, as in the reference's decoder).
+extern "C" bitnet_status_t bitnet_backend_upload_gguf_ternary(bitnet_backend *b, const uint8_t *tensor_host, size_t tensor_bytes,
+                                                              size_t N, size_t K, float *offset_out, bitnet_weights **out)
+{
+    if (!tensor_host) return fail(BITNET_ERR_NULL_POINTER, "upload: null host buffer");
+    const size_t payload = (N * K + 3) / 4;
+    if (tensor_bytes < payload + 8)
+        return fail(BITNET_ERR_INCOMPATIBLE_SHAPES, "Insufficient packed data for tensor: got %zu bytes, expected at least %zu",
+                    tensor_bytes, payload + 8);
+    float scale = 1.0f, offset = 0.0f;
+    unsigned su = (unsigned)tensor_host[0] | ((unsigned)tensor_host[1] << 8) | ((unsigned)tensor_host[2] << 16) | ((unsigned)tensor_host[3] << 24);
+    unsigned ou = (unsigned)tensor_host[4] | ((unsigned)tensor_host[5] << 8) | ((unsigned)tensor_host[6] << 16) | ((unsigned)tensor_host[7] << 24);
+    memcpy(&scale, &su, 4);
+    memcpy(&offset, &ou, 4);
+    if (offset_out) *offset_out = offset;
+    return upload_common(b, tensor_host + 8, UPLOAD_PACKED, N, K, scale, out);
 }
 
 extern "C" bitnet_status_t bitnet_backend_upload_ternary(bitnet_backend *b, const int8_t *ternary_host, size_t N,
                                                          size_t K, float w_scale, bitnet_weights **out)
 {
-    return upload_common(b, ternary_host, true, N, K, w_scale, out);
+    return upload_common(b, ternary_host, UPLOAD_TERNARY, N, K, w_scale, out);
 }
 
 extern "C" bitnet_status_t bitnet_backend_free_weights(bitnet_backend *b, bitnet_weights *w)

@@ -255,6 +255,25 @@ class CudaBackend:
         check(L.load().bitnet_backend_upload_ternary(self._h, t.ctypes.data, t.shape[0], t.shape[1], scale, C.byref(out)))
         return DeviceWeights(self, out.value)
 
+    def upload_f32(self, weights_host) -> DeviceWeights:
+        """Full-precision [out_features, in_features] weights: absmean quantisation and packing on the device."""
+        import numpy as np
+        w = np.ascontiguousarray(weights_host, dtype=np.float32)
+        if w.ndim != 2:
+            raise IncompatibleShapes("weights must be [out_features, in_features]")
+        out = C.c_void_p()
+        check(L.load().bitnet_backend_upload_f32(self._h, w.ctypes.data, w.shape[0], w.shape[1], C.byref(out)))
+        return DeviceWeights(self, out.value)
+
+    def upload_gguf_ternary(self, tensor_bytes, out_features: int, in_features: int):
+        """A GGUF ternary tensor (8 bytes of scale/offset metadata + 2-bit codes, gguf.rs:1089-1165);
+        returns (weights, offset)."""
+        import numpy as np
+        t = np.frombuffer(bytes(tensor_bytes), dtype=np.uint8) if not isinstance(tensor_bytes, np.ndarray) else np.ascontiguousarray(tensor_bytes, dtype=np.uint8)
+        out, off = C.c_void_p(), C.c_float()
+        check(L.load().bitnet_backend_upload_gguf_ternary(self._h, t.ctypes.data, t.size, out_features, in_features, C.byref(off), C.byref(out)))
+        return DeviceWeights(self, out.value), off.value
+
     def bitlinear_forward(self, w: DeviceWeights, x, y, opts: L.ForwardOpts | None = None, stream_idx: int = 0) -> None:
         """x [M,K] fp32 -> y [M,N] fp32, both device tensors."""
         M = _numel(x) // w.in_features

@@ -283,3 +283,18 @@ def sample_tokens(logits: torch.Tensor, rng_state: torch.Tensor | None = None, *
     check(L.load().bitnet_sample_tokens(logits.data_ptr(), B, V, C.byref(cfg), rng_state.data_ptr() if rng_state is not None else None,
                                         out.data_ptr(), _stream(stream)))
     return out
+
+
+def quantize_pack_weights(w: torch.Tensor, stream=None):
+    """absmean ternary quantisation of fp32 weights and 2-bit packing on the device (weights.rs:807-857,
+    packing.rs:352-388); returns (packed uint8 [ceil(n/4)], scale as a Python float)."""
+    w = _require(w, torch.float32, "w")
+    n = w.numel()
+    packed = torch.empty((packed_len(n),), dtype=torch.uint8, device=w.device)
+    scale = torch.empty((1,), dtype=torch.float32, device=w.device)
+    need = C.c_size_t()
+    check(L.load().bitnet_quantize_pack_weights_workspace_size(n, C.byref(need)))
+    ws = _workspace(need.value, w.device, stream)
+    check(L.load().bitnet_quantize_pack_weights(w.data_ptr(), n, packed.data_ptr(), scale.data_ptr(), _aligned_ptr(ws), need.value,
+                                                _stream(stream)))
+    return packed, float(scale.item())

@@ -184,3 +184,69 @@ class ForwardPassPipeline:
 
     def positions(self, batch: int) -> np.ndarray:
         return self._read(L.DECODER_POSITIONS, (batch,), np.int32)
+
+
+@dataclass
+class BackendCapabilities:
+    """BackendCapabilities (bitnet-inference/src/engine/mod.rs:140-148)."""
+    supports_batching: bool
+    supports_streaming: bool
+    max_batch_size: int
+    memory_limit: int | None
+    device_type: str
+
+
+class CudaInferenceBackend:
+    """The product-level plug point: the reference's InferenceBackend trait (bitnet-inference/src/engine/mod.rs:126-138:
+    execute_batch, optimize_model, get_memory_usage, capabilities) on top of the CUDA decode step.
+
+    `optimize_model(model)` takes a model description -- {"config": ForwardPassConfig, "embedding": [vocab, hidden] fp32,
+    "layers": [dict per layer as ForwardPassPipeline.load_layer takes], "lm_head": (packed, scale)} -- and makes it resident
+    on the device.  `execute_batch(inputs)` runs each input (token ids [B, T] or [T]) through the model and returns, per
+    input, the logits of its last position [B, vocab] (ForwardPassPipeline::forward followed by the narrow of
+    generate(), forward_pass_pipeline.rs:245-331)."""
+
+    def __init__(self, backend: CudaBackend | None = None, memory_pool_size: int = 8 << 30):
+        from .cuda import CudaBackendConfig
+        self._own = backend is None
+        self.backend = backend or CudaBackend(CudaBackendConfig(memory_pool_size=memory_pool_size))
+        self.pipeline: ForwardPassPipeline | None = None
+
+    def optimize_model(self, model: dict) -> None:
+        if self.pipeline is not None:
+            self.pipeline.close()
+        self.pipeline = ForwardPassPipeline(self.backend, model["config"])
+        self.pipeline.load_embedding(model["embedding"])
+        for i, lw in enumerate(model["layers"]):
+            self.pipeline.load_layer(i, lw)
+        self.pipeline.load_lm_head(*model["lm_head"])
+
+    def execute_batch(self, inputs) -> list:
+        if self.pipeline is None:
+            raise IncompatibleShapes("no model: call optimize_model first")
+        outs = []
+        for ids in inputs:
+            a = np.ascontiguousarray(ids, dtype=np.int32)
+            if a.ndim == 1:
+                a = a[None, :]
+            self.pipeline.reset()
+            if a.shape[1] > 1:
+                self.pipeline.feed(a[:, :-1])
+            self.pipeline.decode(a[:, -1], 1, SamplingConfig(deterministic=True))
+            outs.append(self.pipeline.logits(a.shape[0]))
+        return outs
+
+    def get_memory_usage(self) -> int:
+        mm = self.backend.memory_manager()
+        return mm._usage()[0]
+
+    def capabilities(self) -> BackendCapabilities:
+        cfg = self.pipeline.config if self.pipeline else None
+        return BackendCapabilities(True, True, cfg.max_batch if cfg else 0, self.backend.memory_manager()._usage()[1], "cuda")
+
+    def close(self) -> None:
+        if self.pipeline is not None:
+            self.pipeline.close()
+            self.pipeline = None
+        if self._own:
+            self.backend.close()

@@ -295,6 +295,14 @@ bitnet_status_t bitnet_unpack_ternary(const uint8_t *packed_dev, size_t n_values
 bitnet_status_t bitnet_sanitize_packed(uint8_t *packed_dev, size_t n_bytes,
                                        unsigned long long *count_dev, bitnet_stream_t stream);
 
+/* absmean_quantize_weights + BitPacked2BitPacker::pack on device buffers (weights.rs:807-857,
+ * packing.rs:352-388): n_values fp32 weights -> ceil(n_values/4) packed bytes and the fp32 scale
+ * sum(W t) / sum(t t) in *scale_dev.  Sums run in double precision in a fixed order. */
+bitnet_status_t bitnet_quantize_pack_weights(const float *w_dev, size_t n_values, uint8_t *packed_dev,
+                                             float *scale_dev, void *workspace_dev, size_t workspace_bytes,
+                                             bitnet_stream_t stream);
+bitnet_status_t bitnet_quantize_pack_weights_workspace_size(size_t n_values, size_t *bytes);
+
 /* One-time preparation of a packed weight buffer for the kernels of this library: the hook that
  * the reference names enable_weight_permutation / permute_weights_16x32
  * (bitnet-cuda/src/kernels/w2a8_gemv.rs:21, :259).  No permutation is needed here -- every kernel
@@ -372,6 +380,16 @@ bitnet_status_t bitnet_backend_upload_packed(bitnet_backend *b, const uint8_t *p
                                              size_t N, size_t K, float w_scale, bitnet_weights **out);
 bitnet_status_t bitnet_backend_upload_ternary(bitnet_backend *b, const int8_t *ternary_host,
                                               size_t N, size_t K, float w_scale, bitnet_weights **out);
+/* Full-precision weights [N,K]: absmean ternary quantisation (absmean_quantize_weights,
+ * bitnet-quant/src/quantization/weights.rs:807-857) and packing on the device; the scale it computes
+ * becomes the handle's w_scale. */
+bitnet_status_t bitnet_backend_upload_f32(bitnet_backend *b, const float *weights_host,
+                                          size_t N, size_t K, bitnet_weights **out);
+/* A ternary tensor of a GGUF file as GgufLoader::decode_ternary_weights reads it
+ * (bitnet-inference/src/gguf.rs:1089-1165): 8 bytes of metadata (f32 scale, f32 offset, little endian)
+ * followed by the 2-bit codes; the codes are uploaded as they are, never unpacked on the host. */
+bitnet_status_t bitnet_backend_upload_gguf_ternary(bitnet_backend *b, const uint8_t *tensor_host, size_t tensor_bytes,
+                                                   size_t N, size_t K, float *offset_out, bitnet_weights **out);
 bitnet_status_t bitnet_backend_free_weights(bitnet_backend *b, bitnet_weights *w);
 bitnet_status_t bitnet_weights_info(const bitnet_weights *w, size_t *N, size_t *K, float *w_scale,
                                     const uint8_t **packed_dev);
@@ -430,6 +448,27 @@ bitnet_status_t bitnet_backend_ffn_plan_create(bitnet_backend *b, const bitnet_f
                                                bitnet_ffn_plan **out);
 bitnet_status_t bitnet_backend_ffn_plan_run(bitnet_ffn_plan *plan);
 void bitnet_backend_ffn_plan_destroy(bitnet_ffn_plan *plan);
+
+/* ---- exchange step of the output-feature-split layer ------------------------------------------------- */
+/* Every GPU holds y[:, its column slice]; all need y[M, N].  No counterpart in the reference, which has no
+ * multi-GPU code.
+ * Peer-store form: this GPU's slice y_local_dev [M, n_local] (row stride ld_local) is written into every entry of
+ * y_peers_dev (n_peers pointers, each to the slice's first column in one GPU's full-width output of row stride ldy,
+ * mapped into this process: CUDA IPC, symmetric memory or peer access).  The caller synchronises the GPUs
+ * afterwards.  (bitnet_forward_opts.y_peers_dev does the same from the decode kernel's epilogue, without this pass.) */
+bitnet_status_t bitnet_allgather_output(const float *y_local_dev, size_t M, size_t n_local, size_t ld_local,
+                                        float *const *y_peers_dev, int32_t n_peers, size_t ldy, bitnet_stream_t stream);
+/* NCCL form.  The library finds NCCL at run time (dlopen of libnccl.so.2, the copy already in the process if there
+ * is one); without it these return BITNET_ERR_UNSUPPORTED_OPERATION.  bitnet_nccl_unique_id on one rank, the 128
+ * bytes handed to the others by the caller's own means, bitnet_nccl_comm_create on every rank with its device
+ * current.  bitnet_allgather_output_nccl: ncclAllGather of the fp32 slices into staging_dev [n_ranks, M, n_local],
+ * then the local reordering into y_full_dev [M, n_ranks * n_local] (row stride ldy). */
+bitnet_status_t bitnet_nccl_unique_id(uint8_t *id_out /* 128 bytes */);
+bitnet_status_t bitnet_nccl_comm_create(const uint8_t *id, int32_t n_ranks, int32_t rank, void **comm_out);
+bitnet_status_t bitnet_nccl_comm_destroy(void *comm);
+bitnet_status_t bitnet_allgather_output_nccl(void *comm, const float *y_local_dev, size_t M, size_t n_local,
+                                             float *staging_dev, float *y_full_dev, int32_t n_ranks, size_t ldy,
+                                             bitnet_stream_t stream);
 
 /* ---- decode step of a whole model (handle based) ------------------------------------------------- */
 /* ForwardPassPipeline (bitnet-inference/src/engine/forward_pass_pipeline.rs:146-362) for one new token per

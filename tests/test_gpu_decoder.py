@@ -11,7 +11,7 @@ import torch
 import oracle
 from oracle import decoder as od
 from bitnet_mlx_rs_b200 import cuda, ops
-from bitnet_mlx_rs_b200.pipeline import ForwardPassConfig, ForwardPassPipeline, SamplingConfig
+from bitnet_mlx_rs_b200.pipeline import CudaInferenceBackend, ForwardPassConfig, ForwardPassPipeline, SamplingConfig
 
 pytestmark = pytest.mark.gpu
 NORM_RTOL, NORM_ATOL = 1e-5, 2e-6       # SubLN: fp32 sums in tree order vs float64
@@ -245,3 +245,28 @@ def test_generate_stops_at_eos_and_is_reproducible():
         p.close()
     finally:
         b.close()
+
+
+def test_inference_backend_plug_point():
+    # InferenceBackend (engine/mod.rs:126-138): optimize_model, execute_batch, get_memory_usage, capabilities
+    cfg, emb, ls, head = small_model(seed=5, max_batch=2)
+    pc = ForwardPassConfig(num_layers=cfg["num_layers"], vocab_size=cfg["vocab_size"], hidden_size=cfg["hidden_size"],
+                           num_heads=cfg["num_heads"], num_kv_heads=cfg["num_kv_heads"], head_dim=cfg["head_dim"],
+                           ffn_intermediate_size=cfg["ffn_size"], max_seq_len=cfg["max_seq_len"], max_batch=2, rms_norm_eps=cfg["norm_eps"])
+    be = CudaInferenceBackend(memory_pool_size=1 << 30)
+    try:
+        before = be.get_memory_usage()
+        be.optimize_model({"config": pc, "embedding": emb, "layers": ls, "lm_head": head})
+        assert be.get_memory_usage() > before
+        caps = be.capabilities()
+        assert caps.supports_batching and caps.max_batch_size == 2 and caps.device_type == "cuda"
+        ids = np.random.default_rng(3).integers(0, cfg["vocab_size"], size=(2, 4)).astype(np.int32)
+        out = be.execute_batch([ids, ids[0]])
+        ref = od.OracleDecoder(cfg, emb, ls, head)
+        for t in range(4):
+            want = ref.step(ids[:, t])
+        assert out[0].shape == (2, cfg["vocab_size"]) and out[1].shape == (1, cfg["vocab_size"])
+        assert np.abs(out[0] - want).max() <= MODEL_LOOSE * np.abs(want).max()
+        np.testing.assert_allclose(out[1][0], out[0][0], rtol=0, atol=MODEL_TOL * np.abs(want).max())
+    finally:
+        be.close()

@@ -412,6 +412,47 @@ def test_backend_host_ffn_async_streams():
         b.close()
 
 
+@pytest.mark.parametrize("shape", [(64, 128), (2560, 640), (37, 29), (1, 5), (700, 2561)])
+def test_device_absmean_quantise_and_pack(shape):
+    # weights.rs:807-857 + packing.rs:352-388 on the device: ternary codes exact, scale to fp32 rounding of double sums
+    rng = np.random.default_rng(shape[0])
+    w = rng.standard_normal(shape).astype(np.float32)
+    w[0, 0] = 0.0
+    packed, scale = ops.quantize_pack_weights(dev(w))
+    t, ref_scale = oracle.absmean_quantize_weights(w)
+    assert np.array_equal(packed.cpu().numpy(), oracle.pack_ternary(t.reshape(-1))[0])
+    assert scale == pytest.approx(ref_scale, rel=1e-6)
+    zero, s0 = ops.quantize_pack_weights(torch.zeros(8, 16, device="cuda"))          # all-zero weights: every code 1, scale 1
+    assert s0 == 1.0 and bool((zero == 0x55).all())
+
+
+def test_backend_ingests_full_precision_and_gguf_tensors():
+    import struct
+    N, K, M = 640, 2560, 4
+    b = cuda.initialize()
+    try:
+        w = np.random.default_rng(2).standard_normal((N, K)).astype(np.float32)
+        x = oracle.gen_activations(21, 1, (M, K))
+        dw = b.upload_f32(w)
+        t, ref_scale = oracle.absmean_quantize_weights(w)
+        assert dw.scale == pytest.approx(ref_scale, rel=1e-6)
+        ref = oracle.bitlinear_forward(oracle.pack_ternary(t.reshape(-1))[0], dw.scale, x, N)["y"]
+        assert np.array_equal(b.bitlinear_forward_host(dw, x), ref)
+        # gguf.rs:1089-1165: scale and offset as little-endian f32, then the codes; code 3 reads as weight 0
+        wp = oracle.gen_ternary_packed(21, 2, N * K).copy()
+        wp[::97] |= 0x03
+        tensor = struct.pack("<ff", 0.0375, -1.5) + wp.tobytes()
+        dg, offset = b.upload_gguf_ternary(tensor, N, K)
+        assert dg.scale == np.float32(0.0375) and offset == -1.5
+        clean = wp.copy()
+        clean[::97] = (clean[::97] & 0xFC) | 0x01
+        assert np.array_equal(b.bitlinear_forward_host(dg, x), oracle.bitlinear_forward(clean, float(np.float32(0.0375)), x, N)["y"])
+        with pytest.raises(cuda.IncompatibleShapes):
+            b.upload_gguf_ternary(tensor[:100], N, K)
+    finally:
+        b.close()
+
+
 @pytest.mark.parametrize("n_lanes", [1, 3])
 def test_backend_ffn_plan_replays_a_batch(n_lanes):
     # a fixed batch of FFN blocks bound to host buffers (some page-locked, some not), replayed twice
