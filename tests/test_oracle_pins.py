@@ -204,3 +204,70 @@ def test_absmean_weight_quantiser():
     thr = np.abs(w).mean() * 0.7
     assert np.array_equal(t, (np.sign(w) * (np.abs(w) > thr)).astype(np.int8))
     assert scale == pytest.approx(float((w * t).sum() / (t * t).sum()), rel=1e-5)
+
+
+# ---- decode-step restatements (oracle/decoder.py) ---------------------------------------------------
+
+def test_sampler_generator_follows_the_reference_recurrence():
+    # sampling.rs:273-276: state = state.wrapping_mul(1103515245).wrapping_add(12345); token = (state / 65536) % 1000
+    from oracle import decoder as od
+    s = 42
+    seen = []
+    for _ in range(4):
+        s = od.lcg_next(s)
+        seen.append((s // 65536) % 1000)
+    assert s == (((((42 * 1103515245 + 12345) * 1103515245 + 12345) * 1103515245 + 12345) * 1103515245 + 12345) % (1 << 64))
+    assert seen == [(((42 * 1103515245 + 12345) % (1 << 64)) // 65536) % 1000] + seen[1:]
+    big = (1 << 64) - 1
+    assert od.lcg_next(big) == (big * 1103515245 + 12345) % (1 << 64)          # wrapping arithmetic
+    assert 0.0 <= od.lcg_uniform(s) < 1.0
+
+
+def test_bf16_rounding_known_answers():
+    from oracle import decoder as od
+    x = np.array([1.0, 1.00390625, 1.001953125, 1.005859375, -2.5, 0.0], dtype=np.float32)
+    # 1 + 2^-8 is exactly half way between bf16 neighbours 1 and 1 + 2^-7: ties go to the even mantissa (1.0);
+    # 1 + 3 * 2^-9 rounds up; 1 + 2^-9 rounds down
+    assert od.bf16_round(x).tolist() == [1.0, 1.0, 1.0, 1.0078125, -2.5, 0.0]
+    import torch
+    r = torch.randn(4096, dtype=torch.float32)
+    assert np.array_equal(od.bf16_round(r.numpy()), r.to(torch.bfloat16).float().numpy())
+
+
+def test_subln_and_attention_restatements_agree_with_torch():
+    import torch
+    from oracle import decoder as od
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((5, 96)).astype(np.float32)
+    w, b = rng.standard_normal(96).astype(np.float32), rng.standard_normal(96).astype(np.float32)
+    t = torch.from_numpy(x).double()
+    want = (t - t.mean(-1, keepdim=True)) / torch.sqrt(t.var(-1, keepdim=True, unbiased=True) + 1e-5) * torch.from_numpy(w).double() + torch.from_numpy(b).double()
+    np.testing.assert_allclose(od.subln(x, w, b, 1e-5), want.float().numpy(), rtol=1e-6, atol=1e-6)
+    nh, nkv, hd, L = 4, 2, 64, 9
+    q = rng.standard_normal(nh * hd).astype(np.float32)
+    k = od.bf16_round(rng.standard_normal((nkv, L, hd)).astype(np.float32))
+    v = od.bf16_round(rng.standard_normal((nkv, L, hd)).astype(np.float32))
+    got = od.attention_decode(q, k, v, nh, nkv, hd)
+    for h in range(nh):
+        s = torch.from_numpy(k[h // 2]).double() @ torch.from_numpy(q[h * hd:(h + 1) * hd]).double() / np.sqrt(hd)
+        ref = torch.softmax(s, 0) @ torch.from_numpy(v[h // 2]).double()
+        np.testing.assert_allclose(got[h * hd:(h + 1) * hd], ref.float().numpy(), rtol=1e-5, atol=1e-6)
+
+
+def test_sampler_restatement_filters():
+    from oracle import decoder as od
+    logits = np.array([0.0, 3.0, 1.0, 3.0, -1.0, 2.0], dtype=np.float32)
+    assert od.sample(logits, 1, deterministic=True)[0] == 1                      # first index on ties
+    seeds = [(i * 2654435761 * 40503) % (1 << 63) for i in range(1, 401)]       # spread: small seeds give small draws
+    # top_k = 2 keeps both 3.0s (ties with the cut-off stay); top_k = 3 adds the 2.0
+    picks = {od.sample(logits, s, top_k=2)[0] for s in seeds[:200]}
+    assert picks == {1, 3}
+    picks = {od.sample(logits, s, top_k=3)[0] for s in seeds}
+    assert picks == {1, 3, 5}
+    # top_p: the two 3.0s hold 0.72 of the mass; 0.5 keeps them (equal values stay together), 0.8 adds the 2.0
+    picks = {od.sample(logits, s, top_p=0.5)[0] for s in seeds[:200]}
+    assert picks == {1, 3}
+    picks = {od.sample(logits, s, top_p=0.8)[0] for s in seeds}
+    assert picks == {1, 3, 5}
+    picks = {od.sample(logits, s, temperature=0.05)[0] for s in seeds[:100]}
+    assert picks == {1, 3}
