@@ -773,7 +773,7 @@ def run_case(spec):
                    torch.randn((M, nkv, K + 8, hd), device="cuda", generator=gen).to(torch.bfloat16)) for _ in range(copies)]
         qkv = torch.randn((M, (nh + 2 * nkv) * hd), device="cuda", generator=gen)
         pos = torch.full((M,), K, dtype=torch.int32, device="cuda")
-        call = lambda i: ops.attention_decode(qkv, caches[i][0], caches[i][1], pos, nh, nkv, hd)   # noqa: E731
+        call = lambda i: ops.attention_decode(qkv, caches[i][0], caches[i][1], pos, nh, nkv, hd, n_splits=N)   # noqa: E731  (N = splits, 0 = choose)
         nbytes = 2 * M * nkv * (K + 1) * hd * 2
         int_ops = 4.0 * M * nh * (K + 1) * hd
     elif kind == "ffn":

@@ -58,7 +58,9 @@ static int resolve_path(int path, size_t M, size_t K, size_t N)
 {
     if (path != BITNET_PATH_AUTO) return path;
     if (M <= 16 && decode_supports(M, K, N)) return BITNET_PATH_DECODE;
-    if (M <= 128 && midm_can_run(M, K, N, false)) return BITNET_PATH_CLUSTER;
+    // a few dozen tokens: the cluster GEMM, unless the layer is so wide that its one-shot CTAs would run in many waves
+    // (the language-model head): the persistent GEMM pipelines those better
+    if (M <= 128 && N <= 32768 && midm_can_run(M, K, N, false)) return BITNET_PATH_CLUSTER;
     if (prefill_supports(M, K, N)) return BITNET_PATH_PREFILL;
     return BITNET_PATH_GENERIC;
 }

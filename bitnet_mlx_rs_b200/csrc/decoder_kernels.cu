@@ -384,12 +384,12 @@ size_t attention_scratch_bytes(size_t B, size_t n_heads, size_t n_kv, size_t hea
     return align_up(B * n_heads * n_splits * head_dim * 4, 256) + align_up(B * n_heads * n_splits * 8, 256) + align_up(B * n_kv * 4, 256);
 }
 
-// Splits per (sequence, KV head): enough CTAs for four per SM (sixteen warps with loads in flight), at least 64 keys
-// per split at the longest context.
+// Splits per (sequence, KV head): about two CTAs per SM in all (more splits cost more in partial results and their
+// fold than they gain in balance), at least 64 keys per split at the longest context.
 int attention_splits(size_t B, size_t n_kv, size_t max_context)
 {
     const size_t pairs = B * n_kv;
-    size_t want = (4 * (size_t)device_sm_count() + pairs - 1) / pairs;
+    size_t want = (2 * (size_t)device_sm_count() + pairs - 1) / pairs;
     const size_t by_len = max_context / 64 > 0 ? max_context / 64 : 1;
     if (want > by_len) want = by_len;
     if (want > 32) want = 32;
