@@ -54,6 +54,7 @@ struct MidParams {
     int pair;                      // 1: cluster = 2 * ck CTAs, ranks >= ck work on the second matrix
     int tmem_cols;
     int a_slots;                   // 32-column slots of expanded weights in tensor memory; slice s uses slot s % a_slots
+    int w_slots;                   // 4 KB slots of packed weights in shared memory; slice s uses slot s % w_slots
     unsigned x_bytes;              // shared memory reserved for the activation slices / the partial tile
 };
 
@@ -176,6 +177,7 @@ midm_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     extern __shared__ unsigned char mm_smem_raw[];
     __shared__ __align__(8) unsigned long long s_full_w[MM_MAX_SLICES], s_full_x[MM_MAX_SLICES], s_a_ready[MM_MAX_SLICES];
     __shared__ __align__(8) unsigned long long s_a_free[MM_MAX_SLICES];   // the MMAs of a slice have read its tensor-memory slot
+    __shared__ __align__(8) unsigned long long s_w_free[MM_MAX_SLICES];   // the expanders hold a slice's packed words in registers
     __shared__ __align__(8) unsigned long long s_acc_full;
     __shared__ unsigned s_tmem_base;
     __shared__ unsigned s_failed;
@@ -201,6 +203,7 @@ midm_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             mm_mbar_init(&s_full_x[s], 1);
             mm_mbar_init(&s_a_ready[s], 4);
             mm_mbar_init(&s_a_free[s], 1);
+            mm_mbar_init(&s_w_free[s], 4);
         }
         mm_mbar_init(&s_acc_full, 1);
         s_failed = 0;
@@ -220,7 +223,8 @@ midm_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         // ===================== TMA: everything this CTA needs, requested at once =====================
         if (lane == 0) {
             const CUtensorMap *mw = matrix ? &map_w2 : &map_w;
-            for (int s = 0; s < ns; ++s) {   // weights do not depend on the kernel in front of this one
+            const int first = ns < p.w_slots ? ns : p.w_slots;
+            for (int s = 0; s < first; ++s) {   // weights do not depend on the kernel in front of this one
                 mm_mbar_expect_tx(&s_full_w[s], MM_WP_BYTES);
                 mm_tma_load_2d(w_base + (size_t)s * MM_WP_BYTES, mw, (s0 + s) * (MM_BK / 4), tile * MM_BF, &s_full_w[s]);
             }
@@ -228,6 +232,11 @@ midm_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             for (int s = 0; s < ns; ++s) {
                 mm_mbar_expect_tx(&s_full_x[s], x_slice_bytes);
                 mm_tma_load_2d(x_base + (size_t)s * x_slice_bytes, &map_x, (s0 + s) * MM_BK, 0, &s_full_x[s]);
+            }
+            for (int s = first; s < ns; ++s) {  // the later slices reuse a slot once the expanders have taken its words
+                if (!mm_mbar_wait(&s_w_free[s - p.w_slots], 0)) { s_failed = 1; break; }
+                mm_mbar_expect_tx(&s_full_w[s], MM_WP_BYTES);
+                mm_tma_load_2d(w_base + (size_t)(s % p.w_slots) * MM_WP_BYTES, mw, (s0 + s) * (MM_BK / 4), tile * MM_BF, &s_full_w[s]);
             }
         }
     } else if (warp == 1) {
@@ -256,7 +265,7 @@ midm_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         bool ok = true;
         for (int s = 0; s < ns && ok; ++s) {
             if (!mm_warp_wait(&s_full_w[s], 0)) { ok = false; break; }
-            const uint4 *src = reinterpret_cast<const uint4 *>(w_base + (size_t)s * MM_WP_BYTES + row * (MM_BK / 4));
+            const uint4 *src = reinterpret_cast<const uint4 *>(w_base + (size_t)(s % p.w_slots) * MM_WP_BYTES + row * (MM_BK / 4));
             const uint4 w0 = src[0], w1 = src[1];
             const unsigned w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
             unsigned r[32];
@@ -266,6 +275,10 @@ midm_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 r[4 * g + 1] = (w[g] >> 2) & 0x03030303u;
                 r[4 * g + 2] = (w[g] >> 4) & 0x03030303u;
                 r[4 * g + 3] = (w[g] >> 6) & 0x03030303u;
+            }
+            if (s + p.w_slots < ns) {       // a later slice lands in this shared-memory slot
+                __syncwarp();
+                if (lane == 0) mm_mbar_arrive(&s_w_free[s]);
             }
             if (s >= p.a_slots) {   // the slot still feeds the MMAs of slice s - a_slots
                 if (!mm_warp_wait(&s_a_free[s - p.a_slots], 0)) { ok = false; break; }
@@ -402,7 +415,7 @@ bool midm_supports(size_t M, size_t K, size_t N)
 }
 
 struct MidPlan {
-    int mt, ck, tmem_cols, a_slots;
+    int mt, ck, tmem_cols, a_slots, w_slots;
     size_t x_bytes, smem;
     size_t tiles, ctas;
 };
@@ -431,7 +444,12 @@ static bool midm_plan(size_t M, size_t K, size_t N, bool pair, MidPlan *out)
         size_t xb = (size_t)ns * mt * MM_BK;
         if (xb < part) xb = part;
         xb = align_up(xb, 1024);
-        size_t smem = xb + (size_t)ns * MM_WP_BYTES + 1024;
+        // packed weights: a slot per slice, or fewer (at least four, reused in turn) when that lets two CTAs share an SM
+        int w_slots = ns;
+        const size_t two_per_sm = 110 * 1024;
+        if (xb + (size_t)ns * MM_WP_BYTES + 1024 > two_per_sm && ns > 4 && xb + 4 * (size_t)MM_WP_BYTES + 1024 <= two_per_sm)
+            w_slots = (int)((two_per_sm - 1024 - xb) / MM_WP_BYTES);
+        size_t smem = xb + (size_t)w_slots * MM_WP_BYTES + 1024;
         if (smem > 220 * 1024) continue;
         // Shared memory is also what keeps tensor memory from being oversubscribed, so that no CTA ever waits
         // inside tcgen05.alloc for a CTA of another cluster (which could be waiting for this cluster in turn):
@@ -439,14 +457,14 @@ static bool midm_plan(size_t M, size_t K, size_t N, bool pair, MidPlan *out)
         // of them fit an SM (and none beside a CTA of the persistent GEMM, which fills an SM's shared memory).
         const size_t floor_bytes = 77 * 1024;
         if (smem < floor_bytes) smem = floor_bytes;
-        const int per_sm = smem <= 110 * 1024 ? 2 : 1;
+        const int per_sm = smem <= two_per_sm ? 2 : 1;
         const size_t ctas = tiles * (size_t)ck * (pair ? 2 : 1);
         const double waves = (double)((ctas + (size_t)sms * per_sm - 1) / ((size_t)sms * per_sm));
-        const double cost = waves * (6.0 + ns) + 0.05 * ck;
+        const double cost = waves * (6.0 + ns) + 0.8 * ck;   // a wider cluster has more partial tiles to sum: measured, about 0.8 of a slice each
         if (!found || cost < best) {
             found = true;
             best = cost;
-            out->mt = mt; out->ck = ck; out->tmem_cols = cols; out->a_slots = a_slots; out->x_bytes = xb; out->smem = smem; out->tiles = tiles; out->ctas = ctas;
+            out->mt = mt; out->ck = ck; out->tmem_cols = cols; out->a_slots = a_slots; out->w_slots = w_slots; out->x_bytes = xb; out->smem = smem; out->tiles = tiles; out->ctas = ctas;
         }
     }
     return found;
@@ -504,6 +522,7 @@ bitnet_status_t launch_midm(const ForwardArgs &a, void *workspace, size_t worksp
     p.M = (int)a.M; p.K = (int)a.K; p.N = (int)a.N; p.ldy = a.ldy ? a.ldy : a.N;
     p.mt = pl.mt; p.k_slices = (int)(a.K / MM_BK); p.ck = pl.ck; p.pair = pair ? 1 : 0; p.tmem_cols = pl.tmem_cols;
     p.a_slots = pl.a_slots;
+    p.w_slots = pl.w_slots;
     p.x_bytes = (unsigned)pl.x_bytes;
 
     {   // once per device, under a lock: host threads launch concurrently
