@@ -64,11 +64,11 @@ def measured_peaks():
     return 6650.0, "fallback"
 
 
-def profiled_traffic():
+def profiled_traffic(name="decode_kernel_ffn_gate_up_m1_ncu.md"):
     """DRAM bytes per launch of the dominant kernel as the committed ncu summary records them (a line
-    `traffic_bytes_per_launch: N` in profiles/decode_kernel_ffn_gate_up_m1_ncu.md); (None, None) without it."""
+    `traffic_bytes_per_launch: N` in that file under profiles/); (None, None) without it."""
     import re
-    f = ROOT / "profiles" / "decode_kernel_ffn_gate_up_m1_ncu.md"
+    f = ROOT / "profiles" / name
     if f.exists():
         m = re.search(r"traffic_bytes_per_launch\s*[:=]\s*(\d+)", f.read_text())
         if m:
@@ -252,14 +252,34 @@ def run_cuda(args):
 
     # per FFN block: M = 1 runs two launches (gate/up pair, down), each quantising its own input;
     # M >= 2 adds one small quantiser launch in front of each (activations are quantised once, not per CTA)
-    launches_per_step = sum((2 if M < 2 else 4) for M in TOKEN_COUNTS) * LAYERS
+    block_launches_per_step = sum((2 if M < 2 else 4) for M in TOKEN_COUNTS) * LAYERS
+
+    # The same 90 blocks as ONE group (bitnet_ffn_group_*): a quantiser launch and a persistent decode launch
+    # per stage, each streaming the weights of every block.  This is the headline form; the per-block forms
+    # (eight streams, one chain) are timed beside it.
+    group = None
+    if not args.per_block:
+        group = ops.FfnGroup([(Wg[l], S[l][0], Wu[l], S[l][1], Wd[l], S[l][2], X[M][l], Y[M][l]) for M, l in calls], HIDDEN, FFN)
+    launches_per_step = 4 if group is not None else block_launches_per_step
 
     # parity spot check against the oracle on layer 0, M=8 (checker only, outside any timing)
+    ry, _ = oracle.ffn_forward(host0[0], scales0[0], host0[1], scales0[1], host0[2], scales0[2], x0, FFN)
     step(False)
     torch.cuda.synchronize()
     if rank == 0:
-        ry, _ = oracle.ffn_forward(host0[0], scales0[0], host0[1], scales0[1], host0[2], scales0[2], x0, FFN)
         np.testing.assert_allclose(Y[8][0].cpu().numpy(), ry, rtol=1e-5, atol=0)
+    if group is not None:
+        per_block = {M: Y[M].clone() for M in TOKEN_COUNTS}
+        for M in TOKEN_COUNTS:
+            Y[M].fill_(float("nan"))
+        group.run()
+        torch.cuda.synchronize()
+        if rank == 0:
+            np.testing.assert_allclose(Y[8][0].cpu().numpy(), ry, rtol=1e-5, atol=0)
+        for M in TOKEN_COUNTS:   # every block of the group, bit for bit against the per-block launches
+            if not torch.equal(Y[M], per_block[M]):
+                raise RuntimeError(f"grouped FFN blocks differ from the per-block launches at M={M}")
+        del per_block
 
     # capture the step in a CUDA graph: try programmatic dependent launch first
     side = torch.cuda.Stream()
@@ -281,15 +301,39 @@ def run_cuda(args):
                 torch.cuda.synchronize()
         return None, "eager"
 
-    graph, mode = capture(True)
-    if args.eager or graph is None:
-        graph, mode = None, "eager"
-    if graph is not None and n_streams > 1:
-        mode += f", {n_streams} concurrent streams, BITNET_FLAG_THROUGHPUT"
+    def capture_group():
+        try:
+            with torch.cuda.stream(side):
+                group.run(stream=side)
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    group.run(stream=side)
+            g.replay()
+            torch.cuda.synchronize()
+            return g, "cuda_graph+pdl"
+        except Exception as ex:
+            print(f"graph capture of the grouped step failed: {ex}", file=sys.stderr)
+            torch.cuda.synchronize()
+            return None, "eager"
+
+    if group is not None:
+        graph, mode = capture_group()
+        if args.eager or graph is None:
+            graph, mode = None, "eager"
+        mode += ", one group of 90 blocks: 4 launches per step (bitnet_ffn_group_run)"
+    else:
+        graph, mode = capture(True)
+        if args.eager or graph is None:
+            graph, mode = None, "eager"
+        if graph is not None and n_streams > 1:
+            mode += f", {n_streams} concurrent streams, BITNET_FLAG_THROUGHPUT"
 
     def run_step():
         if graph is not None:
             graph.replay()
+        elif group is not None:
+            group.run()
         else:
             step(False, False)
 
@@ -319,25 +363,34 @@ def run_cuda(args):
     clocks = sampler.stop() if rank == 0 else None
 
     nbytes = step_bytes()
-    # the same step as ONE dependent chain of launches on one stream (what a single sequence sees)
-    chain = None
-    if graph is not None and n_streams > 1:
-        g1, mode1 = capture(False)
-        if g1 is not None:
-            for _ in range(3):
-                g1.replay()
-            c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            barrier()
-            c0.record()
-            n1 = max(5, min(args.steps, 20))
-            for _ in range(n1):
-                g1.replay()
-            c1.record()
-            barrier()
-            ms1 = c0.elapsed_time(c1) / n1
-            chain = {"ms_per_step": ms1, "value": nbytes / (ms1 * 1e-3) / 1e9, "unit": "GB/s", "launch_mode": mode1,
-                     "us_per_ffn_block": ms1 * 1e3 / len(calls)}
-            del g1
+
+    def per_block_figure(concurrent):
+        g1, mode1 = capture(concurrent)
+        if g1 is None:
+            return None
+        for _ in range(3):
+            g1.replay()
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        c0.record()
+        n1 = max(5, min(args.steps, 20))
+        for _ in range(n1):
+            g1.replay()
+        c1.record()
+        barrier()
+        ms1 = c0.elapsed_time(c1) / n1
+        return {"ms_per_step": ms1, "value": nbytes / (ms1 * 1e-3) / 1e9, "unit": "GB/s", "launch_mode": mode1,
+                "launches_per_step": block_launches_per_step, "us_per_ffn_block": ms1 * 1e3 / len(calls)}
+
+    # the same step as ONE dependent chain of per-block launches on one stream (what a single sequence sees),
+    # and as per-block launches dealt to the streams
+    chain, streamed = None, None
+    if graph is not None and not args.eager:
+        chain = per_block_figure(False)
+        if group is not None and n_streams > 1:
+            streamed = per_block_figure(True)
+            if streamed:
+                streamed["launch_mode"] += f", {n_streams} concurrent streams, BITNET_FLAG_THROUGHPUT"
     value = world * nbytes * args.steps / (ms_total * 1e-3) / 1e9
     per_gpu = value / world
     peak, peak_kind = measured_peaks()
@@ -416,7 +469,7 @@ def run_cuda(args):
         barrier()
         model = model_figures(torch, dist, local, world, peak, layers=args.model_layers or None)
 
-    traffic, traffic_source = profiled_traffic()
+    traffic, traffic_source = profiled_traffic("decode_group_kernel_ffn_gate_up_90_blocks_ncu.md") if group is not None else profiled_traffic()
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         r = cpu_ffn_sample(steps=max(args.steps, 1), warmup=max(args.warmup, 1))   # as many passes as the reference arm times
@@ -437,10 +490,11 @@ def run_cuda(args):
                          # dram__bytes_read.sum + dram__bytes_write.sum of one gate/up launch at M = 1, read from the
                          # committed ncu summary of that kernel (not measured by this run); algorithmic 8.89 MB
                          "traffic": traffic, "traffic_source": traffic_source,
-                         "kernel": "decode_kernel (gate/up pair and down launches; algorithmic bytes per launch "
-                                   f"{step_bytes() / launches_per_step:.0f} on average); achieved = bytes of the whole "
-                                   "step / CUDA-event time of the whole graph-replayed step (every launch in it is "
-                                   "this kernel or its quantiser)"},
+                         "kernel": ("decode_group_kernel (one gate/up launch and one down launch over all 90 blocks; "
+                                    if group is not None else "decode_kernel (gate/up pair and down launches; ") +
+                                   f"algorithmic bytes per launch {step_bytes() / launches_per_step:.0f} on average); achieved "
+                                   "= bytes of the whole step / CUDA-event time of the whole graph-replayed step (every "
+                                   "launch in it is this kernel or its quantiser)"},
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": io_bytes, "d2h_bytes_per_step": io_bytes,
                     "steps": e2e_steps,
                     "api": f"bitnet_backend_ffn_plan_run: the step's 90 FFN blocks bound to page-locked host buffers, dealt to "
@@ -453,6 +507,8 @@ def run_cuda(args):
         }
         if chain:
             line["single_chain"] = chain
+        if streamed:
+            line["per_block_streams"] = streamed
         if cpu:
             line["cpu_baseline"] = cpu
         if extra:
@@ -754,8 +810,9 @@ def prefill_layer_figures(torch, ops, gen):
 def run_case(spec):
     """One BitLinear (or FFN) shape on cuda:0, timed with CUDA events -- the small, self-ending workload that the
     profiling commands under profiles/ run.  spec = kind:M:K:N[:copies[:iters]] with kind one of auto, decode, cluster,
-    prefill, generic (a single BitLinear through that path) or ffn (K = hidden, N = ffn).  `copies` distinct weight
-    buffers are rotated so that every launch streams its weights from HBM rather than L2."""
+    prefill, generic (a single BitLinear through that path), ffn (K = hidden, N = ffn) or ffngroup (`copies` independent
+    FFN blocks of M tokens each as one grouped run).  `copies` distinct weight buffers are rotated so that every launch
+    streams its weights from HBM rather than L2."""
     import torch
 
     from bitnet_mlx_rs_b200 import ops
@@ -776,6 +833,13 @@ def run_case(spec):
         call = lambda i: ops.attention_decode(qkv, caches[i][0], caches[i][1], pos, nh, nkv, hd, n_splits=N)   # noqa: E731  (N = splits, 0 = choose)
         nbytes = 2 * M * nkv * (K + 1) * hd * 2
         int_ops = 4.0 * M * nh * (K + 1) * hd
+    elif kind == "ffngroup":
+        W = [tuple(gen_packed_on_device(torch, K * N, gen) for _ in range(3)) for _ in range(copies)]
+        xs = [gen_activations_on_device(torch, (M, K), gen) for _ in range(copies)]
+        ys = [torch.empty((M, K), device="cuda") for _ in range(copies)]
+        group = ops.FfnGroup([(W[i][0], 0.02, W[i][1], 0.02, W[i][2], 0.02, xs[i], ys[i]) for i in range(copies)], K, N)
+        nbytes = copies * (2 * call_bytes(M, K, N) + call_bytes(M, N, K))
+        int_ops = copies * 6.0 * M * K * N
     elif kind == "ffn":
         W = [tuple(gen_packed_on_device(torch, K * N, gen) for _ in range(3)) for _ in range(copies)]
         y, h = torch.empty((M, K), device="cuda"), torch.empty((M, N), device="cuda")
@@ -788,6 +852,9 @@ def run_case(spec):
         call = lambda i: ops.bitlinear_forward(W[i], 0.02, x, N, out=y, path=kind, pdl=True)   # noqa: E731
         nbytes = call_bytes(M, K, N)
         int_ops = 2.0 * M * K * N
+    if kind == "ffngroup":   # one run covers all copies
+        call = lambda i: group.run() if i == 0 else None   # noqa: E731
+        nbytes, int_ops = nbytes / copies, int_ops / copies
     call(0)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -828,7 +895,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--eager", action="store_true", help="launch kernels one by one instead of replaying a CUDA graph")
     ap.add_argument("--no-pdl", action="store_true")
-    ap.add_argument("--streams", type=int, default=8, help="streams the step's independent FFN blocks are dealt to (1 = one chain)")
+    ap.add_argument("--streams", type=int, default=8, help="streams the per-block form deals the step's independent FFN blocks to (1 = one chain)")
+    ap.add_argument("--per-block", action="store_true", help="headline from per-block launches on --streams streams instead of the grouped launch")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-extra", action="store_true", help="skip the single-kernel figures")
     ap.add_argument("--no-model", action="store_true", help="skip the model decode figure (cfg4)")

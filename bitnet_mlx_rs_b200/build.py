@@ -17,7 +17,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 OBJ = PKG / "build"
 LIB = PKG / "libbitnet_cuda_kernels.so"
-SOURCES = ["abi.cu", "backend.cu", "quant_kernels.cu", "generic_gemm.cu", "decode_gemv.cu", "prefill_gemm.cu", "midm_gemm.cu", "noalloc.cu", "decoder_kernels.cu", "decoder.cu", "weights_kernels.cu", "collective.cu"]
+SOURCES = ["abi.cu", "backend.cu", "quant_kernels.cu", "generic_gemm.cu", "decode_gemv.cu", "decode_group.cu", "prefill_gemm.cu", "midm_gemm.cu", "noalloc.cu", "decoder_kernels.cu", "decoder.cu", "weights_kernels.cu", "collective.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -111,6 +111,7 @@ bool midm_can_run(size_t M, size_t K, size_t N, bool pair);
 size_t midm_workspace_bytes(size_t M, size_t K);
 bitnet_status_t launch_midm(const ForwardArgs &a, void *workspace, size_t workspace_bytes, bool ready, cudaStream_t stream);
 bitnet_status_t midm_take_error_flags(unsigned *flags);
+bitnet_status_t group_take_error_flags(unsigned *flags);   // decode_group.cu
 
 int device_sm_count();
 bitnet_status_t launch_quantize_rows_glued(const float *x, size_t M, size_t K, const RowPre *pre, const RowsOut &rows,

@@ -236,6 +236,45 @@ def ffn_forward_fused(w_gate, s_gate, w_up, s_up, w_down, s_down, x: torch.Tenso
     return y, h
 
 
+class FfnGroup:
+    """A group of independent FFN blocks of one shape (at most 16 tokens each) run as four launches for the whole group
+    (bitnet_ffn_group_*).  members: (w_gate, s_gate, w_up, s_up, w_down, s_down, x [M, hidden], y [M, hidden]) with the
+    packed weights as uint8 tensors; the tensors are bound at creation and kept alive by the group."""
+
+    def __init__(self, members, hidden: int, ffn: int):
+        self._keep = []
+        arr = (L.FfnGroupMember * len(members))()
+        for i, (wg, sg, wu, su, wd, sd, x, y) in enumerate(members):
+            x = _require(x, torch.float32, "x")
+            y = _require(y, torch.float32, "y")
+            if x.dim() != 2 or x.shape[1] != hidden or y.shape != x.shape:
+                raise IncompatibleShapes(f"member {i}: x and y must be [M,{hidden}], got {list(x.shape)} and {list(y.shape)}")
+            for name, w, n, k in (("gate", wg, ffn, hidden), ("up", wu, ffn, hidden), ("down", wd, hidden, ffn)):
+                if w.dtype != torch.uint8 or not w.is_contiguous() or w.numel() != n * k // 4:
+                    raise IncompatibleShapes(f"member {i}: packed {name} weights must hold {n}x{k}/4 bytes")
+            arr[i] = L.FfnGroupMember(wg.data_ptr(), wu.data_ptr(), wd.data_ptr(), sg, su, sd, x.data_ptr(), y.data_ptr(), x.shape[0])
+            self._keep.append((wg, wu, wd, x, y))
+        self._device = members[0][6].device if members else None
+        handle = C.c_void_p()
+        with torch.cuda.device(self._device):
+            check(L.load().bitnet_ffn_group_create(arr, len(members), hidden, ffn, C.byref(handle)))
+        self._handle = handle
+
+    def run(self, stream=None) -> None:
+        check(L.load().bitnet_ffn_group_run(self._handle, _stream(stream)))
+
+    def close(self) -> None:
+        if getattr(self, "_handle", None):
+            L.load().bitnet_ffn_group_destroy(self._handle)
+            self._handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 def row_glue(x: torch.Tensor, glue: L.RowGlue, stream=None) -> None:
     """The glue alone: writes x + residual to glue.sum_out and SubLN(x + residual) to glue.normed_out."""
     x = _require(x, torch.float32, "x")

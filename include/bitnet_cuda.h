@@ -449,6 +449,30 @@ bitnet_status_t bitnet_backend_ffn_plan_create(bitnet_backend *b, const bitnet_f
 bitnet_status_t bitnet_backend_ffn_plan_run(bitnet_ffn_plan *plan);
 void bitnet_backend_ffn_plan_destroy(bitnet_ffn_plan *plan);
 
+/* ---- a group of independent FFN blocks as four launches ------------------------------------------------
+ * Decode-time blocks of one shape (hidden -> ffn -> hidden, at most 16 tokens each) that do not depend on one
+ * another: the same computation as bitnet_ffn_forward per member (FeedForwardNetwork::forward,
+ * bitnet-inference/src/engine/transformer_layers.rs:608-629), bit for bit, but the whole group runs as one
+ * quantiser launch + one persistent gate/up launch + one quantiser launch + one persistent down launch, each
+ * streaming the weights of ALL members (a block of a 2B-class model alone is too short a launch to bring the
+ * memory system to speed).  The reference has no counterpart: its caller loops over the blocks.
+ * Creation (on the current device) binds every member's device pointers and allocates the group's scratch
+ * (tables, quantised-activation images, the gated intermediate); a run enqueues the four launches on `stream`
+ * and may be captured into a CUDA graph.  The caller refreshes the bound x buffers between runs; one run at a
+ * time per group.  Needs hidden % 64 == 0 (<= 8192), ffn % 64 == 0 (<= 16384), 16-byte aligned buffers. */
+typedef struct bitnet_ffn_group bitnet_ffn_group;
+typedef struct bitnet_ffn_group_member {
+    const uint8_t *gate_packed_dev, *up_packed_dev, *down_packed_dev; /* canonical packed [ffn,hidden/4], [ffn,hidden/4], [hidden,ffn/4] */
+    float gate_scale, up_scale, down_scale;
+    const float *x_dev;   /* [M, hidden] */
+    float *y_dev;         /* [M, hidden] */
+    size_t M;             /* 1..16 */
+} bitnet_ffn_group_member;
+bitnet_status_t bitnet_ffn_group_create(const bitnet_ffn_group_member *members, size_t n_members, size_t hidden,
+                                        size_t ffn, bitnet_ffn_group **out);
+bitnet_status_t bitnet_ffn_group_run(bitnet_ffn_group *group, cudaStream_t stream);
+void bitnet_ffn_group_destroy(bitnet_ffn_group *group);
+
 /* ---- exchange step of the output-feature-split layer ------------------------------------------------- */
 /* Every GPU holds y[:, its column slice]; all need y[M, N].  No counterpart in the reference, which has no
  * multi-GPU code.
