@@ -71,6 +71,16 @@ __device__ __forceinline__ void mma_u8s8(int (&d)[4], unsigned a0, unsigned a1, 
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// The same step starting an accumulator: D = A x B with a zero C that costs no register moves.
+__device__ __forceinline__ void mma_u8s8_first(int (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                               unsigned b0, unsigned b1)
+{
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
 __device__ __forceinline__ unsigned word_of(const uint4 &v, int i)
 {
     return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w));

@@ -41,8 +41,10 @@ struct GroupParams {
     const int *cta_member;       // per CTA: the member that holds the first block of its share
     int total_blocks;
     int K, chunks, cw, stages;
-    unsigned stage_stride, bst_offset, red_offset, zero_offset;
+    unsigned stage_stride, bst_offset, red_offset;
 };
+
+constexpr int GROUP_MAX_STAGES = 12;
 
 __device__ __forceinline__ void group_barrier(int threads)
 {
@@ -62,17 +64,20 @@ __global__ void __launch_bounds__(512) group_quantize_kernel(const GroupMember *
 
 // NT: token tiles of 8; SW: loop steps per warp (a step is 4 chunks = 256 k per warp); DUAL: gate/up pair with the
 // ReLU^2 gating in the epilogue.  Consumer warps: p.cw (blockDim.x / 32 - 1), each owning a K slice of every block.
-// Dynamic shared memory: the weight ring, the staging area of one member's image, the K-split sums per stage, and
-// 16 zero bytes that chunks past a warp's slice read as weights.
-template <int NT, int SW, bool DUAL>
-__global__ void __launch_bounds__(NT == 1 ? 512 : 288, 1) decode_group_kernel(const GroupParams p)
+// Dynamic shared memory: the weight ring (every stage ends in 128 bytes of padding that no copy writes: its first
+// 16 bytes are zeroed once and are what chunks past a warp's K slice read as weights), the staging area of one
+// member's image, and the K-split sums per stage.
+// MAXT: thread bound (384 leaves 168 registers a thread).  One CTA per SM: two smaller CTAs per SM (half the ring
+// each, twice the warps) measured 15 % slower, and so did computing two blocks per pass (a stage is held longer).
+template <int NT, int SW, bool DUAL, int MAXT>
+__global__ void __launch_bounds__(MAXT, 1) decode_group_kernel(const GroupParams p)
 {
     constexpr int NW = DUAL ? 2 : 1;
     constexpr int NTD = NT * NW;
     constexpr bool BREG = NT == 1;   // activations of the current member in registers
 
     extern __shared__ __align__(128) unsigned char smem[];
-    __shared__ __align__(8) unsigned long long s_full[DEC_MAX_STAGES], s_done[DEC_MAX_STAGES], s_empty[DEC_MAX_STAGES];
+    __shared__ __align__(8) unsigned long long s_full[GROUP_MAX_STAGES], s_done[GROUP_MAX_STAGES], s_empty[GROUP_MAX_STAGES];
     __shared__ __align__(8) unsigned long long s_img;
     __shared__ unsigned s_dead;   // a bounded wait gave up somewhere in the CTA: everybody stops at the next member
 
@@ -81,6 +86,8 @@ __global__ void __launch_bounds__(NT == 1 ? 512 : 288, 1) decode_group_kernel(co
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, tig = lane & 3;
     const int CW = p.cw, NS = p.stages;
+    // A contiguous share of the block list per CTA, so that it meets only the few members its share crosses (dealing
+    // the blocks of a run round-robin to a team of CTAs, for wider streams in DRAM, measured slower at every team size).
     const int g0 = (int)((long long)blockIdx.x * p.total_blocks / gridDim.x);
     const int g1 = (int)((long long)(blockIdx.x + 1) * p.total_blocks / gridDim.x);
     const unsigned row_bytes = (unsigned)p.K / 4;
@@ -99,7 +106,8 @@ __global__ void __launch_bounds__(NT == 1 ? 512 : 288, 1) decode_group_kernel(co
         s_dead = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (tid < 4) reinterpret_cast<unsigned *>(smem + p.zero_offset)[tid] = 0;
+    for (int z = tid; z < NS * 4; z += (int)blockDim.x)
+        reinterpret_cast<unsigned *>(smem + (size_t)(z >> 2) * p.stage_stride + (size_t)NW * 16 * row_bytes)[z & 3] = 0;
     __syncthreads();
 
     // ======================= producer warp: keep the ring full, across members ===============================
@@ -139,8 +147,9 @@ __global__ void __launch_bounds__(NT == 1 ? 512 : 288, 1) decode_group_kernel(co
     const int cw1 = (int)((long long)(warp + 1) * p.chunks / CW);
     const int Cw = cw1 - cw0;                              // chunks of this warp's K slice (<= 4*SW)
 
-    // Byte offsets of this lane's 16-byte chunks inside a stage; a chunk beyond the slice reads the zero region.
-    constexpr unsigned OFF_ZERO = 0xffffffffu;
+    // Byte offsets of this lane's 16-byte chunks inside a stage; a chunk beyond the slice reads the stage's zeroed
+    // padding (its activation fragments were never written and hold stale bytes).
+    const unsigned OFF_ZERO = (unsigned)NW * 16 * row_bytes;
     unsigned off_a[NW][SW], off_b[NW][SW];
 #pragma unroll
     for (int w = 0; w < NW; ++w)
@@ -167,45 +176,65 @@ __global__ void __launch_bounds__(NT == 1 ? 512 : 288, 1) decode_group_kernel(co
         const GroupMember mb = p.members[mi];
         const int seg_end = min(g1, p.members[mi + 1].blk_begin);
 
-        group_barrier(CW * 32);                            // every warp is through with the previous member's image
-        if (*reinterpret_cast<volatile unsigned *>(&s_dead)) break;
-        if (tid == 0) {
-            mbar_arrive_expect_tx(&s_img, mb.image_bytes);
-            bulk_copy_g2s(s_bst, mb.image, mb.image_bytes, &s_img);
-        }
-        bool ok = mbar_wait(&s_img, seg & 1u);
-
         // a fragment block holds 16 bytes for each (token row, k quad); only the token rows that exist are kept
         const unsigned frag_blk = (unsigned)mb.mrows * 64u;
         // lanes of token rows that do not exist feed accumulator columns nobody reads: they re-read lane 0's bytes
         const unsigned frag_lane_off = ((unsigned)lane < (unsigned)mb.mrows * 4u ? (unsigned)lane : 0u) * 16u;
-        const unsigned char *bst = s_bst + DEC_IMG_HDR + (size_t)warp * (SW * 4 * NT) * frag_blk;
-        const int *hdr_sumq = reinterpret_cast<const int *>(s_bst);
+        const size_t warp_region = DEC_IMG_HDR + (size_t)warp * (SW * 4 * NT) * frag_blk;
+        const unsigned char *bst = s_bst + warp_region;
         const float *hdr_ascale = reinterpret_cast<const float *>(s_bst + DEC_MAX_CWARPS * DEC_MAX_TOKENS * 4);
 
         uint4 breg[BREG ? SW : 1][4][NT];
-        int sq[NT][2];
-        if (ok) {
-            if constexpr (BREG) {
+        int sq[NT][2];        // sum_k q of the whole row: the +1 of the weight code is taken out once per output
+        float asc[NT][2];     // absmax / 127 of this lane's two tokens per tile
+        bool ok = true;
+        if constexpr (BREG) {
+            // One tile of tokens: the member's image goes from global memory (L2: the quantiser launch just wrote it)
+            // straight into registers, so no shared memory is spent on it and the ring gets that room.
+            const unsigned char *img = mb.image;
+            const int *g_sumq = reinterpret_cast<const int *>(img);
+            const float *g_ascale = reinterpret_cast<const float *>(img + DEC_MAX_CWARPS * DEC_MAX_TOKENS * 4);
 #pragma unroll
-                for (int s2 = 0; s2 < SW; ++s2)
+            for (int s2 = 0; s2 < SW; ++s2)
 #pragma unroll
-                    for (int i2 = 0; i2 < 4; ++i2)
+                for (int i2 = 0; i2 < 4; ++i2)
 #pragma unroll
-                        for (int t = 0; t < NT; ++t)
-                            breg[s2][i2][t] = *reinterpret_cast<const uint4 *>(bst + (size_t)((s2 * 4 + i2) * NT + t) * frag_blk + frag_lane_off);
+                    for (int t = 0; t < NT; ++t)
+                        breg[s2][i2][t] = __ldg(reinterpret_cast<const uint4 *>(img + warp_region + (size_t)((s2 * 4 + i2) * NT + t) * frag_blk + frag_lane_off));
+#pragma unroll
+            for (int t = 0; t < NT; ++t)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    sq[t][e] = 0;
+                    for (int w2 = 0; w2 < CW; ++w2) sq[t][e] += __ldg(g_sumq + w2 * DEC_MAX_TOKENS + 8 * t + 2 * tig + e);
+                    asc[t][e] = __ldg(g_ascale + 8 * t + 2 * tig + e);
+                }
+        } else {
+            group_barrier(CW * 32);                        // every warp is through with the previous member's image
+            if (*reinterpret_cast<volatile unsigned *>(&s_dead)) break;
+            if (tid == 0) {
+                mbar_arrive_expect_tx(&s_img, mb.image_bytes);
+                bulk_copy_g2s(s_bst, mb.image, mb.image_bytes, &s_img);
             }
+            ok = mbar_wait(&s_img, seg & 1u);
+            if (ok) {
+                const int *hdr_sumq = reinterpret_cast<const int *>(s_bst);
 #pragma unroll
-            for (int t = 0; t < NT; ++t) {
-                sq[t][0] = hdr_sumq[warp * DEC_MAX_TOKENS + 8 * t + 2 * tig];
-                sq[t][1] = hdr_sumq[warp * DEC_MAX_TOKENS + 8 * t + 2 * tig + 1];
+                for (int t = 0; t < NT; ++t)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        sq[t][e] = 0;
+                        for (int w2 = 0; w2 < CW; ++w2) sq[t][e] += hdr_sumq[w2 * DEC_MAX_TOKENS + 8 * t + 2 * tig + e];
+                        asc[t][e] = hdr_ascale[8 * t + 2 * tig + e];
+                    }
             }
         }
 
         const int nbs = seg_end - gb;
         const int i_end = i + nbs;
         const int local0 = gb - mb.blk_begin - i;          // block `pos` of the ring is the member's block local0 + pos
-        // a stage is refilled only after its block was finished, so the deferral must stay below the ring depth
+        // a stage is refilled only after its block was finished (handing it back as soon as every warp had read it,
+        // with the sums guarded by a barrier of their own, measured slower), so the deferral must stay below the ring depth
         const int defer = (nbs >= 6 && NS > 1) ? 1 : 0;
 
         // Finishes block j if this warp is on duty for it: waits until every warp's partial sums of the block are
@@ -235,14 +264,15 @@ __global__ void __launch_bounds__(NT == 1 ? 512 : 288, 1) decode_group_kernel(co
                     const int row = (r & 2) ? row_b : row_a;
                     if (m < mb.M && row < mb.N) {
                         const size_t o = (size_t)m * mb.ldy + row;
-                        const float a = hdr_ascale[m];
+                        const float a = asc[t][r & 1];
+                        const int rs = sq[t][r & 1];
                         if constexpr (DUAL) {
-                            const float gate = __fmul_rn((float)tot[t][r], __fmul_rn(mb.w_scale, a));
-                            const float up = __fmul_rn((float)tot[NT + t][r], __fmul_rn(mb.w_scale2, a));
+                            const float gate = __fmul_rn((float)((tot[t][r] >> 6) - rs), __fmul_rn(mb.w_scale, a));
+                            const float up = __fmul_rn((float)((tot[NT + t][r] >> 6) - rs), __fmul_rn(mb.w_scale2, a));
                             const float rl = fmaxf(gate, 0.0f);
                             mb.y[o] = __fmul_rn(up, __fmul_rn(rl, rl));
                         } else {
-                            mb.y[o] = __fmul_rn((float)tot[t][r], __fmul_rn(mb.w_scale, a));
+                            mb.y[o] = __fmul_rn((float)((tot[t][r] >> 6) - rs), __fmul_rn(mb.w_scale, a));
                         }
                     }
                 }
@@ -252,19 +282,10 @@ __global__ void __launch_bounds__(NT == 1 ? 512 : 288, 1) decode_group_kernel(co
             if (!mbar_wait(&s_full[s], parity)) { ok = false; break; }
             const unsigned stage_off = (unsigned)s * p.stage_stride;
 
-            int acc[NW][NT][4][4];   // [matrix][token tile][j class][fragment register]
-#pragma unroll
-            for (int w = 0; w < NW; ++w)
-#pragma unroll
-                for (int t = 0; t < NT; ++t)
-#pragma unroll
-                    for (int j = 0; j < 4; ++j)
-#pragma unroll
-                        for (int r = 0; r < 4; ++r) acc[w][t][j][r] = 0;
-
+            int acc[NW][NT][4][4];   // [matrix][token tile][j class][fragment register]; the first step starts them
 #pragma unroll
             for (int s2 = 0; s2 < SW; ++s2) {
-                if (s2 * 4 < Cw) {   // warp-uniform: this step holds at least one chunk of the slice
+                if (s2 == 0 || s2 * 4 < Cw) {   // warp-uniform: this step holds at least one chunk of the slice
                     uint4 bw[4][NT];
 #pragma unroll
                     for (int i2 = 0; i2 < 4; ++i2)
@@ -275,8 +296,8 @@ __global__ void __launch_bounds__(NT == 1 ? 512 : 288, 1) decode_group_kernel(co
                         }
 #pragma unroll
                     for (int w = 0; w < NW; ++w) {
-                        const uint4 wa = *reinterpret_cast<const uint4 *>(smem + (off_a[w][s2] != OFF_ZERO ? stage_off + off_a[w][s2] : p.zero_offset));
-                        const uint4 wb = *reinterpret_cast<const uint4 *>(smem + (off_b[w][s2] != OFF_ZERO ? stage_off + off_b[w][s2] : p.zero_offset));
+                        const uint4 wa = *reinterpret_cast<const uint4 *>(smem + stage_off + off_a[w][s2]);
+                        const uint4 wb = *reinterpret_cast<const uint4 *>(smem + stage_off + off_b[w][s2]);
 #pragma unroll
                         for (int pr = 0; pr < 2; ++pr) {
                             const unsigned a_lo0 = word_of(wa, 2 * pr), a_lo1 = word_of(wa, 2 * pr + 1);
@@ -285,16 +306,21 @@ __global__ void __launch_bounds__(NT == 1 ? 512 : 288, 1) decode_group_kernel(co
                             for (int j = 0; j < 4; ++j) {
                                 const unsigned mask = 0x03030303u << (2 * j);
 #pragma unroll
-                                for (int t = 0; t < NT; ++t)
-                                    mma_u8s8(acc[w][t][j], a_lo0 & mask, a_hi0 & mask, a_lo1 & mask, a_hi1 & mask,
-                                             word_of(bw[2 * pr][t], j), word_of(bw[2 * pr + 1][t], j));
+                                for (int t = 0; t < NT; ++t) {
+                                    if (s2 == 0 && pr == 0)
+                                        mma_u8s8_first(acc[w][t][j], a_lo0 & mask, a_hi0 & mask, a_lo1 & mask, a_hi1 & mask,
+                                                       word_of(bw[0][t], j), word_of(bw[1][t], j));
+                                    else
+                                        mma_u8s8(acc[w][t][j], a_lo0 & mask, a_hi0 & mask, a_lo1 & mask, a_hi1 & mask,
+                                                 word_of(bw[2 * pr][t], j), word_of(bw[2 * pr + 1][t], j));
+                                }
                             }
                         }
                     }
                 }
             }
-
-            // exact partial sums of sum_k (code-1)*q over this warp's K slice, left in this warp's slot
+            // 64 x this warp's exact partial sum of sum_k code*q: class j holds 4^j times its share, so
+            // ((acc0*4 + acc1)*4 + acc2)*4 + acc3 needs no division; the warp on duty divides the total once
             int4 *red = reinterpret_cast<int4 *>(s_red) + (size_t)s * (CW * NTD * 32);
 #pragma unroll
             for (int w = 0; w < NW; ++w)
@@ -303,7 +329,7 @@ __global__ void __launch_bounds__(NT == 1 ? 512 : 288, 1) decode_group_kernel(co
                     int v[4];
 #pragma unroll
                     for (int r = 0; r < 4; ++r)
-                        v[r] = acc[w][t][0][r] + (acc[w][t][1][r] >> 2) + (acc[w][t][2][r] >> 4) + (acc[w][t][3][r] >> 6) - sq[t][r & 1];
+                        v[r] = ((acc[w][t][0][r] * 4 + acc[w][t][1][r]) * 4 + acc[w][t][2][r]) * 4 + acc[w][t][3][r];
                     red[(warp * NTD + w * NT + t) * 32 + lane] = make_int4(v[0], v[1], v[2], v[3]);
                 }
             __syncwarp();
@@ -318,7 +344,12 @@ __global__ void __launch_bounds__(NT == 1 ? 512 : 288, 1) decode_group_kernel(co
             }
         }
         for (; jn < i_end && ok; ++jn, advance(sj, pj)) finish_block(jn);
-        if (!ok) *reinterpret_cast<volatile unsigned *>(&s_dead) = 1u;
+        if (!ok) {
+            // a wait gave up: without a staging area nothing else holds the warps together, this one just stops;
+            // with one, everybody stops at the next member's barrier
+            if constexpr (BREG) return;
+            *reinterpret_cast<volatile unsigned *>(&s_dead) = 1u;
+        }
         gb = seg_end;
     }
 }
@@ -343,7 +374,7 @@ int group_mrows(size_t M) { return M > 4 ? 8 : (M > 2 ? 4 : (M > 1 ? 2 : 1)); }
 struct GroupStage {
     int K = 0, nt = 1, sw = 1, cw = 0, stages = 0, grid = 0, total_blocks = 0, total_tokens = 0;
     bool dual = false;
-    unsigned stage_stride = 0, bst_offset = 0, red_offset = 0, zero_offset = 0;
+    unsigned stage_stride = 0, bst_offset = 0, red_offset = 0;
     size_t smem = 0;
     size_t image_stride = 0;          // bytes between members' images
     GroupMember *members_dev = nullptr;
@@ -370,26 +401,26 @@ bitnet_status_t group_stage_plan(GroupStage &st, size_t K, size_t max_M, bool du
     const int nw = dual ? 2 : 1;
     const unsigned row_bytes = (unsigned)K / 4;
     st.stage_stride = (unsigned)nw * 16 * row_bytes + 128;
-    const size_t bst_bytes = align_up(DEC_IMG_HDR + (size_t)st.cw * st.sw * 4 * st.nt * (size_t)group_mrows(max_M) * 64, 128);
-    st.image_stride = align_up(bst_bytes, 256);
+    const size_t image_bytes = align_up(DEC_IMG_HDR + (size_t)st.cw * st.sw * 4 * st.nt * (size_t)group_mrows(max_M) * 64, 128);
+    st.image_stride = align_up(image_bytes, 256);
+    const size_t bst_bytes = st.nt == 1 ? 0 : image_bytes;   // one token tile: the image lives in registers, not in shared memory
     const size_t red_per_stage = (size_t)st.cw * nw * st.nt * 512;
-    const size_t budget = 208 * 1024;
+    const size_t budget = 226 * 1024;   // all of an SM's shared memory: the ring's depth is the bytes in flight
     if (bst_bytes + 2 * (st.stage_stride + red_per_stage) > budget)
         return fail(BITNET_ERR_UNSUPPORTED_OPERATION, "grouped decode: K=%zu at %zu tokens does not fit shared memory", K, max_M);
     int stages = (int)((budget - bst_bytes) / (st.stage_stride + red_per_stage));
-    if (stages > DEC_MAX_STAGES) stages = DEC_MAX_STAGES;
+    if (stages > GROUP_MAX_STAGES) stages = GROUP_MAX_STAGES;
     st.stages = stages;
     st.bst_offset = (unsigned)stages * st.stage_stride;
     st.red_offset = st.bst_offset + (unsigned)bst_bytes;
-    st.zero_offset = st.red_offset + (unsigned)(stages * red_per_stage);
-    st.smem = (size_t)st.zero_offset + 16;
+    st.smem = (size_t)st.red_offset + (size_t)stages * red_per_stage;
     return BITNET_OK;
 }
 
-template <int NT, int SW, bool DUAL>
+template <int NT, int SW, bool DUAL, int MAXT>
 bitnet_status_t group_launch_one(const GroupStage &st, const GroupParams &p, cudaStream_t stream)
 {
-    auto kernel = decode_group_kernel<NT, SW, DUAL>;
+    auto kernel = decode_group_kernel<NT, SW, DUAL, MAXT>;
     {
         static std::mutex mu;
         static bool raised[64] = {false};
@@ -423,10 +454,26 @@ bitnet_status_t group_launch_one(const GroupStage &st, const GroupParams &p, cud
 template <int NT, bool DUAL>
 bitnet_status_t group_launch_sw(const GroupStage &st, const GroupParams &p, cudaStream_t stream)
 {
-    if (st.sw == 1) return group_launch_one<NT, 1, DUAL>(st, p, stream);
-    if (st.sw == 2) return group_launch_one<NT, 2, DUAL>(st, p, stream);
-    if constexpr (!DUAL) {
-        if (st.sw == 4) return group_launch_one<NT, 4, false>(st, p, stream);
+    if constexpr (NT == 1) {
+        // up to eleven warps: 168 registers a thread, room for two blocks of a gate/up pair per pass
+        if ((st.cw + 1) * 32 <= 384) {
+            if (st.sw == 1) return group_launch_one<1, 1, DUAL, 384>(st, p, stream);
+            if (st.sw == 2) return group_launch_one<1, 2, DUAL, 384>(st, p, stream);
+        }
+        if constexpr (!DUAL) {
+            if (st.sw == 1) return group_launch_one<1, 1, false, 512>(st, p, stream);
+            if (st.sw == 2) return group_launch_one<1, 2, false, 512>(st, p, stream);
+            if (st.sw == 4) return group_launch_one<1, 4, false, 512>(st, p, stream);
+        } else {
+            if (st.sw == 1) return group_launch_one<1, 1, true, 512>(st, p, stream);
+            if (st.sw == 2) return group_launch_one<1, 2, true, 512>(st, p, stream);
+        }
+    } else {
+        if (st.sw == 1) return group_launch_one<2, 1, DUAL, 288>(st, p, stream);
+        if (st.sw == 2) return group_launch_one<2, 2, DUAL, 288>(st, p, stream);
+        if constexpr (!DUAL) {
+            if (st.sw == 4) return group_launch_one<2, 4, false, 288>(st, p, stream);
+        }
     }
     return fail(BITNET_ERR_UNSUPPORTED_OPERATION, "grouped decode: no kernel for this width");
 }
@@ -455,7 +502,6 @@ bitnet_status_t group_stage_run(const GroupStage &st, cudaStream_t stream)
     p.stage_stride = st.stage_stride;
     p.bst_offset = st.bst_offset;
     p.red_offset = st.red_offset;
-    p.zero_offset = st.zero_offset;
     if (st.dual) return st.nt == 1 ? group_launch_sw<1, true>(st, p, stream) : group_launch_sw<2, true>(st, p, stream);
     return st.nt == 1 ? group_launch_sw<1, false>(st, p, stream) : group_launch_sw<2, false>(st, p, stream);
 }
@@ -515,7 +561,7 @@ bitnet_status_t group_stage_build(GroupStage &st, const std::vector<StageMemberI
     dev += align_up((size_t)sms * sizeof(int), 256);
     st.token_member_dev = reinterpret_cast<int *>(dev);
     BITNET_CUDA(cudaMemcpy(st.members_dev, members.data(), (n + 1) * sizeof(GroupMember), cudaMemcpyHostToDevice));
-    BITNET_CUDA(cudaMemcpy(st.cta_member_dev, cta_member.data(), (size_t)sms * sizeof(int), cudaMemcpyHostToDevice));
+    BITNET_CUDA(cudaMemcpy(st.cta_member_dev, cta_member.data(), cta_member.size() * sizeof(int), cudaMemcpyHostToDevice));
     BITNET_CUDA(cudaMemcpy(st.token_member_dev, token_member.data(), token_member.size() * sizeof(int), cudaMemcpyHostToDevice));
     return BITNET_OK;
 }
