@@ -497,8 +497,9 @@ def run_cuda(args):
                                    "launch in it is this kernel or its quantiser)"},
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": io_bytes, "d2h_bytes_per_step": io_bytes,
                     "steps": e2e_steps,
-                    "api": f"bitnet_backend_ffn_plan_run: the step's 90 FFN blocks bound to page-locked host buffers, dealt to "
-                           f"{n_streams} streams; per block H2D of x, the launches, D2H of y",
+                    "api": "bitnet_backend_ffn_plan_run: the step's 90 FFN blocks bound to page-locked host buffers, run as three "
+                           "groups; per group one launch copies its inputs host->device, four launches compute, one launch copies "
+                           "its outputs device->host (copies of one group overlap the kernels of another)",
                     "per_call_async": {"value": e2e_async, "unit": "GB/s",
                                        "api": f"bitnet_backend_ffn_forward_host_async on {E2E_STREAMS} streams, one host thread "
                                               "each, + bitnet_backend_synchronize per step"}},

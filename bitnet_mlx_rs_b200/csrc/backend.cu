@@ -647,6 +647,22 @@ bool host_ptr_is_pinned(const void *p)
     return attr.type == cudaMemoryTypeHost;
 }
 
+// One piece (at most 8 KB) of a copy between page-locked host memory, through its device alias, and device memory.
+struct CopyChunk {
+    const uint4 *src;
+    uint4 *dst;
+    unsigned units;   // 16-byte units
+};
+
+// Many small host<->device copies as one launch: the SMs move the bytes over the host link themselves (every
+// 16-byte unit is one request in flight), where a copy-engine transfer per buffer costs microseconds each.
+__global__ void __launch_bounds__(256) plan_copy_kernel(const CopyChunk *__restrict__ chunks)
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const CopyChunk c = chunks[blockIdx.x];
+    for (unsigned u = threadIdx.x; u < c.units; u += 256) c.dst[u] = c.src[u];
+}
+
 struct PlanCall {
     const Weights *gate, *up, *down;
     size_t M;
@@ -656,6 +672,8 @@ struct PlanCall {
     const float *x_src;   // what the in-graph copy reads: the caller's pinned buffer or this plan's staging
     float *y_dst;
     float *x_dev, *h_dev, *y_dev;
+    const float *x_src_alias;   // device-side aliases of x_src / y_dst (null when the host memory is not mapped)
+    float *y_dst_alias;
     void *ws;
     size_t ws_bytes;
 };
@@ -674,6 +692,15 @@ struct bitnet_ffn_plan {
     bitnet_forward_opts opts = {};
     std::mutex mu;
     size_t bytes_per_run = 0;
+    // Equal shapes and at most 16 tokens per call: the calls run as a few grouped launches (bitnet_ffn_group_*)
+    // instead of two to four launches each; groups[g] covers calls [group_first[g], group_first[g + 1]).
+    std::vector<bitnet_ffn_group *> groups;
+    std::vector<size_t> group_first;
+    std::vector<cudaEvent_t> group_events;   // per group: one per lane (its inputs are on the device), then one (its kernels are done)
+    // When every bound host buffer is mapped into the device's address space, a group's inputs and outputs move
+    // by one copy launch each (plan_copy_kernel) instead of one copy-engine transfer per buffer.
+    CopyChunk *chunks_dev = nullptr;
+    std::vector<unsigned> in_first, in_count, out_first, out_count;   // per group: its chunks in chunks_dev
 };
 
 static void plan_release(bitnet_ffn_plan *p)
@@ -684,6 +711,9 @@ static void plan_release(bitnet_ffn_plan *p)
     if (p->exec) cudaGraphExecDestroy(p->exec);
     if (p->graph) cudaGraphDestroy(p->graph);
     for (cudaEvent_t e : p->events) cudaEventDestroy(e);
+    for (cudaEvent_t e : p->group_events) cudaEventDestroy(e);
+    for (bitnet_ffn_group *g : p->groups) bitnet_ffn_group_destroy(g);
+    if (p->chunks_dev) cudaFree(p->chunks_dev);
     for (cudaStream_t s : p->lanes) cudaStreamDestroy(s);
     if (p->pin_slab) cudaFreeHost(p->pin_slab);
     if (p->dev_slab && p->backend) p->backend->impl.memory->release(p->dev_slab);
@@ -698,6 +728,65 @@ static bitnet_status_t plan_enqueue(bitnet_ffn_plan *p)
     cudaStream_t origin = p->lanes[0];
     BITNET_CUDA(cudaEventRecord(p->events[0], origin));
     for (size_t l = 1; l < L; ++l) BITNET_CUDA(cudaStreamWaitEvent(p->lanes[l], p->events[0], 0));
+    if (!p->groups.empty()) {
+        // Every input copy is queued first, dealt to the lanes; group g starts on the origin stream when ITS inputs
+        // have landed (later groups' copies keep running beside its kernels), and its outputs leave on the lanes
+        // while the next group computes.
+        const size_t G = p->groups.size();
+        auto ev = [&](size_t g, size_t k) { return p->group_events[g * (L + 1) + k]; };
+        if (p->chunks_dev) {
+            // copy launches: inputs of all groups on one lane, kernels on the origin stream, outputs on another lane
+            cudaStream_t in_s = L > 1 ? p->lanes[1] : origin, out_s = L > 2 ? p->lanes[2] : in_s;
+            auto copy = [&](unsigned first, unsigned count, cudaStream_t s) -> bitnet_status_t {
+                BITNET_CUDA(cudaGetLastError());
+                plan_copy_kernel<<<count, 256, 0, s>>>(p->chunks_dev + first);
+                BITNET_CUDA(cudaGetLastError());
+                return BITNET_OK;
+            };
+            for (size_t g = 0; g < G; ++g) {
+                BITNET_TRY(copy(p->in_first[g], p->in_count[g], in_s));
+                if (in_s != origin) BITNET_CUDA(cudaEventRecord(ev(g, 1), in_s));
+            }
+            for (size_t g = 0; g < G; ++g) {
+                if (in_s != origin) BITNET_CUDA(cudaStreamWaitEvent(origin, ev(g, 1), 0));
+                BITNET_TRY(bitnet_ffn_group_run(p->groups[g], origin));
+                if (out_s != origin) {
+                    BITNET_CUDA(cudaEventRecord(ev(g, L), origin));
+                    BITNET_CUDA(cudaStreamWaitEvent(out_s, ev(g, L), 0));
+                }
+                BITNET_TRY(copy(p->out_first[g], p->out_count[g], out_s));
+            }
+            for (size_t l = 1; l < L; ++l) {
+                BITNET_CUDA(cudaEventRecord(p->events[l], p->lanes[l]));
+                BITNET_CUDA(cudaStreamWaitEvent(origin, p->events[l], 0));
+            }
+            return BITNET_OK;
+        }
+        // the origin stream carries the kernels; copies go to the other lanes when there are any
+        auto copy_lane = [&](size_t i) { return L > 1 ? p->lanes[1 + i % (L - 1)] : origin; };
+        for (size_t g = 0; g < G; ++g) {
+            for (size_t i = p->group_first[g]; i < p->group_first[g + 1]; ++i) {
+                const PlanCall &c = p->calls[i];
+                BITNET_CUDA(cudaMemcpyAsync(c.x_dev, c.x_src, c.M * c.gate->K * sizeof(float), cudaMemcpyHostToDevice, copy_lane(i)));
+            }
+            for (size_t l = 1; l < L; ++l) BITNET_CUDA(cudaEventRecord(ev(g, l), p->lanes[l]));
+        }
+        for (size_t g = 0; g < G; ++g) {
+            for (size_t l = 1; l < L; ++l) BITNET_CUDA(cudaStreamWaitEvent(origin, ev(g, l), 0));
+            BITNET_TRY(bitnet_ffn_group_run(p->groups[g], origin));
+            BITNET_CUDA(cudaEventRecord(ev(g, L), origin));
+            for (size_t l = 1; l < L; ++l) BITNET_CUDA(cudaStreamWaitEvent(p->lanes[l], ev(g, L), 0));
+            for (size_t i = p->group_first[g]; i < p->group_first[g + 1]; ++i) {
+                const PlanCall &c = p->calls[i];
+                BITNET_CUDA(cudaMemcpyAsync(c.y_dst, c.y_dev, c.M * c.gate->K * sizeof(float), cudaMemcpyDeviceToHost, copy_lane(i)));
+            }
+        }
+        for (size_t l = 1; l < L; ++l) {
+            BITNET_CUDA(cudaEventRecord(p->events[l], p->lanes[l]));
+            BITNET_CUDA(cudaStreamWaitEvent(origin, p->events[l], 0));
+        }
+        return BITNET_OK;
+    }
     for (size_t i = 0; i < p->calls.size(); ++i) {
         const PlanCall &c = p->calls[i];
         cudaStream_t s = p->lanes[i % L];
@@ -711,6 +800,81 @@ static bitnet_status_t plan_enqueue(bitnet_ffn_plan *p)
         BITNET_CUDA(cudaEventRecord(p->events[l], p->lanes[l]));
         BITNET_CUDA(cudaStreamWaitEvent(origin, p->events[l], 0));
     }
+    return BITNET_OK;
+}
+
+// Groups the plan's calls when they qualify (one shape, at most 16 tokens each, automatic path); otherwise the plan
+// keeps its per-call launches.  Three groups at most, of a few dozen calls each: a group's four launches cost a
+// fixed twenty-odd microseconds, and more groups let copies of one overlap the kernels of another.
+static bitnet_status_t plan_build_groups(bitnet_ffn_plan *p)
+{
+    const size_t n = p->calls.size();
+    if (n < 2 || (p->opts.path != BITNET_PATH_AUTO && p->opts.path != BITNET_PATH_DECODE)) return BITNET_OK;
+    const size_t hidden = p->calls[0].gate->K, ffn = p->calls[0].gate->N;
+    for (const PlanCall &c : p->calls)
+        if (c.gate->K != hidden || c.gate->N != ffn || c.M > 16) return BITNET_OK;
+    if (hidden % 64 || ffn % 64 || hidden > 8192 || ffn > 16384) return BITNET_OK;
+    size_t G = n / 24;
+    if (G < 1) G = 1;
+    if (G > 3) G = 3;
+    const size_t L = p->lanes.size();
+    std::vector<bitnet_ffn_group_member> members(n);
+    for (size_t i = 0; i < n; ++i) {
+        const PlanCall &c = p->calls[i];
+        members[i] = bitnet_ffn_group_member{static_cast<const uint8_t *>(c.gate->packed_dev), static_cast<const uint8_t *>(c.up->packed_dev),
+                                             static_cast<const uint8_t *>(c.down->packed_dev), c.gate->w_scale, c.up->w_scale, c.down->w_scale,
+                                             c.x_dev, c.y_dev, c.M};
+    }
+    for (size_t g = 0; g <= G; ++g) p->group_first.push_back(g * n / G);
+    for (size_t g = 0; g < G; ++g) {
+        bitnet_ffn_group *grp = nullptr;
+        const bitnet_status_t st = bitnet_ffn_group_create(members.data() + p->group_first[g], p->group_first[g + 1] - p->group_first[g], hidden, ffn, &grp);
+        if (st == BITNET_ERR_UNSUPPORTED_OPERATION) {   // this shape has no grouped kernel: per-call launches
+            for (bitnet_ffn_group *q : p->groups) bitnet_ffn_group_destroy(q);
+            p->groups.clear();
+            p->group_first.clear();
+            return BITNET_OK;
+        }
+        if (st != BITNET_OK) return st;
+        p->groups.push_back(grp);
+    }
+    for (size_t k = 0; k < G * (L + 1); ++k) {
+        cudaEvent_t e = nullptr;
+        BITNET_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        p->group_events.push_back(e);
+    }
+    // copy launches need every host buffer mapped for the device (page-locked memory normally is)
+    bool mapped = true;
+    for (PlanCall &c : p->calls) {
+        void *dx = nullptr, *dy = nullptr;
+        if (cudaHostGetDevicePointer(&dx, const_cast<float *>(c.x_src), 0) != cudaSuccess ||
+            cudaHostGetDevicePointer(&dy, c.y_dst, 0) != cudaSuccess || (reinterpret_cast<uintptr_t>(dx) & 15) || (reinterpret_cast<uintptr_t>(dy) & 15)) {
+            cudaGetLastError();
+            mapped = false;
+            break;
+        }
+        c.x_src_alias = static_cast<const float *>(dx);
+        c.y_dst_alias = static_cast<float *>(dy);
+    }
+    if (!mapped) return BITNET_OK;
+    std::vector<CopyChunk> chunks;
+    const unsigned per_chunk = 512;   // 8 KB
+    auto add = [&](const float *src, float *dst, size_t bytes) {
+        const size_t units = bytes / 16;   // hidden % 64 == 0: a row is a whole number of units
+        for (size_t u = 0; u < units; u += per_chunk)
+            chunks.push_back(CopyChunk{reinterpret_cast<const uint4 *>(src) + u, reinterpret_cast<uint4 *>(dst) + u,
+                                       (unsigned)(units - u < per_chunk ? units - u : per_chunk)});
+    };
+    for (size_t g = 0; g < G; ++g) {
+        p->in_first.push_back((unsigned)chunks.size());
+        for (size_t i = p->group_first[g]; i < p->group_first[g + 1]; ++i) add(p->calls[i].x_src_alias, p->calls[i].x_dev, p->calls[i].M * hidden * sizeof(float));
+        p->in_count.push_back((unsigned)chunks.size() - p->in_first[g]);
+        p->out_first.push_back((unsigned)chunks.size());
+        for (size_t i = p->group_first[g]; i < p->group_first[g + 1]; ++i) add(p->calls[i].y_dev, p->calls[i].y_dst_alias, p->calls[i].M * hidden * sizeof(float));
+        p->out_count.push_back((unsigned)chunks.size() - p->out_first[g]);
+    }
+    BITNET_CUDA(cudaMalloc(reinterpret_cast<void **>(&p->chunks_dev), chunks.size() * sizeof(CopyChunk)));
+    BITNET_CUDA(cudaMemcpy(p->chunks_dev, chunks.data(), chunks.size() * sizeof(CopyChunk), cudaMemcpyHostToDevice));
     return BITNET_OK;
 }
 
@@ -784,6 +948,7 @@ extern "C" bitnet_status_t bitnet_backend_ffn_plan_create(bitnet_backend *b, con
             if (st == BITNET_OK) p->events.push_back(e);
         }
     }
+    if (st == BITNET_OK) st = plan_build_groups(p);
     // once eagerly (sets launch attributes, checks every call), then the same thing as a graph
     if (st == BITNET_OK) st = plan_enqueue(p);
     if (st == BITNET_OK) st = check_cuda(cudaStreamSynchronize(p->lanes[0]), "FFN plan: first run");

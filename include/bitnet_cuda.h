@@ -434,6 +434,9 @@ bitnet_status_t bitnet_backend_unpin_host(bitnet_backend *b, void *host_ptr);
  * the calls dealt round-robin to n_lanes streams (0 = 8) so that independent blocks overlap on the
  * device.  Host buffers that are page-locked (bitnet_backend_pin_host, cudaMallocHost, ...) are
  * copied from and to directly; others are staged through pinned memory inside the run.
+ * Calls of one shape with at most 16 tokens each run as up to three FFN groups (bitnet_ffn_group_*,
+ * below) instead of per-call launches: all input copies are queued at once on the lanes, a group's
+ * kernels start when its own inputs have landed, and its outputs leave while the next group computes.
  * bitnet_backend_ffn_plan_run replays the batch and returns when every y_host is complete; the
  * caller refreshes the bound x_host buffers between runs.  One run at a time per plan. */
 typedef struct bitnet_ffn_plan bitnet_ffn_plan;

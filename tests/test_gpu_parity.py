@@ -488,6 +488,29 @@ def test_backend_ffn_plan_replays_a_batch(n_lanes):
         b.close()
 
 
+@pytest.mark.parametrize("token_counts", [[1 + (i * 3) % 8 for i in range(75)],      # three groups of 25 calls
+                                          [4, 20, 1, 8]])                              # 20 tokens: per-call launches
+def test_backend_ffn_plan_grouped_and_per_call_forms(token_counts):
+    hidden, ffn = 128, 192
+    b = cuda.CudaBackend(cuda.CudaBackendConfig(num_streams=2))
+    try:
+        packs = [oracle.gen_ternary_packed(19, i, ffn * hidden) for i in range(3)]
+        scales = [oracle.gen_weight_scale(19, i, k) for i, k in ((0, hidden), (1, hidden), (2, ffn))]
+        w = (b.upload_packed(packs[0], ffn, hidden, scales[0]), b.upload_packed(packs[1], ffn, hidden, scales[1]),
+             b.upload_packed(packs[2], hidden, ffn, scales[2]))
+        xs = [oracle.gen_activations(19, 50 + i, (M, hidden)) for i, M in enumerate(token_counts)]
+        ys = [np.full((M, hidden), np.nan, dtype=np.float32) for M in token_counts]
+        plan = b.ffn_plan([(*w, xs[i], ys[i]) for i in range(len(token_counts))], n_lanes=4)
+        plan.run()
+        for i in range(len(token_counts)):
+            ref, _ = oracle.ffn_forward(packs[0], scales[0], packs[1], scales[1], packs[2], scales[2], xs[i], ffn)
+            assert np.array_equal(ys[i], ref), i
+        plan.close()
+        assert ops.device_error_flags() == 0
+    finally:
+        b.close()
+
+
 @pytest.mark.parametrize("M,K,N", [(1, 2560, 6912), (4, 6912, 2560), (8, 2560, 6912), (3, 320, 129), (16, 1024, 144), (1, 8192, 3584)])
 def test_decode_throughput_flag_same_bits(M, K, N):
     # the small-CTA plan (four consumer warps) gives the same bits as the default plan
