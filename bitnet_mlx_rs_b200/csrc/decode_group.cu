@@ -647,6 +647,9 @@ extern "C" bitnet_status_t bitnet_ffn_group_create(const bitnet_ffn_group_member
 extern "C" bitnet_status_t bitnet_ffn_group_run(bitnet_ffn_group *g, cudaStream_t stream)
 {
     if (!g) return fail(BITNET_ERR_NULL_POINTER, "bitnet_ffn_group_run: null group");
+    int dev = -1;
+    BITNET_CUDA(cudaGetDevice(&dev));
+    if (dev != g->device) return fail(BITNET_ERR_INVALID_CONFIG, "bitnet_ffn_group_run: the group lives on device %d, the current device is %d", g->device, dev);
     BITNET_TRY(group_stage_run(g->pair, stream));
     return group_stage_run(g->down, stream);
 }

@@ -462,7 +462,9 @@ void bitnet_backend_ffn_plan_destroy(bitnet_ffn_plan *plan);
  * Creation (on the current device) binds every member's device pointers and allocates the group's scratch
  * (tables, quantised-activation images, the gated intermediate); a run enqueues the four launches on `stream`
  * and may be captured into a CUDA graph.  The caller refreshes the bound x buffers between runs; one run at a
- * time per group.  Needs hidden % 64 == 0 (<= 8192), ffn % 64 == 0 (<= 16384), 16-byte aligned buffers. */
+ * time per group, on the device it was created on.  Needs hidden % 64 == 0, ffn % 64 == 0 and 16-byte aligned
+ * buffers; widths the grouped kernel cannot split over its warps (hidden above 7680 or ffn above 15360; from
+ * nine tokens per member on, 4096 and 8192) are refused with BITNET_ERR_UNSUPPORTED_OPERATION at creation. */
 typedef struct bitnet_ffn_group bitnet_ffn_group;
 typedef struct bitnet_ffn_group_member {
     const uint8_t *gate_packed_dev, *up_packed_dev, *down_packed_dev; /* canonical packed [ffn,hidden/4], [ffn,hidden/4], [hidden,ffn/4] */
