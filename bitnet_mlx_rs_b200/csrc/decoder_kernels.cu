@@ -14,6 +14,8 @@
 //                                    ignores them; its linear congruential generator is kept for the draw)
 #include <cuda_bf16.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace bitnet {
@@ -134,6 +136,90 @@ __device__ __forceinline__ float warp_reduce_scatter(float (&v)[NV], int lane)
 #pragma unroll
     for (int o = 16 / NV; o >= 1; o >>= 1) v[0] += __shfl_xor_sync(0xffffffffu, v[0], o);
     return v[0];
+}
+
+// The end of an attention CTA: the four warps' partial results (running maximum, sum and unnormalised output per
+// head, in shared memory) are folded; with one split the result is final, otherwise it goes to scratch and the CTA that
+// arrives last at the (sequence, KV head) counter folds the splits.
+template <int G, int HD>
+__device__ __forceinline__ void attention_fold(const AttnParams &p, int split, int kvh, int b, int tid, float (*s_m)[8], float (*s_l)[8],
+                                               float (*s_o)[G][HD], unsigned *s_last)
+{
+    constexpr float NEG_INF = -3.0e38f;
+    const int h0 = kvh * G;
+    for (int e = tid; e < G * HD; e += 128) {
+        const int g = e / HD, d = e - g * HD;
+        float mx = NEG_INF;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) mx = fmaxf(mx, s_m[w][g]);
+        float l = 0.0f, acc = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float f = s_m[w][g] > NEG_INF ? expf(s_m[w][g] - mx) : 0.0f;
+            l += s_l[w][g] * f;
+            acc += s_o[w][g][d] * f;
+        }
+        if (p.n_splits == 1) {
+            p.out[(size_t)b * p.n_heads * HD + (size_t)(h0 + g) * HD + d] = acc / l;
+        } else {
+            const size_t slot = ((size_t)b * p.n_heads + h0 + g) * p.n_splits + split;
+            p.part_o[slot * HD + d] = acc;
+            if (d == 0) { p.part_ml[slot * 2] = mx; p.part_ml[slot * 2 + 1] = l; }
+        }
+    }
+    if (p.n_splits == 1) return;
+
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned old = atomicAdd(p.counters + b * p.n_kv + kvh, 1u);
+        *s_last = old == (unsigned)p.n_splits - 1u ? 1u : 0u;
+    }
+    __syncthreads();
+    if (!*s_last) return;
+    __threadfence();
+    // the last CTA to arrive folds the splits: all maxima and sums first (one load per thread, all in flight at
+    // once), a weight per split and head, then the weighted partial outputs
+    float *s_w = &s_o[0][0][0];                 // [G][32] weights, then [G] sums: the warps' outputs are consumed
+    float *s_lsum = s_w + G * 32;
+    __syncthreads();
+    for (int i = tid; i < G * p.n_splits; i += 128) {
+        const int g = i / p.n_splits, s2 = i - g * p.n_splits;
+        const size_t slot = ((size_t)b * p.n_heads + h0 + g) * p.n_splits + s2;
+        s_w[g * 32 + s2] = __ldcg(p.part_ml + slot * 2);
+        s_w[G * 32 + G + g * 32 + s2] = __ldcg(p.part_ml + slot * 2 + 1);
+    }
+    __syncthreads();
+    if (tid < G) {
+        float mx = NEG_INF;
+        for (int s2 = 0; s2 < p.n_splits; ++s2) mx = fmaxf(mx, s_w[tid * 32 + s2]);
+        float l = 0.0f;
+        for (int s2 = 0; s2 < p.n_splits; ++s2) {
+            const float ms = s_w[tid * 32 + s2];
+            const float f = ms > NEG_INF ? expf(ms - mx) : 0.0f;
+            l += s_w[G * 32 + G + tid * 32 + s2] * f;
+            s_w[tid * 32 + s2] = f;
+        }
+        s_lsum[tid] = l;
+    }
+    __syncthreads();
+    for (int e = tid; e < G * HD; e += 128) {
+        const int g = e / HD, d = e - g * HD;
+        const size_t slot0 = ((size_t)b * p.n_heads + h0 + g) * p.n_splits;
+        float acc = 0.0f;
+        int s2 = 0;
+        for (; s2 + 4 <= p.n_splits; s2 += 4) {
+            const float v0 = __ldcg(p.part_o + (slot0 + s2) * HD + d), v1 = __ldcg(p.part_o + (slot0 + s2 + 1) * HD + d);
+            const float v2 = __ldcg(p.part_o + (slot0 + s2 + 2) * HD + d), v3 = __ldcg(p.part_o + (slot0 + s2 + 3) * HD + d);
+            acc += v0 * s_w[g * 32 + s2];
+            acc += v1 * s_w[g * 32 + s2 + 1];
+            acc += v2 * s_w[g * 32 + s2 + 2];
+            acc += v3 * s_w[g * 32 + s2 + 3];
+        }
+        for (; s2 < p.n_splits; ++s2) acc += __ldcg(p.part_o + (slot0 + s2) * HD + d) * s_w[g * 32 + s2];
+        p.out[(size_t)b * p.n_heads * HD + (size_t)(h0 + g) * HD + d] = acc / s_lsum[g];
+    }
+    if (tid == 0) p.counters[b * p.n_kv + kvh] = 0u;   // ready for the next launch
 }
 
 // grid (n_splits, n_kv, B), 128 threads.  A CTA takes a contiguous range of one sequence's positions for one KV
@@ -302,80 +388,212 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
         for (int d = 0; d < DPL; ++d) s_o[warp][g][lane * DPL + d] = o[g][d];
     __syncthreads();
 
-    const int h0 = kvh * G;
-    for (int e = tid; e < G * HD; e += 128) {
-        const int g = e / HD, d = e - g * HD;
-        float mx = NEG_INF;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) mx = fmaxf(mx, s_m[w][g]);
-        float l = 0.0f, acc = 0.0f;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            const float f = s_m[w][g] > NEG_INF ? expf(s_m[w][g] - mx) : 0.0f;
-            l += s_l[w][g] * f;
-            acc += s_o[w][g][d] * f;
-        }
-        if (p.n_splits == 1) {
-            p.out[(size_t)b * p.n_heads * HD + (size_t)(h0 + g) * HD + d] = acc / l;
-        } else {
-            const size_t slot = ((size_t)b * p.n_heads + h0 + g) * p.n_splits + split;
-            p.part_o[slot * HD + d] = acc;
-            if (d == 0) { p.part_ml[slot * 2] = mx; p.part_ml[slot * 2 + 1] = l; }
-        }
-    }
-    if (p.n_splits == 1) return;
+    attention_fold<G, HD>(p, split, kvh, b, tid, s_m, s_l, s_o, &s_last);
+}
 
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-        const unsigned old = atomicAdd(p.counters + b * p.n_kv + kvh, 1u);
-        s_last = old == (unsigned)p.n_splits - 1u ? 1u : 0u;
-    }
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    // the last CTA to arrive folds the splits: all maxima and sums first (one load per thread, all in flight at
-    // once), a weight per split and head, then the weighted partial outputs
-    float *s_w = &s_o[0][0][0];                 // [G][32] weights, then [G] sums: the warps' outputs are consumed
-    float *s_lsum = s_w + G * 32;
-    __syncthreads();
-    for (int i = tid; i < G * p.n_splits; i += 128) {
-        const int g = i / p.n_splits, s2 = i - g * p.n_splits;
-        const size_t slot = ((size_t)b * p.n_heads + h0 + g) * p.n_splits + s2;
-        s_w[g * 32 + s2] = __ldcg(p.part_ml + slot * 2);
-        s_w[G * 32 + G + g * 32 + s2] = __ldcg(p.part_ml + slot * 2 + 1);
-    }
-    __syncthreads();
-    if (tid < G) {
-        float mx = NEG_INF;
-        for (int s2 = 0; s2 < p.n_splits; ++s2) mx = fmaxf(mx, s_w[tid * 32 + s2]);
-        float l = 0.0f;
-        for (int s2 = 0; s2 < p.n_splits; ++s2) {
-            const float ms = s_w[tid * 32 + s2];
-            const float f = ms > NEG_INF ? expf(ms - mx) : 0.0f;
-            l += s_w[G * 32 + G + tid * 32 + s2] * f;
-            s_w[tid * 32 + s2] = f;
+// ---- the same step on the tensor cores (head_dim 128) -----------------------------------------------------
+//
+// A warp takes tiles of 16 cached positions: the K and V rows of a tile (4 KB each, contiguous in the cache) come in
+// by cp.async into a swizzled shared-memory tile, double buffered per warp.  Scores: S[heads x 16] = Q K^T with
+// mma.sync.m16n8k16 (bf16 in, fp32 out), the query heads of the KV head in rows 0..G-1 of the 16-row operand.  The
+// cache is bf16 already; q and the probabilities are fp32, so each goes in as two bf16 terms (x = hi + lo, the
+// remainder of the first rounding), which keeps the products at fp32 accuracy.  The score fragment of a tile is
+// exactly the A-operand fragment of P for O += P V, with V read through ldmatrix.trans.  Running maximum and sum per
+// head as in the scalar kernel; the end of the CTA is shared with it.
+constexpr int ATC_TILE = 16;                       // positions per tile
+constexpr int ATC_TILE_BYTES = ATC_TILE * 256;     // one of K or V, head_dim 128 in bf16
+
+__device__ __forceinline__ void atc_mma(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void atc_ldmatrix(unsigned (&r)[4], unsigned smem_addr)
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr));
+}
+__device__ __forceinline__ void atc_ldmatrix_trans(unsigned (&r)[4], unsigned smem_addr)
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr));
+}
+// x0, x1 as two packed bf16 pairs: hi holds the rounded values, lo the rounded remainders
+__device__ __forceinline__ void atc_split(float x0, float x1, unsigned &hi, unsigned &lo)
+{
+    const __nv_bfloat16 h0 = __float2bfloat16_rn(x0), h1 = __float2bfloat16_rn(x1);
+    hi = (unsigned)__bfloat16_as_ushort(h0) | ((unsigned)__bfloat16_as_ushort(h1) << 16);
+    lo = pack_bf16(x0 - __bfloat162float(h0), x1 - __bfloat162float(h1));
+}
+
+template <int G>
+__global__ void __launch_bounds__(128, 3) attention_decode_tc_kernel(const AttnParams p)
+{
+    constexpr int HD = 128;
+    constexpr float NEG_INF = -3.0e38f;
+    static_assert(G >= 1 && G <= 8, "query heads per KV head sit in rows 0..7 of the operand");
+
+    extern __shared__ __align__(128) unsigned char atc_smem[];   // [warp][buffer][K tile, V tile]
+    __shared__ float s_m[4][8], s_l[4][8];
+    __shared__ float s_o[4][G][HD];
+    __shared__ unsigned s_last;
+
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, tig = lane & 3;
+    int L = p.pos[b] + 1;                        // keys including the new token
+    if (L > p.max_seq) L = p.max_seq;
+    if (L < 1) L = 1;
+    const int chunk = (L + p.n_splits - 1) / p.n_splits;
+    const int p0 = split * chunk;
+    const int p1 = min(L, p0 + chunk);
+
+    const size_t row0 = ((size_t)b * p.n_kv + kvh) * (size_t)p.max_seq;
+    const unsigned char *kc = reinterpret_cast<const unsigned char *>(p.kcache + row0 * HD);
+    const unsigned char *vc = reinterpret_cast<const unsigned char *>(p.vcache + row0 * HD);
+    // the CTA whose range holds the new position appends it (rounded to the cache's bf16) before any tile is fetched
+    if (p0 <= L - 1 && L - 1 < p1) {
+        if (warp == 0) {
+            const float *knew = p.qkv + (size_t)b * p.ldq + p.k_off + kvh * HD + lane * 4;
+            const float *vnew = p.qkv + (size_t)b * p.ldq + p.v_off + kvh * HD + lane * 4;
+            uint2 *kw = reinterpret_cast<uint2 *>(p.kcache + (row0 + (L - 1)) * HD) + lane;
+            uint2 *vw = reinterpret_cast<uint2 *>(p.vcache + (row0 + (L - 1)) * HD) + lane;
+            *kw = make_uint2(pack_bf16(knew[0], knew[1]), pack_bf16(knew[2], knew[3]));
+            *vw = make_uint2(pack_bf16(vnew[0], vnew[1]), pack_bf16(vnew[2], vnew[3]));
+            __threadfence();
         }
-        s_lsum[tid] = l;
+        __syncthreads();
+    }
+
+    // the query heads, scaled, as A-operand fragments: row g = head g (rows G..15 are zero), two bf16 terms each
+    unsigned qhi[8][2], qlo[8][2];
+    {
+        const float *qrow = p.qkv + (size_t)b * p.ldq + (size_t)(kvh * G + (g < G ? g : 0)) * HD;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int d = ks * 16 + h * 8 + 2 * tig;
+                const float x0 = g < G ? qrow[d] * p.scale : 0.0f, x1 = g < G ? qrow[d + 1] * p.scale : 0.0f;
+                atc_split(x0, x1, qhi[ks][h], qlo[ks][h]);
+            }
+    }
+
+    unsigned char *wbuf = atc_smem + (size_t)warp * 4 * ATC_TILE_BYTES;
+    const unsigned wbuf_u32 = (unsigned)__cvta_generic_to_shared(wbuf);
+    const int n_tiles = p1 > p0 ? (p1 - p0 + ATC_TILE - 1) / ATC_TILE : 0;
+
+    // 16-byte pieces of a tile: piece id = row * 16 + c lands at row * 256 + ((c ^ (row & 7)) * 16); rows past the
+    // range are zero-filled (their scores are masked, their values weigh nothing)
+    auto fetch = [&](int tile, int buf) {
+        const int base = p0 + tile * ATC_TILE;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int id = i * 32 + lane, row = id >> 4, c = id & 15;
+            const int pos = base + row;
+            const unsigned bytes = pos < p1 ? 16u : 0u;
+            const size_t src = (size_t)(pos < p1 ? pos : p1 - 1) * 256 + (size_t)c * 16;
+            const unsigned dst = wbuf_u32 + (unsigned)buf * 2 * ATC_TILE_BYTES + (unsigned)row * 256 + (unsigned)((c ^ (row & 7)) * 16);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(kc + src), "r"(bytes) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + ATC_TILE_BYTES), "l"(vc + src), "r"(bytes) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    float m_run = NEG_INF, l_run = 0.0f;         // of head g (all four lanes of a row hold the same)
+    float o[16][4];                              // [8-dim tile][fragment register]: rows g (registers 0, 1) carry head g
+#pragma unroll
+    for (int dn = 0; dn < 16; ++dn) o[dn][0] = o[dn][1] = o[dn][2] = o[dn][3] = 0.0f;
+
+    if (warp < n_tiles) fetch(warp, 0);
+    int buf = 0;
+    for (int tile = warp; tile < n_tiles; tile += 4, buf ^= 1) {
+        if (tile + 4 < n_tiles) {
+            fetch(tile + 4, buf ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncwarp();
+        const unsigned kt = wbuf_u32 + (unsigned)buf * 2 * ATC_TILE_BYTES, vt = kt + ATC_TILE_BYTES;
+        const int lrow = lane & 7, lmat = lane >> 3;
+
+        // ---- scores of 16 positions: two 8-position tiles ----
+        float sc[2][4];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.0f;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+            // matrices: (positions 0-7, dims 16ks..+7), (0-7, +8..15), (8-15, ..+7), (8-15, +8..15)
+            const int row = (lmat >> 1) * 8 + lrow, c = ks * 2 + (lmat & 1);
+            unsigned kb[4];
+            atc_ldmatrix(kb, kt + (unsigned)row * 256 + (unsigned)((c ^ (row & 7)) * 16));
+            atc_mma(sc[0], qhi[ks][0], 0u, qhi[ks][1], 0u, kb[0], kb[1]);
+            atc_mma(sc[0], qlo[ks][0], 0u, qlo[ks][1], 0u, kb[0], kb[1]);
+            atc_mma(sc[1], qhi[ks][0], 0u, qhi[ks][1], 0u, kb[2], kb[3]);
+            atc_mma(sc[1], qlo[ks][0], 0u, qlo[ks][1], 0u, kb[2], kb[3]);
+        }
+        // registers 0, 1 of tile nt: head g at positions base + 8 nt + 2 tig, + 1
+        const int base = p0 + tile * ATC_TILE;
+        float tmax = NEG_INF;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                if (base + nt * 8 + 2 * tig + e >= p1) sc[nt][e] = NEG_INF;
+                tmax = fmaxf(tmax, sc[nt][e]);
+            }
+        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+        const float m_new = fmaxf(m_run, tmax);    // the tile's first position always exists: finite
+        const float corr = m_run > NEG_INF ? expf(m_run - m_new) : 0.0f;
+        float pr[2][2], psum = 0.0f;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                pr[nt][e] = sc[nt][e] > NEG_INF ? expf(sc[nt][e] - m_new) : 0.0f;
+                psum += pr[nt][e];
+            }
+        psum += __shfl_xor_sync(0xffffffffu, psum, 1);
+        psum += __shfl_xor_sync(0xffffffffu, psum, 2);
+        l_run = l_run * corr + psum;
+        m_run = m_new;
+        // P as the A operand of the second product: k = position; rows 8..15 stay zero
+        unsigned phi[2], plo[2];
+        atc_split(pr[0][0], pr[0][1], phi[0], plo[0]);
+        atc_split(pr[1][0], pr[1][1], phi[1], plo[1]);
+
+        // ---- O = O * corr + P V ----
+#pragma unroll
+        for (int dn = 0; dn < 16; dn += 2) {
+            // matrices: (positions 0-7, dims 8dn..+7), (8-15, same), (0-7, next 8 dims), (8-15, next 8 dims); transposed
+            const int row = (lmat & 1) * 8 + lrow, c = dn + (lmat >> 1);
+            unsigned vb[4];
+            atc_ldmatrix_trans(vb, vt + (unsigned)row * 256 + (unsigned)((c ^ (row & 7)) * 16));
+            o[dn][0] *= corr; o[dn][1] *= corr;
+            o[dn + 1][0] *= corr; o[dn + 1][1] *= corr;
+            atc_mma(o[dn], phi[0], 0u, phi[1], 0u, vb[0], vb[1]);
+            atc_mma(o[dn], plo[0], 0u, plo[1], 0u, vb[0], vb[1]);
+            atc_mma(o[dn + 1], phi[0], 0u, phi[1], 0u, vb[2], vb[3]);
+            atc_mma(o[dn + 1], plo[0], 0u, plo[1], 0u, vb[2], vb[3]);
+        }
+        __syncwarp();   // every lane is through with this buffer before the next fetch overwrites it
+    }
+
+    // the four warps' partial results meet in shared memory
+    if (g < G) {
+        if (tig == 0) { s_m[warp][g] = m_run; s_l[warp][g] = l_run; }
+#pragma unroll
+        for (int dn = 0; dn < 16; ++dn) {
+            s_o[warp][g][dn * 8 + 2 * tig] = o[dn][0];
+            s_o[warp][g][dn * 8 + 2 * tig + 1] = o[dn][1];
+        }
     }
     __syncthreads();
-    for (int e = tid; e < G * HD; e += 128) {
-        const int g = e / HD, d = e - g * HD;
-        const size_t slot0 = ((size_t)b * p.n_heads + h0 + g) * p.n_splits;
-        float acc = 0.0f;
-        int s2 = 0;
-        for (; s2 + 4 <= p.n_splits; s2 += 4) {
-            const float v0 = __ldcg(p.part_o + (slot0 + s2) * HD + d), v1 = __ldcg(p.part_o + (slot0 + s2 + 1) * HD + d);
-            const float v2 = __ldcg(p.part_o + (slot0 + s2 + 2) * HD + d), v3 = __ldcg(p.part_o + (slot0 + s2 + 3) * HD + d);
-            acc += v0 * s_w[g * 32 + s2];
-            acc += v1 * s_w[g * 32 + s2 + 1];
-            acc += v2 * s_w[g * 32 + s2 + 2];
-            acc += v3 * s_w[g * 32 + s2 + 3];
-        }
-        for (; s2 < p.n_splits; ++s2) acc += __ldcg(p.part_o + (slot0 + s2) * HD + d) * s_w[g * 32 + s2];
-        p.out[(size_t)b * p.n_heads * HD + (size_t)(h0 + g) * HD + d] = acc / s_lsum[g];
-    }
-    if (tid == 0) p.counters[b * p.n_kv + kvh] = 0u;   // ready for the next launch
+    attention_fold<G, HD>(p, split, kvh, b, tid, s_m, s_l, s_o, &s_last);
 }
 
 size_t attention_scratch_bytes(size_t B, size_t n_heads, size_t n_kv, size_t head_dim, size_t n_splits)
@@ -384,11 +602,13 @@ size_t attention_scratch_bytes(size_t B, size_t n_heads, size_t n_kv, size_t hea
     return align_up(B * n_heads * n_splits * head_dim * 4, 256) + align_up(B * n_heads * n_splits * 8, 256) + align_up(B * n_kv * 4, 256);
 }
 
-// Splits per (sequence, KV head): about two CTAs per SM in all (more splits cost more in partial results and their
-// fold than they gain in balance), at least 64 keys per split at the longest context.
+// Splits per (sequence, KV head): one when the pairs alone fill the SMs, else about two CTAs per SM in all (more
+// splits cost more in partial results and their fold than they gain in balance), at least 64 keys per split at the
+// longest context.
 int attention_splits(size_t B, size_t n_kv, size_t max_context)
 {
     const size_t pairs = B * n_kv;
+    if (pairs >= (size_t)device_sm_count()) return 1;   // a CTA per pair already fills the SMs: folding splits only costs
     size_t want = (2 * (size_t)device_sm_count() + pairs - 1) / pairs;
     const size_t by_len = max_context / 64 > 0 ? max_context / 64 : 1;
     if (want > by_len) want = by_len;
@@ -412,6 +632,38 @@ static bitnet_status_t launch_attention_t(const AttnParams &p, size_t B, uint32_
         cfg.numAttrs = 1;
     }
     BITNET_CUDA(cudaLaunchKernelEx(&cfg, attention_decode_kernel<G, HD, NB>, p));
+    return BITNET_OK;
+}
+
+template <int G>
+static bitnet_status_t launch_attention_tc(const AttnParams &p, size_t B, uint32_t flags, cudaStream_t stream)
+{
+    const size_t smem = 4 * 4 * ATC_TILE_BYTES;   // four warps x two buffers x (K tile + V tile)
+    {
+        static std::mutex mu;
+        static bool raised[64] = {false};
+        int dev = 0;
+        BITNET_CUDA(cudaGetDevice(&dev));
+        const bool tracked = dev >= 0 && dev < 64;
+        std::lock_guard<std::mutex> lock(mu);
+        if (!tracked || !raised[dev]) {
+            BITNET_CUDA(cudaFuncSetAttribute(attention_decode_tc_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            if (tracked) raised[dev] = true;
+        }
+    }
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attrs[1];
+    cfg.gridDim = dim3((unsigned)p.n_splits, (unsigned)p.n_kv, (unsigned)B);
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cfg.attrs = attrs;
+    if (flags & BITNET_FLAG_PDL) {
+        attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attrs[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.numAttrs = 1;
+    }
+    BITNET_CUDA(cudaLaunchKernelEx(&cfg, attention_decode_tc_kernel<G>, p));
     return BITNET_OK;
 }
 
@@ -446,6 +698,14 @@ bitnet_status_t launch_attention_decode(const float *qkv, size_t ldq, size_t k_o
         p.part_ml = reinterpret_cast<float *>(s);
         s += align_up(B * n_heads * n_splits * 8, 256);
         p.counters = reinterpret_cast<unsigned *>(s);
+    }
+    // the tensor-core form from 64 (sequence, KV head) pairs on; below that its fixed cost per CTA (query fragments,
+    // the first tile's round trip) outweighs the cheaper positions (measured: 14.3 against 12.5 us at 40 pairs)
+    if (head_dim == 128 && B * n_kv >= 64 && (G == 1 || G == 2 || G == 4 || G == 8)) {
+        if (G == 1) return launch_attention_tc<1>(p, B, flags, stream);
+        if (G == 2) return launch_attention_tc<2>(p, B, flags, stream);
+        if (G == 4) return launch_attention_tc<4>(p, B, flags, stream);
+        return launch_attention_tc<8>(p, B, flags, stream);
     }
 #define BITNET_ATTN_CASE(GV, HDV, NBV) \
     if (G == GV && head_dim == HDV) return launch_attention_t<GV, HDV, NBV>(p, B, flags, stream)

@@ -118,6 +118,41 @@ def test_attention_decode_matches_oracle(n_heads, n_kv, hd, n_splits):
         assert np.array_equal(after_k[b][:, others], kc[b][:, others]) and np.array_equal(after_v[b][:, others], vc[b][:, others])
 
 
+@pytest.mark.parametrize("n_heads,n_kv", [(16, 4), (8, 8), (16, 8), (32, 4)])      # 4, 1, 2 and 8 query heads per KV head
+@pytest.mark.parametrize("n_splits", [1, 3, 0])
+def test_attention_decode_tensor_core_form(n_heads, n_kv, n_splits):
+    """Enough (sequence, KV head) pairs for the tensor-core kernel (head_dim 128, 64 pairs or more): contexts of one key,
+    a partial tile, whole tiles, the last cache row; same tolerance as the scalar form."""
+    hd, max_seq = 128, 200
+    B = 64 // n_kv + 1
+    rng = np.random.default_rng(n_heads * 11 + n_splits)
+    pos = rng.integers(0, max_seq, size=B).astype(np.int32)
+    pos[:6] = [0, 1, 15, 16, 47, max_seq - 1]
+    qkv = rng.standard_normal((B, (n_heads + 2 * n_kv) * hd)).astype(np.float32)
+    kc = od.bf16_round(rng.standard_normal((B, n_kv, max_seq, hd)).astype(np.float32))
+    vc = od.bf16_round(rng.standard_normal((B, n_kv, max_seq, hd)).astype(np.float32))
+    dk, dv = dev(kc).to(torch.bfloat16), dev(vc).to(torch.bfloat16)
+    for _ in range(2):
+        out = ops.attention_decode(dev(qkv), dk, dv, dev(pos), n_heads, n_kv, hd, n_splits=n_splits)
+    torch.cuda.synchronize()
+    qd, kd = n_heads * hd, n_kv * hd
+    got = out.cpu().numpy()
+    for b in range(B):
+        L = pos[b] + 1
+        k_new = od.bf16_round(qkv[b, qd:qd + kd]).reshape(n_kv, 1, hd)
+        v_new = od.bf16_round(qkv[b, qd + kd:]).reshape(n_kv, 1, hd)
+        ref = od.attention_decode(qkv[b, :qd], np.concatenate([kc[b, :, :L - 1], k_new], axis=1),
+                                  np.concatenate([vc[b, :, :L - 1], v_new], axis=1), n_heads, n_kv, hd)
+        np.testing.assert_allclose(got[b], ref, rtol=ATTN_RTOL, atol=ATTN_ATOL)
+        assert np.array_equal(dk[b, :, pos[b]].float().cpu().numpy(), k_new[:, 0])
+        assert np.array_equal(dv[b, :, pos[b]].float().cpu().numpy(), v_new[:, 0])
+    after_k = dk.float().cpu().numpy()
+    for b in range(B):
+        others = np.arange(max_seq) != pos[b]
+        assert np.array_equal(after_k[b][:, others], kc[b][:, others])
+    assert ops.device_error_flags() == 0
+
+
 def test_sampler_argmax_and_draws():
     B, V = 6, 5000
     rng = np.random.default_rng(4)
