@@ -436,7 +436,8 @@ bitnet_status_t bitnet_backend_unpin_host(bitnet_backend *b, void *host_ptr);
  * copied from and to directly; others are staged through pinned memory inside the run.
  * Calls of one shape with at most 16 tokens each run as up to three FFN groups (bitnet_ffn_group_*,
  * below) instead of per-call launches: all input copies are queued at once on the lanes, a group's
- * kernels start when its own inputs have landed, and its outputs leave while the next group computes.
+ * kernels start when its own inputs have landed, and its outputs leave while the next group computes (the
+ * groups' scratch is allocated with cudaMalloc, outside the backend's pool and its byte budget).
  * bitnet_backend_ffn_plan_run replays the batch and returns when every y_host is complete; the
  * caller refreshes the bound x_host buffers between runs.  One run at a time per plan. */
 typedef struct bitnet_ffn_plan bitnet_ffn_plan;
