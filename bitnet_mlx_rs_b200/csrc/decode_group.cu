@@ -577,7 +577,6 @@ struct bitnet_ffn_group {
     int device = 0;
     void *slab = nullptr;
     GroupStage pair, down;     // gate/up with the gating, then the down projection
-    bool has_down = false;
 };
 
 static void group_release(bitnet_ffn_group *g)
@@ -639,7 +638,6 @@ extern "C" bitnet_status_t bitnet_ffn_group_create(const bitnet_ffn_group_member
     st = group_stage_build(g->pair, a, tab_pair, img_pair);
     if (st == BITNET_OK) st = group_stage_build(g->down, b, tab_down, img_down);
     if (st != BITNET_OK) { group_release(g); return st; }
-    g->has_down = true;
     *out = g;
     return BITNET_OK;
 }
