@@ -563,6 +563,32 @@ def single_kernel_figures(torch, ops, gen, peak):
         gbs = call_bytes(M, K, N) / us / 1e3
         out[name] = {"us": us, "gbs": gbs, "frac_of_peak": gbs / peak, "weight_copies": copies, "launch": launch}
         del W
+    # cfg1 as a batch: 96 independent single-token 2560 -> 2560 projections (weights of their own, 157 MB) as one group
+    M, K, N, n = 1, 2560, 2560, 96
+    members = [(gen_packed_on_device(torch, N * K, gen), 0.01, gen_activations_on_device(torch, (M, K), gen),
+                torch.empty((M, N), device="cuda")) for _ in range(n)]
+    group = ops.BitLinearGroup(members, N, K)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        group.run(stream=side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            group.run(stream=side)
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(10):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (10 * n)
+    gbs = call_bytes(M, K, N) / us / 1e3
+    out["cfg1_m1_2560x2560_group_of_96"] = {"us": us, "gbs": gbs, "frac_of_peak": gbs / peak, "members": n,
+                                             "launch": "cuda graph, bitnet_bitlinear_group_run (2 launches for the group)"}
+    group.close()
     out["cfg3_prefill_layer_m2048"] = prefill_layer_figures(torch, ops, gen)
     return out
 

@@ -83,6 +83,10 @@ class FfnCall(C.Structure):
     _fields_ = [("gate", vp), ("up", vp), ("down", vp), ("M", sz), ("x_host", vp), ("y_host", vp)]
 
 
+class BitLinearGroupMember(C.Structure):
+    _fields_ = [("packed_dev", vp), ("w_scale", f32), ("x_dev", vp), ("y_dev", vp), ("M", sz), ("ldy", sz)]
+
+
 class FfnGroupMember(C.Structure):
     _fields_ = [("gate_packed_dev", vp), ("up_packed_dev", vp), ("down_packed_dev", vp), ("gate_scale", f32), ("up_scale", f32),
                 ("down_scale", f32), ("x_dev", vp), ("y_dev", vp), ("M", sz)]
@@ -162,6 +166,9 @@ SIGNATURES = {
     "bitnet_allgather_output_nccl": (i32, [vp, vp, sz, sz, vp, vp, i32, sz, vp]),
     "bitnet_backend_pin_host": (i32, [vp, vp, sz]),
     "bitnet_backend_unpin_host": (i32, [vp, vp]),
+    "bitnet_bitlinear_group_create": (i32, [_P(BitLinearGroupMember), sz, sz, sz, _P(vp)]),
+    "bitnet_bitlinear_group_run": (i32, [vp, vp]),
+    "bitnet_bitlinear_group_destroy": (None, [vp]),
     "bitnet_ffn_group_create": (i32, [_P(FfnGroupMember), sz, sz, sz, _P(vp)]),
     "bitnet_ffn_group_run": (i32, [vp, vp]),
     "bitnet_ffn_group_destroy": (None, [vp]),

@@ -653,3 +653,71 @@ extern "C" bitnet_status_t bitnet_ffn_group_run(bitnet_ffn_group *g, cudaStream_
 }
 
 extern "C" void bitnet_ffn_group_destroy(bitnet_ffn_group *g) { group_release(g); }
+
+// ---- a group of independent BitLinear calls of one shape -------------------------------------------------
+
+struct bitnet_bitlinear_group {
+    int device = 0;
+    void *slab = nullptr;
+    GroupStage stage;
+};
+
+static void linear_group_release(bitnet_bitlinear_group *g)
+{
+    if (!g) return;
+    if (g->slab) {
+        cudaSetDevice(g->device);
+        cudaFree(g->slab);
+    }
+    delete g;
+}
+
+extern "C" bitnet_status_t bitnet_bitlinear_group_create(const bitnet_bitlinear_group_member *members, size_t n_members, size_t K,
+                                                         size_t N, bitnet_bitlinear_group **out)
+{
+    if (!out) return fail(BITNET_ERR_NULL_POINTER, "bitnet_bitlinear_group_create: null output");
+    *out = nullptr;
+    if (!members || n_members == 0) return fail(BITNET_ERR_INVALID_CONFIG, "bitnet_bitlinear_group_create: no members");
+    if (n_members > (1u << 20)) return fail(BITNET_ERR_INVALID_CONFIG, "bitnet_bitlinear_group_create: too many members");
+    if (K == 0 || N == 0 || N > (1u << 30)) return fail(BITNET_ERR_INCOMPATIBLE_SHAPES, "bitnet_bitlinear_group_create: bad dimension");
+    size_t max_M = 0, tokens = 0;
+    for (size_t i = 0; i < n_members; ++i) {
+        const bitnet_bitlinear_group_member &m = members[i];
+        if (!m.packed_dev || !m.x_dev || !m.y_dev) return fail(BITNET_ERR_NULL_POINTER, "BitLinear group: member %zu has a null pointer", i);
+        if (m.M == 0 || m.M > DEC_MAX_TOKENS) return fail(BITNET_ERR_UNSUPPORTED_OPERATION, "BitLinear group: member %zu has %zu tokens (1..16)", i, m.M);
+        if (misaligned16(m.packed_dev) || misaligned16(m.x_dev) || misaligned16(m.y_dev))
+            return fail(BITNET_ERR_INVALID_CONFIG, "BitLinear group: buffers of member %zu must be 16-byte aligned", i);
+        if (m.ldy && m.ldy < N) return fail(BITNET_ERR_INCOMPATIBLE_SHAPES, "BitLinear group: member %zu has ldy %zu < N %zu", i, m.ldy, N);
+        if (m.M > max_M) max_M = m.M;
+        tokens += m.M;
+    }
+    bitnet_bitlinear_group *g = new (std::nothrow) bitnet_bitlinear_group();
+    if (!g) return fail(BITNET_ERR_MEMORY_ALLOCATION, "out of host memory");
+    bitnet_status_t st = group_stage_plan(g->stage, K, max_M, false);
+    if (st == BITNET_OK) st = check_cuda(cudaGetDevice(&g->device), "cudaGetDevice");
+    if (st != BITNET_OK) { linear_group_release(g); return st; }
+    const size_t tables = group_stage_table_bytes(n_members, tokens, device_sm_count());
+    st = check_cuda(cudaMalloc(&g->slab, tables + n_members * g->stage.image_stride), "cudaMalloc (BitLinear group)");
+    if (st != BITNET_OK) { linear_group_release(g); return st; }
+    std::vector<StageMemberIn> in(n_members);
+    for (size_t i = 0; i < n_members; ++i) {
+        const bitnet_bitlinear_group_member &m = members[i];
+        in[i] = StageMemberIn{m.packed_dev, nullptr, m.x_dev, m.y_dev, m.w_scale, 0.0f, m.M, N, m.ldy ? m.ldy : N};
+    }
+    unsigned char *dev = static_cast<unsigned char *>(g->slab);
+    st = group_stage_build(g->stage, in, dev, dev + tables);
+    if (st != BITNET_OK) { linear_group_release(g); return st; }
+    *out = g;
+    return BITNET_OK;
+}
+
+extern "C" bitnet_status_t bitnet_bitlinear_group_run(bitnet_bitlinear_group *g, cudaStream_t stream)
+{
+    if (!g) return fail(BITNET_ERR_NULL_POINTER, "bitnet_bitlinear_group_run: null group");
+    int dev = -1;
+    BITNET_CUDA(cudaGetDevice(&dev));
+    if (dev != g->device) return fail(BITNET_ERR_INVALID_CONFIG, "bitnet_bitlinear_group_run: the group lives on device %d, the current device is %d", g->device, dev);
+    return group_stage_run(g->stage, stream);
+}
+
+extern "C" void bitnet_bitlinear_group_destroy(bitnet_bitlinear_group *g) { linear_group_release(g); }

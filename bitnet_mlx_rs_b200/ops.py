@@ -236,6 +236,44 @@ def ffn_forward_fused(w_gate, s_gate, w_up, s_up, w_down, s_down, x: torch.Tenso
     return y, h
 
 
+class BitLinearGroup:
+    """A group of independent BitLinear calls of one shape [N, K] (at most 16 tokens each) run as two launches for the
+    whole group (bitnet_bitlinear_group_*).  members: (packed weights uint8, w_scale, x [M, K], y [M, N]); the tensors
+    are bound at creation and kept alive by the group."""
+
+    def __init__(self, members, N: int, K: int):
+        self._keep = []
+        arr = (L.BitLinearGroupMember * len(members))()
+        for i, (w, s, x, y) in enumerate(members):
+            x = _require(x, torch.float32, "x")
+            y = _require(y, torch.float32, "y")
+            if x.dim() != 2 or x.shape[1] != K or y.dim() != 2 or y.shape[0] != x.shape[0] or y.shape[1] != N:
+                raise IncompatibleShapes(f"member {i}: x must be [M,{K}] and y [M,{N}], got {list(x.shape)} and {list(y.shape)}")
+            if w.dtype != torch.uint8 or not w.is_contiguous() or w.numel() != packed_len(N * K):
+                raise IncompatibleShapes(f"member {i}: packed weights must hold {packed_len(N * K)} bytes")
+            arr[i] = L.BitLinearGroupMember(w.data_ptr(), s, x.data_ptr(), y.data_ptr(), x.shape[0], 0)
+            self._keep.append((w, x, y))
+        self._device = members[0][2].device if members else None
+        handle = C.c_void_p()
+        with torch.cuda.device(self._device):
+            check(L.load().bitnet_bitlinear_group_create(arr, len(members), K, N, C.byref(handle)))
+        self._handle = handle
+
+    def run(self, stream=None) -> None:
+        check(L.load().bitnet_bitlinear_group_run(self._handle, _stream(stream)))
+
+    def close(self) -> None:
+        if getattr(self, "_handle", None):
+            L.load().bitnet_bitlinear_group_destroy(self._handle)
+            self._handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 class FfnGroup:
     """A group of independent FFN blocks of one shape (at most 16 tokens each) run as four launches for the whole group
     (bitnet_ffn_group_*).  members: (w_gate, s_gate, w_up, s_up, w_down, s_down, x [M, hidden], y [M, hidden]) with the

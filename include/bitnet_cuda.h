@@ -479,6 +479,24 @@ bitnet_status_t bitnet_ffn_group_create(const bitnet_ffn_group_member *members, 
 bitnet_status_t bitnet_ffn_group_run(bitnet_ffn_group *group, cudaStream_t stream);
 void bitnet_ffn_group_destroy(bitnet_ffn_group *group);
 
+/* The same for plain BitLinear calls of one shape [N, K] (TernaryProcessor::quantize_activations +
+ * ternary_matmul_generic per member, ternary_operations.rs:117-172, :283-338): a quantiser launch and ONE persistent
+ * launch over the weights of every member; bit-identical to bitnet_bitlinear_forward per member.  N need not be a
+ * multiple of 16; ldy = 0 means N. */
+typedef struct bitnet_bitlinear_group bitnet_bitlinear_group;
+typedef struct bitnet_bitlinear_group_member {
+    const uint8_t *packed_dev;  /* canonical packed [N, K/4] */
+    float w_scale;
+    const float *x_dev;         /* [M, K] */
+    float *y_dev;               /* [M, ldy] */
+    size_t M;                   /* 1..16 */
+    size_t ldy;
+} bitnet_bitlinear_group_member;
+bitnet_status_t bitnet_bitlinear_group_create(const bitnet_bitlinear_group_member *members, size_t n_members, size_t K,
+                                              size_t N, bitnet_bitlinear_group **out);
+bitnet_status_t bitnet_bitlinear_group_run(bitnet_bitlinear_group *group, cudaStream_t stream);
+void bitnet_bitlinear_group_destroy(bitnet_bitlinear_group *group);
+
 /* ---- exchange step of the output-feature-split layer ------------------------------------------------- */
 /* Every GPU holds y[:, its column slice]; all need y[M, N].  No counterpart in the reference, which has no
  * multi-GPU code.

@@ -89,3 +89,28 @@ def test_group_refuses_what_it_cannot_run():
         ops.FfnGroup([(*m[:6], torch.zeros((17, 128), device="cuda"), torch.zeros((17, 128), device="cuda")) for m in members], 128, 128)
     with pytest.raises(cuda.IncompatibleShapes):
         ops.FfnGroup(members, 128, 192)                         # packed sizes disagree with the stated shape
+
+
+@pytest.mark.parametrize("K,N,token_counts", [
+    (2560, 2560, [1, 1, 4, 8, 1]),                 # the attention-projection shape
+    (64, 100, [1, 16, 3]),                          # a ragged last block of rows, two token tiles
+    (1088, 40, [2] * 9),                            # uneven K slices, fewer blocks than SMs
+    (8192, 48, [8, 1]),                             # four steps per warp
+])
+def test_bitlinear_group_matches_oracle(K, N, token_counts):
+    host, members = [], []
+    for i, M in enumerate(token_counts):
+        wp = oracle.gen_ternary_packed(41, i, N * K)
+        ws = oracle.gen_weight_scale(41, i, K)
+        x = oracle.gen_activations(41, 100 + i, (M, K))
+        host.append((wp, ws, x))
+        members.append((dev(wp), ws, dev(x), torch.full((M, N), float("nan"), device="cuda")))
+    group = ops.BitLinearGroup(members, N, K)
+    group.run()
+    group.run()                                     # a second run over the same bound buffers
+    torch.cuda.synchronize()
+    for i, ((wp, ws, x), m) in enumerate(zip(host, members)):
+        ref = oracle.bitlinear_forward(wp, ws, x, N)["y"]
+        assert np.array_equal(m[3].cpu().numpy(), ref), f"member {i}"
+    assert ops.device_error_flags() == 0
+    group.close()
