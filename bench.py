@@ -702,8 +702,9 @@ def model_figures(torch, dist, local, world, peak_gbs, layers=None):
 
 def nsplit_figures(torch, dist, ops, world, rank):
     """cfg5: the oversized layer K = 8192, N = 28672 at M in {1, 16, 256}, output features split over the ranks.  Two forms:
-    every rank computes its column slice and the fp32 slices are all-gathered with NCCL; or (decode shapes) every rank's
-    kernel stores its slice straight into every GPU's output over NVLink and a barrier replaces the collective.  Before
+    every rank computes its column slice and the fp32 slices are all-gathered with NCCL; or every rank's kernel (the decode
+    kernel up to 16 tokens, the persistent GEMM above) stores its slice straight into every GPU's output over NVLink and
+    a barrier replaces the collective.  Before
     any timing each form's result is compared bit for bit with the single-GPU result of the same layer on this rank.
     Times: CUDA events, graph replay where it captures, maximum over ranks."""
     from bitnet_mlx_rs_b200 import parallel
@@ -715,7 +716,7 @@ def nsplit_figures(torch, dist, ops, world, rank):
     for c in range(copies):
         full = gen_packed_on_device(torch, N * K, gen)
         layers.append(parallel.NSplitBitLinear(full, 0.01, N, K))
-        fused.append(parallel.FusedNSplitBitLinear(full, 0.01, N, K))
+        fused.append(parallel.FusedNSplitBitLinear(full, 0.01, N, K, max_tokens=256))
         if c == 0:
             full0 = full
         del full
@@ -757,10 +758,8 @@ def nsplit_figures(torch, dist, ops, world, rank):
         y_one = ops.bitlinear_forward(full0, 0.01, x, N)          # the whole layer on this GPU alone
         y_ag = layers[0].forward(x)
         same_ag = bool(torch.equal(y_ag, y_one))
-        same_fused = None
-        if M <= 16:
-            y_f = fused[0].forward(x).clone()
-            same_fused = bool(torch.equal(y_f, y_one))
+        y_f = fused[0].forward(x).clone()
+        same_fused = bool(torch.equal(y_f, y_one))
         flags = torch.tensor([int(same_ag), int(same_fused is not False)], device="cuda")
         dist.all_reduce(flags, op=dist.ReduceOp.MIN)
         entry = {"equals_single_gpu": bool(flags[0].item()) and bool(flags[1].item()),
@@ -769,12 +768,9 @@ def nsplit_figures(torch, dist, ops, world, rank):
         run1, mode1 = graphed(lambda: ops.bitlinear_forward(full0, 0.01, x, N, out=y_buf, pdl=True))
         entry["us_one_gpu"] = timed(run1, 20)
         entry["us_allgather"] = timed(lambda: [layers[i].forward(x) for i in range(copies)], 4) / copies
-        if M <= 16:
-            runf, modef = graphed(lambda: [fused[i].forward(x) for i in range(copies)])
-            entry["us_fused"] = timed(runf, 4) / copies
-            entry["fused_launch"] = modef
-        else:
-            entry["us_fused"] = None
+        runf, modef = graphed(lambda: [fused[i].forward(x) for i in range(copies)])
+        entry["us_fused"] = timed(runf, 4) / copies
+        entry["fused_launch"] = modef
         out[f"m{M}"] = entry
     return out
 

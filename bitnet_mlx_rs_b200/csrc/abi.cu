@@ -238,8 +238,8 @@ static bitnet_status_t forward_impl(const uint8_t *weights_dev, const size_t *ro
     const bool glue = has_glue(pre);
     if (o.n_peers < 0 || o.n_peers > BITNET_MAX_PEERS)
         return fail(BITNET_ERR_INVALID_CONFIG, "n_peers must be in 0..%d (got %d)", BITNET_MAX_PEERS, o.n_peers);
-    if (o.n_peers > 0 && path != BITNET_PATH_DECODE)
-        return fail(BITNET_ERR_UNSUPPORTED_OPERATION, "peer outputs are written by the decode kernel only (M <= 16)");
+    if (o.n_peers > 0 && path != BITNET_PATH_DECODE && !(path == BITNET_PATH_PREFILL && n_members == 1 && !o.acc_out_dev))
+        return fail(BITNET_ERR_UNSUPPORTED_OPERATION, "peer outputs are written by the decode kernel (M <= 16) and by the persistent GEMM (path prefill)");
 
     if (path == BITNET_PATH_DECODE) {
         ForwardArgs a = {};
@@ -311,6 +311,11 @@ static bitnet_status_t forward_impl(const uint8_t *weights_dev, const size_t *ro
             a.wp = w_m; a.w_scale = scales[mbr]; a.x = x_eff; a.y = y_m; a.acc_out = acc_m;
             a.q_out = mbr == 0 ? o.q_out_dev : nullptr; a.a_scale_out = mbr == 0 ? o.a_scale_out_dev : nullptr;
             a.M = M; a.K = K; a.N = n_m; a.ldy = ldy; a.flags = o.flags;
+            for (int r = 0; r < o.n_peers; ++r) {
+                if (!o.y_peers_dev[r]) return fail(BITNET_ERR_NULL_POINTER, "y_peers_dev[%d] is null", r);
+                a.y_peers[r] = o.y_peers_dev[r];
+            }
+            a.n_peers = o.n_peers;
             BITNET_TRY(launch_prefill(a, ws, path_ws, s));
         } else {
             int8_t *q = reinterpret_cast<int8_t *>(ws);

@@ -361,6 +361,8 @@ struct PrefillParams {
     int tma_store;       // y can be written with TMA (16-byte aligned rows), else plain stores
     int bt;              // tokens per tile (the MMA's N): a multiple of 32, at most PF_BT
     int whole_tiles;     // ranges end on tile boundaries (no tile is split between CTAs)
+    float *y_peers[8];   // output-feature split over several GPUs: every output goes to each of these (own and peer
+    int n_peers;         // memory, plain stores over NVLink; TMA is used for this GPU's memory only); 0 = write y only
 };
 
 // instruction descriptor: D = s32, A = u8 (codes, tensor memory), B = s8 (activations, K-major), N = tokens, M = 128
@@ -798,6 +800,15 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     }
                     if (p.tma_store) {
                         send_chunk(r, n_tile * PF_BF + quarter * 32, m0 + c * 32);
+                    } else if (p.n_peers) {
+                        // this GPU's column slice, stored into every GPU's full-width output: a warp writes 128
+                        // contiguous bytes per token row and destination
+                        for (int pr = 0; pr < p.n_peers; ++pr) {
+                            float *ycol = p.y_peers[pr] + (size_t)(m0 + c * 32) * p.ldy + n;
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (n_ok && j < m_left) ycol[(size_t)j * p.ldy] = __uint_as_float(r[j]);
+                        }
                     } else {
                         float *ycol = p.y + (size_t)(m0 + c * 32) * p.ldy + n;
 #pragma unroll
@@ -994,6 +1005,12 @@ bitnet_status_t launch_prefill(const ForwardArgs &a, void *workspace, size_t wor
     p.k_tiles = (int)(a.K / PF_BK);
     // y leaves through TMA when its rows are 16-byte aligned; any other output takes plain stores
     p.tma_store = ((reinterpret_cast<uintptr_t>(a.y) & 15) == 0 && (p.ldy % 4) == 0) ? 1 : 0;
+    p.n_peers = a.n_peers;
+    for (int r = 0; r < a.n_peers && r < 8; ++r) p.y_peers[r] = a.y_peers[r];
+    if (a.n_peers) {
+        if (a.acc_out) return fail(BITNET_ERR_INVALID_CONFIG, "peer outputs and acc_out exclude each other");
+        p.tma_store = 0;   // peer memory takes plain stores
+    }
     if (p.tma_store)
         BITNET_TRY(encode_map(&map_y, a.y, a.N, a.M, p.ldy * 4, 32, 32, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_DATA_TYPE_FLOAT32));
     else

@@ -69,10 +69,10 @@ class NSplitBitLinear:
 
 
 class FusedNSplitBitLinear:
-    """Output-feature-split BitLinear for decode shapes (M <= 16) without a collective: every rank's
-    kernel stores its column slice straight into ALL ranks' full-width outputs (plain peer stores
-    over NVLink from the kernel's epilogue), and a symmetric-memory barrier tells the ranks that the
-    slices have arrived.  The outputs live in torch symmetric memory, which maps every rank's
+    """Output-feature-split BitLinear without a collective: every rank's kernel (the decode kernel up to
+    16 tokens, the persistent GEMM above) stores its column slice straight into ALL ranks' full-width
+    outputs (plain peer stores over NVLink from the kernel's epilogue), and a symmetric-memory barrier
+    tells the ranks that the slices have arrived.  The outputs live in torch symmetric memory, which maps every rank's
     buffer into every process.  The barrier before the launch keeps a fast rank from overwriting an
     output that a slow rank is still reading."""
 
@@ -86,8 +86,6 @@ class FusedNSplitBitLinear:
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         if self.world > 8:
             raise ValueError("at most 8 ranks (one node)")
-        if max_tokens > 16:
-            raise ValueError("the fused output path covers decode shapes only (at most 16 tokens)")
         self.out_features, self.in_features, self.scale, self.max_tokens = out_features, in_features, scale, max_tokens
         self.packed, (self.r0, self.r1) = packed_row_slice(packed_full, out_features, in_features, self.world, self.rank)
         self.packed = self.packed.contiguous()
@@ -105,8 +103,8 @@ class FusedNSplitBitLinear:
         if M > self.max_tokens:
             raise ValueError(f"{M} tokens > max_tokens {self.max_tokens}")
         self.handle.barrier(channel=0)   # nobody still reads the previous result
-        self._ops.bitlinear_forward(self.packed, self.scale, x, self.r1 - self.r0, path="decode", out=self._unused[:M],
-                                    ldy=self.out_features, y_peers=self.peer_ptrs)
+        self._ops.bitlinear_forward(self.packed, self.scale, x, self.r1 - self.r0, path="decode" if M <= 16 else "prefill",
+                                    out=self._unused[:M], ldy=self.out_features, y_peers=self.peer_ptrs)
         self.handle.barrier(channel=1)   # every rank's slice has landed everywhere
         return self.y[:M]
 

@@ -92,8 +92,9 @@ typedef struct bitnet_forward_opts {
        output element into each of these buffers (this GPU's and its peers', mapped into this process:
        CUDA IPC, symmetric memory or cudaDeviceEnablePeerAccess) instead of y_dev alone, which replaces
        the all-gather of the column slices by plain peer stores over NVLink.  Each pointer addresses
-       the slice's first column in that GPU's full-width output (row stride ldy).  Decode shapes
-       (M <= 16) only; the caller synchronises the GPUs afterwards.  No counterpart in the
+       the slice's first column in that GPU's full-width output (row stride ldy).  Written by the
+       decode kernel (M <= 16) and by the persistent GEMM (path BITNET_PATH_PREFILL, one weight
+       matrix, no acc_out); the caller synchronises the GPUs afterwards.  No counterpart in the
        reference, which has no multi-GPU code. */
     float *y_peers_dev[8];
 } bitnet_forward_opts;
