@@ -771,6 +771,10 @@ def nsplit_figures(torch, dist, ops, world, rank):
         runf, modef = graphed(lambda: [fused[i].forward(x) for i in range(copies)])
         entry["us_fused"] = timed(runf, 4) / copies
         entry["fused_launch"] = modef
+        # without the barrier in front: each layer object alternates two outputs, and between two uses of one of them
+        # lie the barriers of the other rotated layers, so no rank can still be reading it
+        runf1, _ = graphed(lambda: [fused[i].forward(x, guard=False) for i in range(copies)])
+        entry["us_fused_one_barrier"] = timed(runf1, 4) / copies
         out[f"m{M}"] = entry
     return out
 

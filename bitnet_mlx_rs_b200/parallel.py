@@ -73,8 +73,12 @@ class FusedNSplitBitLinear:
     16 tokens, the persistent GEMM above) stores its column slice straight into ALL ranks' full-width
     outputs (plain peer stores over NVLink from the kernel's epilogue), and a symmetric-memory barrier
     tells the ranks that the slices have arrived.  The outputs live in torch symmetric memory, which maps every rank's
-    buffer into every process.  The barrier before the launch keeps a fast rank from overwriting an
-    output that a slow rank is still reading."""
+    buffer into every process.  Two output buffers alternate from call to call.  With `guard=True` (the default) a
+    barrier before the launch keeps a fast rank from overwriting an output that a slow rank is still reading; with
+    `guard=False` that barrier is dropped, which is safe when every rank is through with the result of call n before
+    any rank passes the barrier of call n + 1 -- true for calls issued in stream order, one after the other, since a
+    buffer is written again only by call n + 2 (a captured graph that holds ONE call replays the same buffer every
+    time: keep the guard there)."""
 
     def __init__(self, packed_full: torch.Tensor, scale: float, out_features: int, in_features: int, max_tokens: int = 16,
                  group=None):
@@ -91,22 +95,31 @@ class FusedNSplitBitLinear:
         self.packed = self.packed.contiguous()
         if (self.r0 * 4) % 16:
             raise ValueError("a rank's first column must be 16-byte aligned in the output row")
-        self.y = symm_mem.empty((max_tokens, out_features), dtype=torch.float32, device=packed_full.device)
-        self.handle = symm_mem.rendezvous(self.y, self.group)
-        # this rank's slice inside every rank's output
-        self.peer_ptrs = [int(ptr) + 4 * self.r0 for ptr in self.handle.buffer_ptrs]
+        self.ys, self.handles, self.peer_ptrs = [], [], []
+        for _ in range(2):
+            y = symm_mem.empty((max_tokens, out_features), dtype=torch.float32, device=packed_full.device)
+            handle = symm_mem.rendezvous(y, self.group)
+            self.ys.append(y)
+            self.handles.append(handle)
+            # this rank's slice inside every rank's output
+            self.peer_ptrs.append([int(ptr) + 4 * self.r0 for ptr in handle.buffer_ptrs])
+        self._turn = 0
         self._unused = torch.empty((max_tokens, self.r1 - self.r0), dtype=torch.float32, device=packed_full.device)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        """x [M,K] (replicated on every rank) -> y [M,N] (complete on every rank, a view of the shared output)."""
+    def forward(self, x: torch.Tensor, guard: bool = True) -> torch.Tensor:
+        """x [M,K] (replicated on every rank) -> y [M,N] (complete on every rank, a view of one of the two shared
+        outputs; valid until the call after next)."""
         M = x.shape[0]
         if M > self.max_tokens:
             raise ValueError(f"{M} tokens > max_tokens {self.max_tokens}")
-        self.handle.barrier(channel=0)   # nobody still reads the previous result
+        t = self._turn
+        self._turn ^= 1
+        if guard:
+            self.handles[t].barrier(channel=0)   # nobody still reads what this buffer held
         self._ops.bitlinear_forward(self.packed, self.scale, x, self.r1 - self.r0, path="decode" if M <= 16 else "prefill",
-                                    out=self._unused[:M], ldy=self.out_features, y_peers=self.peer_ptrs)
-        self.handle.barrier(channel=1)   # every rank's slice has landed everywhere
-        return self.y[:M]
+                                    out=self._unused[:M], ldy=self.out_features, y_peers=self.peer_ptrs[t])
+        self.handles[t].barrier(channel=1)   # every rank's slice has landed everywhere
+        return self.ys[t][:M]
 
 
 def row_sharded_forward(forward: Callable[[torch.Tensor], torch.Tensor], x_all: torch.Tensor, group=None) -> torch.Tensor:
