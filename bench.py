@@ -712,11 +712,12 @@ def nsplit_figures(torch, dist, ops, world, rank):
     n_local = N // world
     gen = torch.Generator(device="cuda").manual_seed(7)   # the same weights on every rank; each keeps its slice
     copies = max(2, -(-(160 << 20) // (n_local * K // 4)))   # rotate enough slices to exceed L2
+    copies += copies % 2   # an even count: the two shared outputs then alternate across graph replays too
     layers, fused, full0 = [], [], None
     for c in range(copies):
         full = gen_packed_on_device(torch, N * K, gen)
         layers.append(parallel.NSplitBitLinear(full, 0.01, N, K))
-        fused.append(parallel.FusedNSplitBitLinear(full, 0.01, N, K, max_tokens=256))
+        fused.append(parallel.FusedNSplitBitLinear(full, 0.01, N, K, max_tokens=256, share_outputs_with=fused[0] if fused else None))
         if c == 0:
             full0 = full
         del full
@@ -771,8 +772,8 @@ def nsplit_figures(torch, dist, ops, world, rank):
         runf, modef = graphed(lambda: [fused[i].forward(x) for i in range(copies)])
         entry["us_fused"] = timed(runf, 4) / copies
         entry["fused_launch"] = modef
-        # without the barrier in front: each layer object alternates two outputs, and between two uses of one of them
-        # lie the barriers of the other rotated layers, so no rank can still be reading it
+        # without the barrier in front: the rotated layers alternate two outputs between them, calls are issued in
+        # stream order, so a buffer is written again only after every rank passed the barrier of the call in between
         runf1, _ = graphed(lambda: [fused[i].forward(x, guard=False) for i in range(copies)])
         entry["us_fused_one_barrier"] = timed(runf1, 4) / copies
         out[f"m{M}"] = entry

@@ -81,7 +81,10 @@ class FusedNSplitBitLinear:
     time: keep the guard there)."""
 
     def __init__(self, packed_full: torch.Tensor, scale: float, out_features: int, in_features: int, max_tokens: int = 16,
-                 group=None):
+                 group=None, share_outputs_with: "FusedNSplitBitLinear | None" = None):
+        """share_outputs_with: another layer of the same output width, token limit and group whose two output buffers
+        this one uses too (the layers of a model need one pair between them); the alternation then runs over the
+        calls of all sharing layers."""
         import torch.distributed._symmetric_memory as symm_mem
 
         from . import ops
@@ -95,15 +98,19 @@ class FusedNSplitBitLinear:
         self.packed = self.packed.contiguous()
         if (self.r0 * 4) % 16:
             raise ValueError("a rank's first column must be 16-byte aligned in the output row")
-        self.ys, self.handles, self.peer_ptrs = [], [], []
-        for _ in range(2):
-            y = symm_mem.empty((max_tokens, out_features), dtype=torch.float32, device=packed_full.device)
-            handle = symm_mem.rendezvous(y, self.group)
-            self.ys.append(y)
-            self.handles.append(handle)
-            # this rank's slice inside every rank's output
-            self.peer_ptrs.append([int(ptr) + 4 * self.r0 for ptr in handle.buffer_ptrs])
-        self._turn = 0
+        if share_outputs_with is not None:
+            o = share_outputs_with
+            if (o.out_features, o.max_tokens, o.world) != (out_features, max_tokens, self.world):
+                raise ValueError("layers that share outputs must agree on width, token limit and group size")
+            self._out = o._out
+        else:
+            self._out = {"ys": [], "handles": [], "turn": 0}
+            for _ in range(2):
+                y = symm_mem.empty((max_tokens, out_features), dtype=torch.float32, device=packed_full.device)
+                self._out["ys"].append(y)
+                self._out["handles"].append(symm_mem.rendezvous(y, self.group))
+        # this rank's slice inside every rank's output
+        self.peer_ptrs = [[int(ptr) + 4 * self.r0 for ptr in h.buffer_ptrs] for h in self._out["handles"]]
         self._unused = torch.empty((max_tokens, self.r1 - self.r0), dtype=torch.float32, device=packed_full.device)
 
     def forward(self, x: torch.Tensor, guard: bool = True) -> torch.Tensor:
@@ -112,14 +119,15 @@ class FusedNSplitBitLinear:
         M = x.shape[0]
         if M > self.max_tokens:
             raise ValueError(f"{M} tokens > max_tokens {self.max_tokens}")
-        t = self._turn
-        self._turn ^= 1
+        t = self._out["turn"]
+        self._out["turn"] = t ^ 1
+        handle = self._out["handles"][t]
         if guard:
-            self.handles[t].barrier(channel=0)   # nobody still reads what this buffer held
+            handle.barrier(channel=0)   # nobody still reads what this buffer held
         self._ops.bitlinear_forward(self.packed, self.scale, x, self.r1 - self.r0, path="decode" if M <= 16 else "prefill",
                                     out=self._unused[:M], ldy=self.out_features, y_peers=self.peer_ptrs[t])
-        self.handles[t].barrier(channel=1)   # every rank's slice has landed everywhere
-        return self.ys[t][:M]
+        handle.barrier(channel=1)   # every rank's slice has landed everywhere
+        return self._out["ys"][t][:M]
 
 
 def row_sharded_forward(forward: Callable[[torch.Tensor], torch.Tensor], x_all: torch.Tensor, group=None) -> torch.Tensor:
