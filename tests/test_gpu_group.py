@@ -35,6 +35,7 @@ def check_members(host, members, F):
 
 @pytest.mark.parametrize("H,F,token_counts", [
     (2560, 6912, [1, 4, 8]),                       # the 2B shape: ten warps x one step, fourteen x two
+    (2560, 6912, [16, 9, 1]),                      # the same with two token tiles: five warps x two steps, seven x four
     (256, 192, [1, 2, 3, 5, 8]),                   # every image height (1, 2, 4, 8 token rows)
     (128, 1088, [7, 1]),                           # seventeen chunks over five warps: uneven K slices
     (1024, 2048, [16, 9, 1, 12]),                  # two token tiles
